@@ -1,0 +1,280 @@
+"""CudaAccelerator and its memory manager: the host-side mirror of the reference's backend objects.
+
+`CudaAccelerator` stands where `new CudaAccelerator(deviceId: 0)` stands in
+src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:184-194; `CudaMemoryManager` and `UnifiedBuffer`
+keep the member names of src/Backends/DotCompute.Backends.CUDA/Memory/CudaMemoryManager.cs:140-292 and
+src/Core/DotCompute.Abstractions/Interfaces/IUnifiedMemoryBuffer.cs:13-261. All work is done by libdcb200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import threading
+
+import numpy as np
+
+from . import errors, native as N
+
+_DTYPE_TO_T = {
+    np.dtype(np.int8): N.T_I8, np.dtype(np.uint8): N.T_U8, np.dtype(np.int16): N.T_I16, np.dtype(np.uint16): N.T_U16,
+    np.dtype(np.int32): N.T_I32, np.dtype(np.uint32): N.T_U32, np.dtype(np.int64): N.T_I64, np.dtype(np.uint64): N.T_U64,
+    np.dtype(np.float32): N.T_F32, np.dtype(np.float64): N.T_F64, np.dtype(np.bool_): N.T_BOOL,
+}
+_T_TO_DTYPE = {v: k for k, v in _DTYPE_TO_T.items()}
+
+
+def dcb_type(dtype) -> int:
+    dt = np.dtype(dtype)
+    if dt not in _DTYPE_TO_T:
+        raise errors.NotSupportedException(f"Type {dt} is not supported for CUDA kernel generation.")
+    return _DTYPE_TO_T[dt]
+
+
+def np_dtype(t: int) -> np.dtype:
+    return _T_TO_DTYPE[t]
+
+
+class BufferState(enum.Enum):
+    """Residency states of IUnifiedMemoryBuffer.State."""
+    Uninitialized = 0
+    HostOnly = 1
+    DeviceOnly = 2
+    Synchronized = 3
+    HostDirty = 4
+    DeviceDirty = 5
+    Disposed = 6
+
+
+class CudaAccelerator:
+    """One GPU: context, stream, compiled-pipeline cache."""
+
+    _default = None
+    _lock = threading.Lock()
+
+    def __init__(self, deviceId: int = 0):
+        self._h = C.c_void_p()
+        N.check(N.lib().dcb_init(int(deviceId), C.byref(self._h)))
+        self.DeviceId = int(deviceId)
+        self.Memory = CudaMemoryManager(self)
+        self._disposed = False
+        name = C.create_string_buffer(256)
+        sm, mem, maj, mnr = C.c_int32(), C.c_int64(), C.c_int32(), C.c_int32()
+        N.check(N.lib().dcb_device_info(self._h, name, 256, C.byref(sm), C.byref(mem), C.byref(maj), C.byref(mnr)), self._h)
+        self.Name = name.value.decode()
+        self.MultiProcessorCount = sm.value
+        self.TotalMemory = mem.value
+        self.ComputeCapability = (maj.value, mnr.value)
+
+    @classmethod
+    def Default(cls) -> "CudaAccelerator":
+        """Process-wide accelerator on the device torchrun assigned (LOCAL_RANK), else device 0."""
+        import os
+        with cls._lock:
+            if cls._default is None or cls._default._disposed:
+                cls._default = cls(int(os.environ.get("LOCAL_RANK", "0")))
+            return cls._default
+
+    @property
+    def handle(self):
+        if self._disposed:
+            raise errors.ObjectDisposedException("CudaAccelerator")
+        return self._h
+
+    def SetStream(self, cuda_stream: int | None) -> None:
+        """Enqueue on an existing cudaStream_t (for instance torch's current stream); None restores the own stream."""
+        N.check(N.lib().dcb_set_stream(self.handle, C.c_void_p(cuda_stream or 0)), self._h)
+
+    def Synchronize(self) -> None:
+        N.check(N.lib().dcb_stream_sync(self.handle, None), self._h)
+
+    def SetSpinLimit(self, max_polls: int) -> None:
+        N.check(N.lib().dcb_set_spin_limit(self.handle, int(max_polls)), self._h)
+
+    @property
+    def LaunchCount(self) -> int:
+        v = C.c_int64()
+        N.check(N.lib().dcb_launch_count(self.handle, C.byref(v)), self._h)
+        return v.value
+
+    def Dispose(self) -> None:
+        if not self._disposed:
+            self._disposed = True
+            N.lib().dcb_shutdown(self._h)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.Dispose()
+
+
+class PinnedArray:
+    """Page-locked host memory viewed as a numpy array (CudaPinnedMemoryAllocator)."""
+
+    def __init__(self, acc: CudaAccelerator, length: int, dtype):
+        self._acc = acc
+        self.dtype = np.dtype(dtype)
+        self.Length = int(length)
+        self._ptr = C.c_void_p()
+        nbytes = max(self.Length * self.dtype.itemsize, 1)
+        N.check(N.lib().dcb_host_alloc_pinned(acc.handle, nbytes, C.byref(self._ptr)), acc.handle)
+        raw = (C.c_char * nbytes).from_address(self._ptr.value)
+        self.array = np.frombuffer(raw, dtype=self.dtype, count=self.Length)
+
+    @property
+    def ptr(self) -> int:
+        return self._ptr.value
+
+    def Dispose(self) -> None:
+        if self._ptr:
+            self.array = None
+            N.lib().dcb_host_free_pinned(self._acc.handle, self._ptr)
+            self._ptr = C.c_void_p()
+
+
+class UnifiedBuffer:
+    """Device-resident typed buffer: the IUnifiedMemoryBuffer<T> of this engine."""
+
+    def __init__(self, acc: CudaAccelerator, handle, length: int, dtype, parent=None):
+        self._acc = acc
+        self._h = handle
+        self.Length = int(length)
+        self.dtype = np.dtype(dtype)
+        self._parent = parent       # keeps the owner of a slice alive
+        self.State = BufferState.DeviceOnly
+        self.IsDisposed = False
+
+    # -- properties of the interface
+    @property
+    def SizeInBytes(self) -> int:
+        return self.Length * self.dtype.itemsize
+
+    @property
+    def Accelerator(self) -> CudaAccelerator:
+        return self._acc
+
+    @property
+    def IsOnDevice(self) -> bool:
+        return not self.IsDisposed
+
+    @property
+    def IsOnHost(self) -> bool:
+        return False
+
+    @property
+    def handle(self):
+        if self.IsDisposed:
+            raise errors.ObjectDisposedException("UnifiedBuffer")
+        return self._h
+
+    def GetDeviceMemory(self) -> int:
+        return N.lib().dcb_devptr(self.handle) or 0
+
+    # -- transfers
+    def CopyFromAsync(self, source: np.ndarray, offset: int = 0) -> None:
+        if source is None:
+            raise errors.ArgumentNullException("source")
+        src = np.ascontiguousarray(source, dtype=self.dtype)
+        if offset < 0 or offset + src.size > self.Length:
+            raise errors.ArgumentException("source does not fit the buffer at this offset")
+        N.check(N.lib().dcb_h2d_async(self._acc.handle, self.handle, offset * self.dtype.itemsize,
+                                      src.ctypes.data_as(C.c_void_p), src.nbytes, None), self._acc.handle)
+        self._acc.Synchronize()   # `src` may be a temporary
+        self.State = BufferState.Synchronized
+
+    def CopyToAsync(self, destination: np.ndarray | None = None, offset: int = 0, count: int | None = None) -> np.ndarray:
+        n = self.Length - offset if count is None else int(count)
+        if offset < 0 or n < 0 or offset + n > self.Length:
+            raise errors.ArgumentException("range outside the buffer")
+        if destination is None:
+            destination = np.empty(n, dtype=self.dtype)
+        if destination.dtype != self.dtype or destination.size < n or not destination.flags.c_contiguous:
+            raise errors.ArgumentException("destination must be a contiguous array of the buffer's element type")
+        N.check(N.lib().dcb_d2h_async(self._acc.handle, destination.ctypes.data_as(C.c_void_p), self.handle,
+                                      offset * self.dtype.itemsize, n * self.dtype.itemsize, None), self._acc.handle)
+        self._acc.Synchronize()
+        return destination
+
+    def ToArray(self) -> np.ndarray:
+        return self.CopyToAsync()
+
+    def FillAsync(self, value, offset: int = 0, count: int | None = None) -> None:
+        n = self.Length - offset if count is None else int(count)
+        pat = np.array([value], dtype=self.dtype)
+        N.check(N.lib().dcb_fill_async(self._acc.handle, self.handle, offset * self.dtype.itemsize,
+                                       pat.ctypes.data_as(C.c_void_p), self.dtype.itemsize, n, None), self._acc.handle)
+        self._acc.Synchronize()
+
+    # -- views (zero copy)
+    def Slice(self, offset: int, length: int) -> "UnifiedBuffer":
+        if offset < 0 or length < 0 or offset + length > self.Length:
+            raise errors.ArgumentException("slice outside the buffer")
+        h = C.c_void_p()
+        N.check(N.lib().dcb_buf_slice(self._acc.handle, self.handle, offset * self.dtype.itemsize,
+                                      length * self.dtype.itemsize, C.byref(h)), self._acc.handle)
+        return UnifiedBuffer(self._acc, h, length, self.dtype, parent=self)
+
+    def AsType(self, dtype) -> "UnifiedBuffer":
+        dt = np.dtype(dtype)
+        if self.SizeInBytes % dt.itemsize:
+            raise errors.ArgumentException("buffer size is not a multiple of the new element size")
+        h = C.c_void_p()
+        N.check(N.lib().dcb_buf_slice(self._acc.handle, self.handle, 0, self.SizeInBytes, C.byref(h)), self._acc.handle)
+        return UnifiedBuffer(self._acc, h, self.SizeInBytes // dt.itemsize, dt, parent=self)
+
+    def EnsureOnDevice(self) -> None:
+        _ = self.handle
+
+    def Dispose(self) -> None:
+        if not self.IsDisposed:
+            self.IsDisposed = True
+            self.State = BufferState.Disposed
+            if not self._acc._disposed:
+                N.lib().dcb_free(self._acc._h, self._h)
+
+    def __len__(self):
+        return self.Length
+
+
+class CudaMemoryManager:
+    """AllocateAsync / AllocateAndCopyAsync / FreeAsync over the device's stream-ordered pool."""
+
+    def __init__(self, acc: CudaAccelerator):
+        self._acc = acc
+
+    def AllocateAsync(self, length: int, dtype) -> UnifiedBuffer:
+        if length < 0:
+            raise errors.ArgumentException("length must not be negative")
+        dt = np.dtype(dtype)
+        dcb_type(dt)
+        h = C.c_void_p()
+        N.check(N.lib().dcb_alloc(self._acc.handle, int(length) * dt.itemsize, C.byref(h)), self._acc.handle)
+        return UnifiedBuffer(self._acc, h, length, dt)
+
+    def AllocateAndCopyAsync(self, source: np.ndarray) -> UnifiedBuffer:
+        if source is None:
+            raise errors.ArgumentNullException("source")
+        src = np.ascontiguousarray(source)
+        buf = self.AllocateAsync(src.size, src.dtype)
+        if src.size:
+            buf.CopyFromAsync(src)
+        return buf
+
+    def WrapDevicePointer(self, device_ptr: int, length: int, dtype) -> UnifiedBuffer:
+        """Adopt memory owned by someone else (for instance a torch tensor's data_ptr()) without copying."""
+        dt = np.dtype(dtype)
+        h = C.c_void_p()
+        N.check(N.lib().dcb_buf_wrap(self._acc.handle, C.c_void_p(device_ptr), int(length) * dt.itemsize, C.byref(h)), self._acc.handle)
+        return UnifiedBuffer(self._acc, h, length, dt)
+
+    def AllocatePinned(self, length: int, dtype) -> PinnedArray:
+        return PinnedArray(self._acc, length, dtype)
+
+    def FreeAsync(self, buffer: UnifiedBuffer) -> None:
+        buffer.Dispose()
+
+    @property
+    def Statistics(self) -> dict:
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        N.check(N.lib().dcb_memory_stats(self._acc.handle, C.byref(a), C.byref(b), C.byref(c)), self._acc.handle)
+        return {"CurrentAllocatedMemory": a.value, "PeakMemoryUsage": b.value, "AllocationCount": c.value}

@@ -1,0 +1,1115 @@
+// dcb_api.cu — the C ABI of libdcb200.so (see include/dcb200.h).
+//
+// Host side of the engine: context and stream per GPU, stream-ordered device memory and pinned staging,
+// translation of a query's lambdas into one fused kernel (NVRTC, or the ahead-of-time table), launch
+// shaping, and the semantics of the terminal operators. Everything here runs on the GPU or fails with a
+// status; there is no host computation path.
+#include <cuda_runtime.h>
+#include <nvrtc.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/dcb200.h"
+#include "dcb_builtin.h"
+#include "dcb_kernels.cuh"
+#include "dcb_translate.h"
+
+// Text of dcb_kernels.cuh, generated at build time, handed to NVRTC in front of every chain.
+static const char* const kKernelsHeaderText =
+#include "build/dcb_kernels_embed.inc"
+    ;
+
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kMaxPartials = 8192;
+constexpr size_t kHostChunkBytes = 32u << 20;
+
+thread_local char tl_error[1024] = "";
+
+struct Scratch {
+    dcb::Partial* partials = nullptr;
+    unsigned int* words = nullptr;      // [0] reduce ticket, [1] compaction tile counter, [2] abort flag
+    unsigned long long* desc = nullptr; // look-back descriptors
+    size_t desc_cap = 0;
+    unsigned int epoch = 0;
+};
+
+}  // namespace
+
+struct dcb_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    cudaStream_t own_stream = nullptr, stream = nullptr, copy_stream = nullptr, out_stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    uint32_t spin_limit = 1u << 22;
+    char err[1024] = "";
+    std::mutex mu;
+    std::map<std::string, dcb_pipeline*> cache;
+    int64_t bytes_in_use = 0, peak_bytes = 0, n_allocs = 0, launches = 0;
+    void* stage_in[2] = {nullptr, nullptr};
+    size_t stage_in_cap[2] = {0, 0};
+    void* stage_out = nullptr;
+    size_t stage_out_cap = 0;
+    bool alive = true;
+};
+
+struct dcb_buf {
+    dcb_ctx* ctx = nullptr;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    bool owned = false;
+};
+
+struct dcb_pipeline {
+    dcb_ctx* ctx = nullptr;
+    dcbt::ChainInfo info;
+    std::string source;
+    cudaLibrary_t lib = nullptr;
+    const void* k_vec = nullptr;
+    const void* k_scalar = nullptr;
+    bool precompiled = false;
+    int unroll = 4;
+    int occ_vec = 1, occ_scalar = 1;     // resident blocks per SM
+    int rows_vec = 1, rows_scalar = 1;   // compaction rows per warp
+    Scratch sc;
+    dcb::DeviceResult* d_result = nullptr;
+    void* h_record = nullptr;            // pinned, DCB_DEVICE_RESULT_BYTES * kMaxChunks
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    double compile_ms = 0;
+    int refs = 1;
+    bool alive = true;
+};
+
+struct dcb_kernel {
+    dcb_ctx* ctx = nullptr;
+    cudaLibrary_t lib = nullptr;
+    const void* fn = nullptr;
+};
+
+namespace {
+
+dcb_status set_err(dcb_ctx* ctx, dcb_status st, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    snprintf(tl_error, sizeof tl_error, "%s", buf);
+    if (ctx) snprintf(ctx->err, sizeof ctx->err, "%s", buf);
+    return st;
+}
+
+dcb_status cuda_fail(dcb_ctx* ctx, cudaError_t e, const char* what) {
+    dcb_status st = DCB_ERR_CUDA;
+    if (e == cudaErrorMemoryAllocation) st = DCB_ERR_OUT_OF_MEMORY;
+    else if (e == cudaErrorNotReady) st = DCB_ERR_NOT_READY;
+    else if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) st = DCB_ERR_NO_DEVICE;
+    else if (e == cudaErrorInvalidValue) st = DCB_ERR_INVALID_ARGUMENT;
+    (void)cudaGetLastError();
+    return set_err(ctx, st, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+#define CU(ctx, call)                                                \
+    do {                                                             \
+        cudaError_t e__ = (call);                                    \
+        if (e__ != cudaSuccess) return cuda_fail((ctx), e__, #call); \
+    } while (0)
+
+#define NEED(ctx, cond, what)                                                         \
+    do {                                                                              \
+        if (!(cond)) return set_err((ctx), DCB_ERR_INVALID_ARGUMENT, "%s", (what));   \
+    } while (0)
+
+dcb_status use(dcb_ctx* ctx) {
+    if (!ctx) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "ctx is null");
+    if (!ctx->alive) return set_err(nullptr, DCB_ERR_DISPOSED, "context was shut down");
+    CU(ctx, cudaSetDevice(ctx->device));
+    return DCB_OK;
+}
+
+cudaStream_t pick(dcb_ctx* ctx, void* stream) { return stream ? (cudaStream_t)stream : ctx->stream; }
+
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+__global__ void fill_kernel(unsigned char* dst, size_t count, unsigned long long pattern, int pattern_bytes) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        switch (pattern_bytes) {
+            case 1: dst[i] = (unsigned char)pattern; break;
+            case 2: reinterpret_cast<unsigned short*>(dst)[i] = (unsigned short)pattern; break;
+            case 4: reinterpret_cast<unsigned int*>(dst)[i] = (unsigned int)pattern; break;
+            default: reinterpret_cast<unsigned long long*>(dst)[i] = pattern; break;
+        }
+    }
+}
+
+// Bytes a pointer must be aligned to for the vector variant: one pack of E elements, at most 16.
+size_t pack_align(int elems, int type) { return (size_t)std::min(16, elems * dcbt::type_size(type)); }
+
+int compact_rows(int block, int elems, int out_type) {
+    const int per_row = block * elems * dcbt::type_size(out_type);
+    const int fit = 32768 / per_row;
+    return fit < 1 ? 1 : (fit > 4 ? 4 : fit);
+}
+
+dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
+    dcb_ctx* ctx = p->ctx;
+    Scratch& sc = p->sc;
+    if (!sc.partials) {
+        CU(ctx, cudaMalloc(&sc.partials, sizeof(dcb::Partial) * kMaxPartials));
+        CU(ctx, cudaMalloc(&sc.words, 64));
+        CU(ctx, cudaMemset(sc.words, 0, 64));
+    }
+    if ((size_t)num_tiles > sc.desc_cap) {
+        size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
+        cap = std::max(cap, sc.desc_cap * 2);
+        if (sc.desc) { CU(ctx, cudaStreamSynchronize(s)); CU(ctx, cudaFree(sc.desc)); sc.desc = nullptr; }
+        CU(ctx, cudaMalloc(&sc.desc, cap * sizeof(unsigned long long)));
+        CU(ctx, cudaMemset(sc.desc, 0, cap * sizeof(unsigned long long)));
+        sc.desc_cap = cap;
+        sc.epoch = 0;
+    }
+    return DCB_OK;
+}
+
+dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
+    const int unroll = env_int("DCB200_UNROLL", 4);
+    p->unroll = unroll;
+    p->source = dcbt::build_program(p->info, "", kKernelsHeaderText, kBlock, unroll, true);
+    nvrtcProgram prog = nullptr;
+    if (nvrtcCreateProgram(&prog, p->source.c_str(), "dcb_pipeline.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        return set_err(ctx, DCB_ERR_COMPILE, "nvrtcCreateProgram failed");
+    // No --use_fast_math and no FMA contraction: a Select must round exactly like the C# lambda does.
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-fmad=false", "-lineinfo"};
+    nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+    if (r != NVRTC_SUCCESS) {
+        size_t n = 0;
+        nvrtcGetProgramLogSize(prog, &n);
+        std::string log(n + 1, '\0');
+        nvrtcGetProgramLog(prog, &log[0]);
+        nvrtcDestroyProgram(&prog);
+        return set_err(ctx, DCB_ERR_COMPILE, "NVRTC: %s: %.800s", nvrtcGetErrorString(r), log.c_str());
+    }
+    size_t sz = 0;
+    nvrtcGetCUBINSize(prog, &sz);
+    std::vector<char> cubin(sz);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    CU(ctx, cudaLibraryLoadData(&p->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    const char* stem = (p->info.terminal == DCB_OP_TOARRAY) ? (p->info.has_filter ? "dcb_compact_" : "dcb_map_") : "dcb_reduce_";
+    cudaKernel_t kv = nullptr, ks = nullptr;
+    CU(ctx, cudaLibraryGetKernel(&kv, p->lib, (std::string(stem) + "vec").c_str()));
+    CU(ctx, cudaLibraryGetKernel(&ks, p->lib, (std::string(stem) + "scalar").c_str()));
+    p->k_vec = (const void*)kv;
+    p->k_scalar = (const void*)ks;
+    return DCB_OK;
+}
+
+dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
+    const int e_vec = 16 / dcbt::type_size(p->info.in0);
+    p->rows_vec = compact_rows(kBlock, e_vec, p->info.out_type);
+    p->rows_scalar = compact_rows(kBlock, 1, p->info.out_type);
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_vec, kBlock, 0) == cudaSuccess && occ > 0) p->occ_vec = occ;
+    else { (void)cudaGetLastError(); p->occ_vec = 4; }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_scalar, kBlock, 0) == cudaSuccess && occ > 0) p->occ_scalar = occ;
+    else { (void)cudaGetLastError(); p->occ_scalar = 4; }
+    const int cap = env_int("DCB200_BLOCKS_PER_SM", 0);
+    if (cap > 0) { p->occ_vec = std::min(p->occ_vec, cap); p->occ_scalar = std::min(p->occ_scalar, cap); }
+    CU(ctx, cudaMalloc(&p->d_result, DCB_DEVICE_RESULT_BYTES));
+    CU(ctx, cudaMemset(p->d_result, 0, DCB_DEVICE_RESULT_BYTES));
+    CU(ctx, cudaHostAlloc(&p->h_record, DCB_DEVICE_RESULT_BYTES, cudaHostAllocDefault));
+    CU(ctx, cudaEventCreate(&p->ev0));
+    CU(ctx, cudaEventCreate(&p->ev1));
+    return ensure_scratch(p, 0, ctx->stream);
+}
+
+void free_pipeline(dcb_pipeline* p) {
+    if (!p) return;
+    if (p->sc.partials) cudaFree(p->sc.partials);
+    if (p->sc.words) cudaFree(p->sc.words);
+    if (p->sc.desc) cudaFree(p->sc.desc);
+    if (p->d_result) cudaFree(p->d_result);
+    if (p->h_record) cudaFreeHost(p->h_record);
+    if (p->ev0) cudaEventDestroy(p->ev0);
+    if (p->ev1) cudaEventDestroy(p->ev1);
+    if (p->lib) cudaLibraryUnload(p->lib);
+    p->alive = false;
+    delete p;
+}
+
+dcb_status desc_to_ops(const dcb_pipeline_desc* desc, std::vector<dcbt::OpSpec>* ops, char* err, size_t err_cap) {
+    if (!desc || desc->n_ops <= 0 || !desc->ops) { snprintf(err, err_cap, "pipeline description is null or empty"); return DCB_ERR_INVALID_ARGUMENT; }
+    for (int i = 0; i < desc->n_ops; ++i) {
+        dcbt::OpSpec o;
+        o.kind = desc->ops[i].kind;
+        const bool needs_lambda = o.kind == DCB_OP_SELECT || o.kind == DCB_OP_WHERE || o.kind == DCB_OP_ZIP;
+        if (needs_lambda && !desc->ops[i].lambda) { snprintf(err, err_cap, "operator %d has a null lambda", i); return DCB_ERR_INVALID_ARGUMENT; }
+        if (desc->ops[i].lambda) o.lambda = desc->ops[i].lambda;
+        ops->push_back(o);
+    }
+    return DCB_OK;
+}
+
+}  // namespace
+
+// ============================================================================================ status
+extern "C" int32_t dcb_abi_version(void) { return DCB_ABI_VERSION; }
+
+extern "C" int32_t dcb_status_class(dcb_status s) {
+    if (s == DCB_OK) return DCB_CLASS_NONE;
+    switch (s / 100) {
+        case 1: return DCB_CLASS_TRANSIENT;
+        case 2: return DCB_CLASS_RESOURCE;
+        case 3: return DCB_CLASS_PROGRAMMER;
+        case 4: return DCB_CLASS_FATAL;
+        case 5: return DCB_CLASS_QUERY;
+        default: return DCB_CLASS_FATAL;
+    }
+}
+
+extern "C" const char* dcb_status_name(dcb_status s) {
+    switch (s) {
+        case DCB_OK: return "DCB_OK";
+        case DCB_ERR_NOT_READY: return "DCB_ERR_NOT_READY";
+        case DCB_ERR_TIMEOUT: return "DCB_ERR_TIMEOUT";
+        case DCB_ERR_OUT_OF_MEMORY: return "DCB_ERR_OUT_OF_MEMORY";
+        case DCB_ERR_OUTPUT_TOO_SMALL: return "DCB_ERR_OUTPUT_TOO_SMALL";
+        case DCB_ERR_INVALID_ARGUMENT: return "DCB_ERR_INVALID_ARGUMENT";
+        case DCB_ERR_NOT_SUPPORTED: return "DCB_ERR_NOT_SUPPORTED";
+        case DCB_ERR_COMPILE: return "DCB_ERR_COMPILE";
+        case DCB_ERR_DISPOSED: return "DCB_ERR_DISPOSED";
+        case DCB_ERR_NO_DEVICE: return "DCB_ERR_NO_DEVICE";
+        case DCB_ERR_CUDA: return "DCB_ERR_CUDA";
+        case DCB_ERR_EMPTY_SEQUENCE: return "DCB_ERR_EMPTY_SEQUENCE";
+        case DCB_ERR_OVERFLOW: return "DCB_ERR_OVERFLOW";
+        default: return "DCB_ERR_UNKNOWN";
+    }
+}
+
+extern "C" int32_t dcb_type_size(int32_t type) { return dcbt::type_size(type); }
+
+// ========================================================================================= lifecycle
+extern "C" dcb_status dcb_device_count(int32_t* out_count) {
+    if (!out_count) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "out_count is null");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    *out_count = (e == cudaSuccess) ? n : 0;
+    if (e != cudaSuccess || n == 0) { (void)cudaGetLastError(); return set_err(nullptr, DCB_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e)); }
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_init(int32_t device, dcb_ctx** out_ctx) {
+    if (!out_ctx) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "out_ctx is null");
+    *out_ctx = nullptr;
+    int n = 0;
+    dcb_status st = dcb_device_count(&n);
+    if (st != DCB_OK) return st;
+    if (device < 0 || device >= n) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "device %d out of range (0..%d)", device, n - 1);
+    dcb_ctx* ctx = new dcb_ctx();
+    ctx->device = device;
+    cudaError_t e = cudaSetDevice(device);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaDeviceGetDefaultMemPool(&ctx->pool, device);
+    if (e == cudaSuccess) {
+        // Keep freed blocks in the pool: a query allocates and frees the same sizes over and over.
+        unsigned long long keep = ~0ull;
+        e = cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    if (e != cudaSuccess) { dcb_status s = cuda_fail(nullptr, e, "dcb_init"); delete ctx; return s; }
+    ctx->stream = ctx->own_stream;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    ctx->spin_limit = (uint32_t)env_int("DCB200_SPIN_LIMIT", 1 << 22);
+    if (prop.major != 10) {
+        delete ctx;
+        return set_err(nullptr, DCB_ERR_NO_DEVICE, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+    }
+    *out_ctx = ctx;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_shutdown(dcb_ctx* ctx) {
+    if (!ctx) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "ctx is null");
+    if (!ctx->alive) return DCB_ERR_DISPOSED;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    for (auto& kv : ctx->cache) free_pipeline(kv.second);
+    ctx->cache.clear();
+    for (int i = 0; i < 2; ++i) if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
+    if (ctx->stage_out) cudaFree(ctx->stage_out);
+    cudaStreamDestroy(ctx->own_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+    cudaStreamDestroy(ctx->out_stream);
+    ctx->alive = false;
+    delete ctx;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_last_error(dcb_ctx* ctx, char* buf, size_t cap) {
+    if (!buf || cap == 0) return DCB_ERR_INVALID_ARGUMENT;
+    snprintf(buf, cap, "%s", (ctx && ctx->alive) ? ctx->err : tl_error);
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_device_info(dcb_ctx* ctx, char* name, size_t name_cap, int32_t* sm_count, int64_t* total_mem,
+                                      int32_t* cc_major, int32_t* cc_minor) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    cudaDeviceProp prop;
+    CU(ctx, cudaGetDeviceProperties(&prop, ctx->device));
+    if (name && name_cap) snprintf(name, name_cap, "%s", prop.name);
+    if (sm_count) *sm_count = prop.multiProcessorCount;
+    if (total_mem) *total_mem = (int64_t)prop.totalGlobalMem;
+    if (cc_major) *cc_major = prop.major;
+    if (cc_minor) *cc_minor = prop.minor;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_set_stream(dcb_ctx* ctx, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    ctx->stream = stream ? (cudaStream_t)stream : ctx->own_stream;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_stream_sync(dcb_ctx* ctx, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    CU(ctx, cudaStreamSynchronize(pick(ctx, stream)));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, max_polls > 0, "max_polls must be positive");
+    ctx->spin_limit = max_polls;
+    return DCB_OK;
+}
+
+// ============================================================================================ memory
+extern "C" dcb_status dcb_alloc(dcb_ctx* ctx, size_t bytes, dcb_buf** out_buf) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_buf != nullptr, "out_buf is null");
+    *out_buf = nullptr;
+    void* p = nullptr;
+    if (bytes > 0) {
+        CU(ctx, cudaMallocAsync(&p, bytes, ctx->stream));
+    }
+    dcb_buf* b = new dcb_buf();
+    b->ctx = ctx; b->ptr = p; b->bytes = bytes; b->owned = true;
+    {
+        std::lock_guard<std::mutex> g(ctx->mu);
+        ctx->bytes_in_use += (int64_t)bytes;
+        ctx->peak_bytes = std::max(ctx->peak_bytes, ctx->bytes_in_use);
+        ctx->n_allocs += 1;
+    }
+    *out_buf = b;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_free(dcb_ctx* ctx, dcb_buf* buf) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, buf != nullptr, "buf is null");
+    if (buf->ctx != ctx) return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "buffer belongs to another context");
+    if (buf->owned && buf->ptr) {
+        CU(ctx, cudaFreeAsync(buf->ptr, ctx->stream));
+        std::lock_guard<std::mutex> g(ctx->mu);
+        ctx->bytes_in_use -= (int64_t)buf->bytes;
+    }
+    delete buf;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_buf_wrap(dcb_ctx* ctx, void* device_ptr, size_t bytes, dcb_buf** out_buf) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_buf != nullptr, "out_buf is null");
+    NEED(ctx, device_ptr != nullptr || bytes == 0, "device_ptr is null");
+    dcb_buf* b = new dcb_buf();
+    b->ctx = ctx; b->ptr = device_ptr; b->bytes = bytes; b->owned = false;
+    *out_buf = b;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_buf_slice(dcb_ctx* ctx, dcb_buf* parent, size_t byte_offset, size_t bytes, dcb_buf** out_buf) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, parent != nullptr && out_buf != nullptr, "parent or out_buf is null");
+    if (byte_offset > parent->bytes || bytes > parent->bytes - byte_offset)
+        return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "slice [%zu, +%zu) outside a buffer of %zu bytes", byte_offset, bytes, parent->bytes);
+    dcb_buf* b = new dcb_buf();
+    b->ctx = ctx; b->ptr = (char*)parent->ptr + byte_offset; b->bytes = bytes; b->owned = false;
+    *out_buf = b;
+    return DCB_OK;
+}
+
+extern "C" void* dcb_devptr(const dcb_buf* buf) { return buf ? buf->ptr : nullptr; }
+extern "C" size_t dcb_buf_bytes(const dcb_buf* buf) { return buf ? buf->bytes : 0; }
+
+static dcb_status check_range(dcb_ctx* ctx, const dcb_buf* b, size_t off, size_t bytes, const char* what) {
+    if (!b) return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "%s buffer is null", what);
+    if (off > b->bytes || bytes > b->bytes - off)
+        return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "%s range [%zu, +%zu) outside a buffer of %zu bytes", what, off, bytes, b->bytes);
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_h2d_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const void* host, size_t bytes, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if ((st = check_range(ctx, dst, dst_off, bytes, "destination"))) return st;
+    NEED(ctx, host != nullptr || bytes == 0, "host pointer is null");
+    if (bytes) CU(ctx, cudaMemcpyAsync((char*)dst->ptr + dst_off, host, bytes, cudaMemcpyHostToDevice, pick(ctx, stream)));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_d2h_async(dcb_ctx* ctx, void* host, const dcb_buf* src, size_t src_off, size_t bytes, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if ((st = check_range(ctx, src, src_off, bytes, "source"))) return st;
+    NEED(ctx, host != nullptr || bytes == 0, "host pointer is null");
+    if (bytes) CU(ctx, cudaMemcpyAsync(host, (const char*)src->ptr + src_off, bytes, cudaMemcpyDeviceToHost, pick(ctx, stream)));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_d2d_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const dcb_buf* src, size_t src_off, size_t bytes, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if ((st = check_range(ctx, dst, dst_off, bytes, "destination"))) return st;
+    if ((st = check_range(ctx, src, src_off, bytes, "source"))) return st;
+    if (bytes) CU(ctx, cudaMemcpyAsync((char*)dst->ptr + dst_off, (const char*)src->ptr + src_off, bytes, cudaMemcpyDeviceToDevice, pick(ctx, stream)));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_fill_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const void* pattern, int32_t pattern_bytes, size_t count, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, pattern != nullptr, "pattern is null");
+    NEED(ctx, pattern_bytes == 1 || pattern_bytes == 2 || pattern_bytes == 4 || pattern_bytes == 8, "pattern must be 1, 2, 4 or 8 bytes");
+    if ((st = check_range(ctx, dst, dst_off, count * (size_t)pattern_bytes, "destination"))) return st;
+    NEED(ctx, dst_off % (size_t)pattern_bytes == 0, "offset must be a multiple of the pattern size");
+    if (count == 0) return DCB_OK;
+    unsigned long long pat = 0;
+    memcpy(&pat, pattern, (size_t)pattern_bytes);
+    const int grid = (int)std::min<size_t>((count + 255) / 256, (size_t)ctx->sm_count * 8);
+    fill_kernel<<<grid, 256, 0, pick(ctx, stream)>>>((unsigned char*)dst->ptr + dst_off, count, pat, pattern_bytes);
+    CU(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_host_alloc_pinned(dcb_ctx* ctx, size_t bytes, void** out_host) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_host != nullptr, "out_host is null");
+    *out_host = nullptr;
+    if (bytes == 0) return DCB_OK;
+    CU(ctx, cudaHostAlloc(out_host, bytes, cudaHostAllocPortable));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_host_free_pinned(dcb_ctx* ctx, void* host) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if (host) CU(ctx, cudaFreeHost(host));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pin_host(dcb_ctx* ctx, void* host, size_t bytes) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, host != nullptr && bytes > 0, "host range is empty");
+    CU(ctx, cudaHostRegister(host, bytes, cudaHostRegisterPortable));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_unpin_host(dcb_ctx* ctx, void* host) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, host != nullptr, "host pointer is null");
+    CU(ctx, cudaHostUnregister(host));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_memory_stats(dcb_ctx* ctx, int64_t* bytes_in_use, int64_t* peak_bytes, int64_t* n_allocs) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (bytes_in_use) *bytes_in_use = ctx->bytes_in_use;
+    if (peak_bytes) *peak_bytes = ctx->peak_bytes;
+    if (n_allocs) *n_allocs = ctx->n_allocs;
+    return DCB_OK;
+}
+
+// =========================================================================================== compile
+extern "C" dcb_status dcb_translate_lambda(const char* lambda, const int32_t* param_types, int32_t n_params, char* out_code,
+                                           size_t out_cap, int32_t* result_type, char* err, size_t err_cap) {
+    if (err && err_cap) err[0] = '\0';
+    if (!lambda || !param_types || n_params < 1 || n_params > 2 || !out_code || out_cap == 0)
+        return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "bad argument to dcb_translate_lambda");
+    std::vector<std::string> args;
+    std::vector<int> types;
+    for (int i = 0; i < n_params; ++i) { args.push_back("p" + std::to_string(i)); types.push_back(param_types[i]); }
+    std::string code, e;
+    int rt = 0;
+    if (!dcbt::translate_lambda(lambda, args, types, &code, &rt, &e)) {
+        if (err && err_cap) snprintf(err, err_cap, "%s", e.c_str());
+        return set_err(nullptr, DCB_ERR_NOT_SUPPORTED, "%s", e.c_str());
+    }
+    if (code.size() + 1 > out_cap) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "output buffer too small (%zu needed)", code.size() + 1);
+    memcpy(out_code, code.c_str(), code.size() + 1);
+    if (result_type) *result_type = rt;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pipeline_generate_source(const dcb_pipeline_desc* desc, char* buf, size_t cap, size_t* needed,
+                                                   char* err, size_t err_cap) {
+    char e[512] = "";
+    std::vector<dcbt::OpSpec> ops;
+    dcb_status st = desc_to_ops(desc, &ops, e, sizeof e);
+    dcbt::ChainInfo info;
+    std::string es;
+    if (st == DCB_OK) {
+        int s2 = 0;
+        if (!dcbt::build_chain(desc->elem_type0, desc->elem_type1, ops, &info, &es, &s2)) { st = s2; snprintf(e, sizeof e, "%s", es.c_str()); }
+    }
+    if (st != DCB_OK) {
+        if (err && err_cap) snprintf(err, err_cap, "%s", e);
+        return set_err(nullptr, st, "%s", e);
+    }
+    std::string src = dcbt::build_program(info, "", "", kBlock, 4, true);
+    if (needed) *needed = src.size() + 1;
+    if (buf && cap) { snprintf(buf, cap, "%s", src.c_str()); }
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc* desc, dcb_pipeline** out_pipeline) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_pipeline != nullptr, "out_pipeline is null");
+    *out_pipeline = nullptr;
+    const auto t0 = std::chrono::steady_clock::now();
+    char e[512] = "";
+    std::vector<dcbt::OpSpec> ops;
+    if ((st = desc_to_ops(desc, &ops, e, sizeof e))) return set_err(ctx, st, "%s", e);
+    dcbt::ChainInfo info;
+    std::string es;
+    int s2 = 0;
+    if (!dcbt::build_chain(desc->elem_type0, desc->elem_type1, ops, &info, &es, &s2)) return set_err(ctx, s2, "%s", es.c_str());
+    const bool force_jit = (desc->flags & DCB_PIPE_FORCE_JIT) != 0 || env_int("DCB200_FORCE_JIT", 0) != 0;
+    const std::string cache_key = info.key + (force_jit ? "#jit" : "");
+
+    std::lock_guard<std::mutex> g(ctx->mu);
+    auto it = ctx->cache.find(cache_key);
+    if (it != ctx->cache.end()) {
+        it->second->refs += 1;
+        *out_pipeline = it->second;
+        return DCB_OK;
+    }
+    dcb_pipeline* p = new dcb_pipeline();
+    p->ctx = ctx;
+    p->info = info;
+    const dcb_builtin_entry* b = force_jit ? nullptr : dcb_builtin_find(info.key.c_str());
+    if (b) {
+        p->precompiled = true;
+        p->k_vec = b->k_vec;
+        p->k_scalar = b->k_scalar;
+        p->unroll = b->unroll;
+        p->source = dcbt::build_program(info, "", "", kBlock, b->unroll, true);
+    } else if ((st = load_jit(ctx, p)) != DCB_OK) {
+        free_pipeline(p);
+        return st;
+    }
+    if ((st = finish_pipeline(ctx, p)) != DCB_OK) { free_pipeline(p); return st; }
+    p->compile_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    ctx->cache[cache_key] = p;
+    *out_pipeline = p;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pipeline_destroy(dcb_pipeline* p) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    // Pipelines live in their context's cache until dcb_shutdown; destroy only drops the caller's reference.
+    std::lock_guard<std::mutex> g(p->ctx->mu);
+    if (p->refs > 0) p->refs -= 1;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pipeline_info_get(const dcb_pipeline* p, dcb_pipeline_info* out) {
+    if (!p || !out) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "null argument");
+    out->terminal = p->info.terminal;
+    out->out_type = p->info.out_type;
+    out->result_type = p->info.result_type;
+    out->has_filter = p->info.has_filter ? 1 : 0;
+    out->n_inputs = p->info.n_in;
+    out->precompiled = p->precompiled ? 1 : 0;
+    out->tile_elems = (p->info.terminal == DCB_OP_TOARRAY && p->info.has_filter)
+                          ? (int64_t)(kBlock / 32) * p->rows_vec * 32 * (16 / dcbt::type_size(p->info.in0)) : 0;
+    out->compile_ms = p->compile_ms;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_pipeline_source(const dcb_pipeline* p, char* buf, size_t cap, size_t* needed) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    // Only the generated part is returned (chain + kernel entry points), not the template header in front of it.
+    const std::string src = dcbt::build_program(p->info, "", "", kBlock, p->unroll, true);
+    if (needed) *needed = src.size() + 1;
+    if (buf && cap) snprintf(buf, cap, "%s", src.c_str());
+    return DCB_OK;
+}
+
+// =============================================================================================== run
+namespace {
+
+bool aligned_to(const void* p, size_t a) { return a <= 1 || ((uintptr_t)p % a) == 0; }
+
+dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cudaStream_t s) {
+    CU(ctx, cudaLaunchKernel(fn, dim3(grid), dim3(kBlock), args, 0, s));
+    ctx->launches += 1;
+    return DCB_OK;
+}
+
+dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
+                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches) {
+    dcb_ctx* ctx = p->ctx;
+    const dcbt::ChainInfo& I = p->info;
+    NEED(ctx, n >= 0, "element count is negative");
+    NEED(ctx, n == 0 || in0 != nullptr, "in0 is null");
+    NEED(ctx, I.n_in == 1 || n == 0 || in1 != nullptr, "in1 is null for a Zip pipeline");
+    const bool to_array = I.terminal == DCB_OP_TOARRAY;
+    if (to_array) {
+        NEED(ctx, out_cap >= 0, "output capacity is negative");
+        NEED(ctx, out != nullptr || out_cap == 0 || n == 0, "out is null");
+    }
+    dcb::DeviceResult* res = d_result ? (dcb::DeviceResult*)d_result : p->d_result;
+    const int e_vec = 16 / dcbt::type_size(I.in0);
+    bool vec = aligned_to(in0, 16);
+    if (I.n_in == 2) vec = vec && aligned_to(in1, pack_align(e_vec, I.in1));
+    if (to_array) vec = vec && aligned_to(out, pack_align(e_vec, I.out_type)) ;
+    if (env_int("DCB200_FORCE_SCALAR", 0)) vec = false;
+    const void* fn = vec ? p->k_vec : p->k_scalar;
+    const int E = vec ? e_vec : 1;
+    long long nn = n;
+
+    if (to_array && !I.has_filter) {
+        NEED(ctx, out_cap >= n, "output capacity below the element count");
+        if (n == 0) return DCB_OK;
+        const int unroll = vec ? p->unroll : p->unroll * 2;
+        const int64_t tiles = (n / E + (int64_t)kBlock * unroll - 1) / ((int64_t)kBlock * unroll);
+        const int64_t max_grid = (int64_t)ctx->sm_count * (vec ? p->occ_vec : p->occ_scalar);
+        const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out};
+        if (launches) *launches += 1;
+        return launch(ctx, fn, grid, args, s);
+    }
+    if (to_array) {
+        const int rows = vec ? p->rows_vec : p->rows_scalar;
+        const int64_t tile = (int64_t)(kBlock / 32) * rows * 32 * E;
+        long long num_tiles = (n + tile - 1) / tile;
+        if (num_tiles == 0) {
+            // Nothing to scan: the record is the previous one (or zero).
+            if (d_prev) CU(ctx, cudaMemcpyAsync(res, d_prev, DCB_DEVICE_RESULT_BYTES, cudaMemcpyDeviceToDevice, s));
+            else CU(ctx, cudaMemsetAsync(res, 0, DCB_DEVICE_RESULT_BYTES, s));
+            return DCB_OK;
+        }
+        NEED(ctx, num_tiles < (1ll << 31), "too many tiles for one launch");
+        dcb_status st = ensure_scratch(p, num_tiles, s);
+        if (st) return st;
+        Scratch& sc = p->sc;
+        sc.epoch += 1;
+        if (sc.epoch >= 0x3fffu) {   // epoch field is 14 bits: wipe the descriptors before reusing a value
+            CU(ctx, cudaMemsetAsync(sc.desc, 0, sc.desc_cap * sizeof(unsigned long long), s));
+            CU(ctx, cudaMemsetAsync(sc.words, 0, 64, s));
+            sc.epoch = 1;
+        }
+        unsigned int epoch = sc.epoch, spin = ctx->spin_limit;
+        unsigned int* counter = sc.words + 1;
+        unsigned int* abort_flag = sc.words + 2;
+        long long cap = out_cap;
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&counter,
+                        (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag};
+        if (launches) *launches += 1;
+        return launch(ctx, fn, (unsigned)num_tiles, args, s);
+    }
+    // reductions
+    {
+        dcb_status st = ensure_scratch(p, 0, s);
+        if (st) return st;
+        const int unroll = vec ? p->unroll : p->unroll * 2;
+        const int64_t tiles = (n / E + (int64_t)kBlock * unroll - 1) / ((int64_t)kBlock * unroll);
+        int64_t max_grid = (int64_t)ctx->sm_count * (vec ? p->occ_vec : p->occ_scalar);
+        max_grid = std::min<int64_t>(max_grid, kMaxPartials);
+        const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
+        unsigned int* ticket = p->sc.words;
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res};
+        if (launches) *launches += 1;
+        return launch(ctx, fn, grid, args, s);
+    }
+}
+
+float round_f32(double v) { return (float)v; }
+
+}  // namespace
+
+extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* host_record, dcb_result* r) {
+    if (!p || !host_record || !r) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "null argument");
+    dcb_ctx* ctx = p->ctx;
+    const dcb::DeviceResult* d = (const dcb::DeviceResult*)host_record;
+    const dcbt::ChainInfo& I = p->info;
+    const uint32_t keep_launches = r->launches;
+    const float km = r->kernel_ms, tm = r->total_ms;
+    memset(r, 0, sizeof *r);
+    r->launches = keep_launches; r->kernel_ms = km; r->total_ms = tm;
+    r->count = d->count;
+    const uint64_t fl = d->flags;
+    if (fl & dcb::FLAG_SAW_NAN) r->flags |= DCB_RES_SAW_NAN;
+    const int rt = I.result_type;
+    switch (I.terminal) {
+        case DCB_OP_TOARRAY:
+            if (fl & dcb::FLAG_TIMEOUT) { r->flags |= DCB_RES_TIMEOUT; return set_err(ctx, DCB_ERR_TIMEOUT, "a look-back wait in the compaction kernel ran out"); }
+            if (fl & dcb::FLAG_TRUNCATED) { r->flags |= DCB_RES_TRUNCATED; return set_err(ctx, DCB_ERR_OUTPUT_TOO_SMALL, "%lld elements survive, the output holds fewer", (long long)d->count); }
+            return DCB_OK;
+        case DCB_OP_COUNT:
+            r->i64 = d->count; r->u64 = (uint64_t)d->count;
+            return DCB_OK;
+        case DCB_OP_SUM:
+        case DCB_OP_AVERAGE: {
+            const bool avg = I.terminal == DCB_OP_AVERAGE;
+            if (avg && d->count == 0) return set_err(ctx, DCB_ERR_EMPTY_SEQUENCE, "Average of an empty sequence");
+            if (I.out_type == DCB_T_F32 || I.out_type == DCB_T_F64) {
+                double v = avg ? d->fsum / (double)d->count : d->fsum;
+                r->f64 = (rt == DCB_T_F32) ? (double)round_f32(v) : v;
+                return DCB_OK;
+            }
+            // integer Sum is checked in System.Linq: leaving the element type's range is an error
+            const bool hi_ok = d->isum_hi == ((d->isum_lo < 0) ? -1 : 0);
+            bool overflow = !hi_ok;
+            if (I.out_type == DCB_T_I32 && !avg) overflow = overflow || d->isum_lo > 2147483647LL || d->isum_lo < -2147483648LL;
+            if (overflow) { r->flags |= DCB_RES_OVERFLOW; return set_err(ctx, DCB_ERR_OVERFLOW, "integer Sum overflowed %s", dcbt::csharp_name(I.out_type)); }
+            if (avg) r->f64 = (double)d->isum_lo / (double)d->count;
+            else { r->i64 = d->isum_lo; r->u64 = (uint64_t)d->isum_lo; }
+            return DCB_OK;
+        }
+        case DCB_OP_MIN:
+        case DCB_OP_MAX: {
+            if (d->count == 0) return set_err(ctx, DCB_ERR_EMPTY_SEQUENCE, "%s of an empty sequence", I.terminal == DCB_OP_MIN ? "Min" : "Max");
+            const bool mn = I.terminal == DCB_OP_MIN;
+            if (rt == DCB_T_F32 || rt == DCB_T_F64) {
+                // Enumerable.Min returns NaN if any element is NaN; Enumerable.Max only if all are.
+                const double nan = std::numeric_limits<double>::quiet_NaN();
+                if (mn) r->f64 = (fl & dcb::FLAG_SAW_NAN) ? nan : d->fmin;
+                else r->f64 = (fl & dcb::FLAG_SAW_NUMBER) ? d->fmax : nan;
+            } else {
+                r->i64 = mn ? d->imin : d->imax;
+                r->u64 = (uint64_t)r->i64;
+            }
+            return DCB_OK;
+        }
+        default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "pipeline has no terminal");
+    }
+}
+
+extern "C" dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,
+                                             int64_t out_cap, void* d_result, const void* d_prev, void* stream) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    dcb_status st = use(p->ctx);
+    if (st) return st;
+    return run_async_impl(p, in0, in1, n, out, out_cap, d_result, d_prev, pick(p->ctx, stream), nullptr);
+}
+
+extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,
+                                       int64_t out_cap, dcb_result* result, void* stream) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    dcb_ctx* ctx = p->ctx;
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, result != nullptr, "result is null");
+    memset(result, 0, sizeof *result);
+    cudaStream_t s = pick(ctx, stream);
+    const bool plain_map = p->info.terminal == DCB_OP_TOARRAY && !p->info.has_filter;
+    CU(ctx, cudaEventRecord(p->ev0, s));
+    uint32_t launches = 0;
+    if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches))) return st;
+    CU(ctx, cudaEventRecord(p->ev1, s));
+    if (!plain_map) CU(ctx, cudaMemcpyAsync(p->h_record, p->d_result, DCB_DEVICE_RESULT_BYTES, cudaMemcpyDeviceToHost, s));
+    CU(ctx, cudaStreamSynchronize(s));
+    float ms = 0;
+    CU(ctx, cudaEventElapsedTime(&ms, p->ev0, p->ev1));
+    result->launches = launches; result->kernel_ms = ms; result->total_ms = ms;
+    if (plain_map) { result->count = n; return DCB_OK; }
+    return dcb_result_finalize(p, p->h_record, result);
+}
+
+namespace {
+
+dcb_status grow(dcb_ctx* ctx, void** buf, size_t* cap, size_t need) {
+    if (need <= *cap) return DCB_OK;
+    if (*buf) { CU(ctx, cudaDeviceSynchronize()); CU(ctx, cudaFree(*buf)); *buf = nullptr; *cap = 0; }
+    CU(ctx, cudaMalloc(buf, need));
+    *cap = need;
+    return DCB_OK;
+}
+
+// Fold the per-chunk records of a chunked reduction in chunk order (deterministic).
+void fold_records(const dcbt::ChainInfo& I, const dcb::DeviceResult* recs, int n, dcb::DeviceResult* out) {
+    *out = recs[0];
+    for (int i = 1; i < n; ++i) {
+        const dcb::DeviceResult& r = recs[i];
+        out->fsum += r.fsum;
+        const unsigned long long lo = (unsigned long long)out->isum_lo + (unsigned long long)r.isum_lo;
+        out->isum_hi += r.isum_hi + (lo < (unsigned long long)r.isum_lo ? 1 : 0);
+        out->isum_lo = (long long)lo;
+        out->count += r.count;
+        if (r.fmin < out->fmin) out->fmin = r.fmin;
+        if (r.fmax > out->fmax) out->fmax = r.fmax;
+        if (I.out_type == DCB_T_U64) {
+            if ((unsigned long long)r.imin < (unsigned long long)out->imin) out->imin = r.imin;
+            if ((unsigned long long)r.imax > (unsigned long long)out->imax) out->imax = r.imax;
+        } else {
+            if (r.imin < out->imin) out->imin = r.imin;
+            if (r.imax > out->imax) out->imax = r.imax;
+        }
+        out->flags |= r.flags;
+    }
+    out->count_f = (double)out->count;
+}
+
+}  // namespace
+
+extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
+                                            void* host_out, int64_t host_out_cap, dcb_result* result) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    dcb_ctx* ctx = p->ctx;
+    dcb_status st = use(ctx);
+    if (st) return st;
+    const dcbt::ChainInfo& I = p->info;
+    NEED(ctx, result != nullptr, "result is null");
+    NEED(ctx, n >= 0, "element count is negative");
+    NEED(ctx, n == 0 || host_in0 != nullptr, "host_in0 is null");
+    NEED(ctx, I.n_in == 1 || n == 0 || host_in1 != nullptr, "host_in1 is null for a Zip pipeline");
+    memset(result, 0, sizeof *result);
+    const bool to_array = I.terminal == DCB_OP_TOARRAY;
+    const bool compaction = to_array && I.has_filter;
+    const size_t sz0 = (size_t)dcbt::type_size(I.in0), sz1 = I.n_in == 2 ? (size_t)dcbt::type_size(I.in1) : 0;
+    const size_t szo = (size_t)dcbt::type_size(I.out_type);
+    if (to_array) {
+        NEED(ctx, host_out_cap >= 0 && (host_out != nullptr || host_out_cap == 0), "host_out is null");
+        if (!I.has_filter) NEED(ctx, host_out_cap >= n, "output capacity below the element count");
+    }
+    // Chunks are whole tiles of the widest kernel shape so that every chunk but the last starts 16-byte aligned.
+    int64_t chunk = (int64_t)(kHostChunkBytes / std::max(sz0, sz1));
+    chunk = std::max<int64_t>(chunk - chunk % 16384, 16384);
+    const int n_chunks = (int)std::max<int64_t>(1, (n + chunk - 1) / chunk);
+    if ((st = grow(ctx, &ctx->stage_in[0], &ctx->stage_in_cap[0], std::max<size_t>((size_t)n * sz0, 256)))) return st;
+    if (I.n_in == 2 && (st = grow(ctx, &ctx->stage_in[1], &ctx->stage_in_cap[1], std::max<size_t>((size_t)n * sz1, 256)))) return st;
+    if (to_array && (st = grow(ctx, &ctx->stage_out, &ctx->stage_out_cap, std::max<size_t>((size_t)n * szo, 256)))) return st;
+    // Per-chunk records live at the tail of a scratch allocation.
+    dcb::DeviceResult* d_recs = nullptr;
+    CU(ctx, cudaMallocAsync((void**)&d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, ctx->stream));
+    dcb::DeviceResult* h_recs = nullptr;
+    CU(ctx, cudaHostAlloc((void**)&h_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaHostAllocDefault));
+
+    cudaStream_t cs = ctx->copy_stream, ks = ctx->stream, os = ctx->out_stream;
+    std::vector<cudaEvent_t> copied((size_t)n_chunks), computed((size_t)n_chunks);
+    for (int c = 0; c < n_chunks; ++c) {
+        cudaEventCreateWithFlags(&copied[c], cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&computed[c], cudaEventDisableTiming);
+    }
+    auto cleanup = [&]() {
+        for (int c = 0; c < n_chunks; ++c) { cudaEventDestroy(copied[c]); cudaEventDestroy(computed[c]); }
+        cudaFreeAsync(d_recs, ctx->stream);
+        cudaFreeHost(h_recs);
+    };
+    cudaEvent_t t0 = p->ev0, t1 = p->ev1;
+    uint32_t launches = 0;
+    st = DCB_OK;
+    cudaError_t ce = cudaEventRecord(t0, ks);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(cs, t0, 0);   // copies start after earlier work on the compute stream
+    for (int c = 0; c < n_chunks && ce == cudaSuccess && st == DCB_OK; ++c) {
+        const int64_t off = (int64_t)c * chunk, len = std::min<int64_t>(chunk, n - off);
+        if (len > 0) {
+            ce = cudaMemcpyAsync((char*)ctx->stage_in[0] + off * sz0, (const char*)host_in0 + off * sz0, (size_t)len * sz0, cudaMemcpyHostToDevice, cs);
+            if (ce == cudaSuccess && I.n_in == 2)
+                ce = cudaMemcpyAsync((char*)ctx->stage_in[1] + off * sz1, (const char*)host_in1 + off * sz1, (size_t)len * sz1, cudaMemcpyHostToDevice, cs);
+        }
+        if (ce == cudaSuccess) ce = cudaEventRecord(copied[c], cs);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(ks, copied[c], 0);
+        if (ce != cudaSuccess) break;
+        const void* a = (const char*)ctx->stage_in[0] + off * sz0;
+        const void* b = I.n_in == 2 ? (const char*)ctx->stage_in[1] + off * sz1 : nullptr;
+        if (compaction) {
+            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), ctx->stage_out, n, d_recs + c, c ? d_recs + c - 1 : nullptr, ks, &launches);
+        } else if (to_array) {
+            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), (char*)ctx->stage_out + off * szo, len, nullptr, nullptr, ks, &launches);
+            if (st == DCB_OK && len > 0) {
+                // results of a plain map leave chunk by chunk on a third stream, overlapping the uploads
+                ce = cudaEventRecord(computed[c], ks);
+                if (ce == cudaSuccess) ce = cudaStreamWaitEvent(os, computed[c], 0);
+                if (ce == cudaSuccess)
+                    ce = cudaMemcpyAsync((char*)host_out + off * szo, (const char*)ctx->stage_out + off * szo, (size_t)len * szo, cudaMemcpyDeviceToHost, os);
+            }
+        } else {
+            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches);
+        }
+    }
+    if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
+    if (st != DCB_OK) { cudaDeviceSynchronize(); cleanup(); return st; }
+    const bool plain_map = to_array && !compaction;
+    if (!plain_map) {
+        ce = cudaMemcpyAsync(h_recs, d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaMemcpyDeviceToHost, ks);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(ks);
+        if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "reading the records back"); }
+    }
+    dcb::DeviceResult total;
+    memset(&total, 0, sizeof total);
+    if (compaction) {
+        total = h_recs[n_chunks - 1];
+        for (int c = 0; c < n_chunks; ++c) total.flags |= h_recs[c].flags;
+        const int64_t cnt = total.count;
+        if (!(total.flags & dcb::FLAG_TIMEOUT)) {
+            if (cnt > host_out_cap) total.flags |= dcb::FLAG_TRUNCATED;
+            const int64_t ncopy = std::min<int64_t>(cnt, host_out_cap);
+            if (ncopy > 0) ce = cudaMemcpyAsync(host_out, ctx->stage_out, (size_t)ncopy * szo, cudaMemcpyDeviceToHost, ks);
+        }
+    } else if (!plain_map) {
+        fold_records(I, h_recs, n_chunks, &total);
+    }
+    if (ce == cudaSuccess) ce = cudaEventRecord(t1, ks);
+    if (ce == cudaSuccess && plain_map) ce = cudaStreamSynchronize(os);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(ks);
+    if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    cleanup();
+    result->launches = launches; result->total_ms = ms; result->kernel_ms = 0;
+    if (plain_map) { result->count = n; return DCB_OK; }
+    return dcb_result_finalize(p, &total, result);
+}
+
+// ============================================================================== [Kernel] source kernels
+extern "C" dcb_status dcb_kernel_compile(dcb_ctx* ctx, const char* cuda_source, const char* entry_point, dcb_kernel** out_kernel) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, cuda_source != nullptr && entry_point != nullptr && out_kernel != nullptr, "null argument");
+    *out_kernel = nullptr;
+    nvrtcProgram prog = nullptr;
+    if (nvrtcCreateProgram(&prog, cuda_source, "kernel.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        return set_err(ctx, DCB_ERR_COMPILE, "nvrtcCreateProgram failed");
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-fmad=false", "-lineinfo"};
+    nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+    if (r != NVRTC_SUCCESS) {
+        size_t n = 0;
+        nvrtcGetProgramLogSize(prog, &n);
+        std::string log(n + 1, '\0');
+        nvrtcGetProgramLog(prog, &log[0]);
+        nvrtcDestroyProgram(&prog);
+        return set_err(ctx, DCB_ERR_COMPILE, "NVRTC: %s: %.800s", nvrtcGetErrorString(r), log.c_str());
+    }
+    size_t sz = 0;
+    nvrtcGetCUBINSize(prog, &sz);
+    std::vector<char> cubin(sz);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    dcb_kernel* k = new dcb_kernel();
+    k->ctx = ctx;
+    cudaError_t e = cudaLibraryLoadData(&k->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    cudaKernel_t fn = nullptr;
+    if (e == cudaSuccess) e = cudaLibraryGetKernel(&fn, k->lib, entry_point);
+    if (e != cudaSuccess) {
+        if (k->lib) cudaLibraryUnload(k->lib);
+        delete k;
+        if (e == cudaErrorSymbolNotFound) { (void)cudaGetLastError(); return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "entry point '%s' not found (it must be extern \"C\")", entry_point); }
+        return cuda_fail(ctx, e, "loading the compiled kernel");
+    }
+    k->fn = (const void*)fn;
+    *out_kernel = k;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_kernel_launch(dcb_kernel* k, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_bytes,
+                                        void** args, void* stream) {
+    if (!k) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "kernel is null");
+    dcb_ctx* ctx = k->ctx;
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, grid != nullptr && block != nullptr, "grid or block is null");
+    NEED(ctx, grid[0] && grid[1] && grid[2] && block[0] && block[1] && block[2], "grid and block dimensions must be positive");
+    NEED(ctx, (uint64_t)block[0] * block[1] * block[2] <= 1024, "a block holds at most 1024 threads");
+    CU(ctx, cudaLaunchKernel(k->fn, dim3(grid[0], grid[1], grid[2]), dim3(block[0], block[1], block[2]), args, shared_bytes, pick(ctx, stream)));
+    ctx->launches += 1;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_kernel_destroy(dcb_kernel* k) {
+    if (!k) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "kernel is null");
+    cudaSetDevice(k->ctx->device);
+    if (k->lib) cudaLibraryUnload(k->lib);
+    delete k;
+    return DCB_OK;
+}
+
+// ============================================================================================ timing
+extern "C" dcb_status dcb_event_create(dcb_ctx* ctx, void** out_event) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_event != nullptr, "out_event is null");
+    cudaEvent_t e;
+    CU(ctx, cudaEventCreate(&e));
+    *out_event = (void*)e;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_event_record(dcb_ctx* ctx, void* event, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, event != nullptr, "event is null");
+    CU(ctx, cudaEventRecord((cudaEvent_t)event, pick(ctx, stream)));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_event_elapsed_ms(dcb_ctx* ctx, void* start, void* stop, float* out_ms) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, start && stop && out_ms, "null argument");
+    CU(ctx, cudaEventSynchronize((cudaEvent_t)stop));
+    CU(ctx, cudaEventElapsedTime(out_ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_event_destroy(dcb_ctx* ctx, void* event) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if (event) CU(ctx, cudaEventDestroy((cudaEvent_t)event));
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_launch_count(dcb_ctx* ctx, int64_t* out_launches) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_launches != nullptr, "out_launches is null");
+    *out_launches = ctx->launches;
+    return DCB_OK;
+}

@@ -1,0 +1,747 @@
+// dcb_translate.cpp — see dcb_translate.h.
+#include "dcb_translate.h"
+
+#include <algorithm>
+#include <cctype>
+#include <cerrno>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+
+namespace dcbt {
+
+// Operator and status codes shared with dcb200.h (kept numeric here so this file has no CUDA dependency).
+enum { OP_SELECT = 1, OP_WHERE = 2, OP_ZIP = 3, OP_TOARRAY = 16, OP_SUM = 17, OP_MIN = 18, OP_MAX = 19, OP_AVERAGE = 20, OP_COUNT = 21 };
+enum { ST_INVALID_ARGUMENT = 301, ST_NOT_SUPPORTED = 302 };
+enum { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8 };
+
+static const char* kCuda[] = {"void", "signed char", "unsigned char", "short", "unsigned short", "int", "unsigned int",
+                              "long long", "unsigned long long", "float", "double", "bool"};
+static const char* kCs[] = {"void", "sbyte", "byte", "short", "ushort", "int", "uint", "long", "ulong", "float", "double", "bool"};
+static const int kSize[] = {0, 1, 1, 2, 2, 4, 4, 8, 8, 4, 8, 1};
+
+const char* cuda_name(int t) { return (t >= 0 && t <= T_BOOL) ? kCuda[t] : "void"; }
+const char* csharp_name(int t) { return (t >= 0 && t <= T_BOOL) ? kCs[t] : "void"; }
+int type_size(int t) { return (t >= 0 && t <= T_BOOL) ? kSize[t] : 0; }
+bool is_numeric(int t) { return t >= T_I8 && t <= T_F64; }
+static bool is_integral(int t) { return t >= T_I8 && t <= T_U64; }
+static bool is_signed_int(int t) { return t == T_I8 || t == T_I16 || t == T_I32 || t == T_I64; }
+static bool is_float(int t) { return t == T_F32 || t == T_F64; }
+static int unsigned_of(int t) { return t == T_I32 ? T_U32 : t == T_I64 ? T_U64 : t; }
+
+unsigned long long fnv1a(const std::string& s) {
+    unsigned long long h = 1469598103934665603ull;
+    for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
+// ---------------------------------------------------------------------------------------------- tokens
+struct Tok {
+    enum Kind { END, NUM, IDENT, PUNCT } kind = END;
+    std::string text;
+};
+
+static bool lex(const std::string& s, std::vector<Tok>* out, std::string* err) {
+    size_t i = 0, n = s.size();
+    while (i < n) {
+        char c = s[i];
+        if (isspace((unsigned char)c)) { ++i; continue; }
+        Tok t;
+        if (isdigit((unsigned char)c) || (c == '.' && i + 1 < n && isdigit((unsigned char)s[i + 1]))) {
+            size_t j = i;
+            bool hex = (c == '0' && j + 1 < n && (s[j + 1] == 'x' || s[j + 1] == 'X'));
+            bool bin = (c == '0' && j + 1 < n && (s[j + 1] == 'b' || s[j + 1] == 'B'));
+            if (hex || bin) {
+                j += 2;
+                while (j < n && (isxdigit((unsigned char)s[j]) || s[j] == '_')) ++j;
+            } else {
+                while (j < n && (isdigit((unsigned char)s[j]) || s[j] == '_')) ++j;
+                if (j < n && s[j] == '.' && j + 1 < n && isdigit((unsigned char)s[j + 1])) {
+                    ++j;
+                    while (j < n && (isdigit((unsigned char)s[j]) || s[j] == '_')) ++j;
+                }
+                if (j < n && (s[j] == 'e' || s[j] == 'E')) {
+                    size_t k = j + 1;
+                    if (k < n && (s[k] == '+' || s[k] == '-')) ++k;
+                    if (k < n && isdigit((unsigned char)s[k])) {
+                        j = k;
+                        while (j < n && isdigit((unsigned char)s[j])) ++j;
+                    }
+                }
+            }
+            while (j < n && isalpha((unsigned char)s[j])) ++j;   // suffix
+            t.kind = Tok::NUM; t.text = s.substr(i, j - i); i = j;
+        } else if (isalpha((unsigned char)c) || c == '_' || c == '@') {
+            size_t j = i + 1;
+            while (j < n && (isalnum((unsigned char)s[j]) || s[j] == '_')) ++j;
+            t.kind = Tok::IDENT; t.text = s.substr(i, j - i); i = j;
+        } else {
+            static const char* three[] = {">>>", nullptr};
+            static const char* two[] = {"=>", "==", "!=", "<=", ">=", "&&", "||", "<<", ">>", nullptr};
+            t.kind = Tok::PUNCT;
+            bool done = false;
+            for (int k = 0; three[k] && !done; ++k)
+                if (s.compare(i, 3, three[k]) == 0) { t.text = three[k]; i += 3; done = true; }
+            for (int k = 0; two[k] && !done; ++k)
+                if (s.compare(i, 2, two[k]) == 0) { t.text = two[k]; i += 2; done = true; }
+            if (!done) {
+                if (strchr("+-*/%&|^~!<>?:(),.", c) == nullptr) { *err = std::string("unexpected character '") + c + "'"; return false; }
+                t.text = std::string(1, c); ++i;
+            }
+        }
+        out->push_back(t);
+    }
+    out->push_back(Tok());
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------- typed nodes
+struct Node {
+    std::string code;
+    int type = T_NONE;
+    bool const_int = false;       // an int-typed constant expression (C# lets it narrow implicitly when it fits)
+    long long cval = 0;
+};
+
+static std::string conv(const Node& n, int to) {
+    if (n.type == to) return n.code;
+    return std::string("((") + cuda_name(to) + ")(" + n.code + "))";
+}
+
+// C# implicit numeric conversions (from -> to).
+static bool implicit_ok(int from, int to) {
+    if (from == to) return true;
+    switch (from) {
+        case T_I8: return to == T_I16 || to == T_I32 || to == T_I64 || to == T_F32 || to == T_F64;
+        case T_U8: return to == T_I16 || to == T_U16 || to == T_I32 || to == T_U32 || to == T_I64 || to == T_U64 || to == T_F32 || to == T_F64;
+        case T_I16: return to == T_I32 || to == T_I64 || to == T_F32 || to == T_F64;
+        case T_U16: return to == T_I32 || to == T_U32 || to == T_I64 || to == T_U64 || to == T_F32 || to == T_F64;
+        case T_I32: return to == T_I64 || to == T_F32 || to == T_F64;
+        case T_U32: return to == T_I64 || to == T_U64 || to == T_F32 || to == T_F64;
+        case T_I64: case T_U64: return to == T_F32 || to == T_F64;
+        case T_F32: return to == T_F64;
+        default: return false;
+    }
+}
+
+static bool const_fits(long long v, int t) {
+    switch (t) {
+        case T_I8: return v >= -128 && v <= 127;
+        case T_U8: return v >= 0 && v <= 255;
+        case T_I16: return v >= -32768 && v <= 32767;
+        case T_U16: return v >= 0 && v <= 65535;
+        case T_U32: return v >= 0 && v <= 4294967295LL;
+        case T_U64: return v >= 0;
+        default: return false;
+    }
+}
+
+// Binary numeric promotion (ECMA-334 12.4.7.3). Returns T_NONE when C# would reject the pair.
+static int promote_binary(const Node& a, const Node& b) {
+    int x = a.type, y = b.type;
+    if (!is_numeric(x) || !is_numeric(y)) return T_NONE;
+    if (x == T_F64 || y == T_F64) return T_F64;
+    if (x == T_F32 || y == T_F32) return T_F32;
+    if (x == T_U64 || y == T_U64) {
+        int o = (x == T_U64) ? y : x;
+        const Node& on = (x == T_U64) ? b : a;
+        if (is_signed_int(o) && !(on.const_int && on.cval >= 0)) return T_NONE;
+        return T_U64;
+    }
+    if (x == T_I64 || y == T_I64) return T_I64;
+    if (x == T_U32 || y == T_U32) {
+        int o = (x == T_U32) ? y : x;
+        const Node& on = (x == T_U32) ? b : a;
+        if (is_signed_int(o)) return (on.const_int && on.cval >= 0) ? T_U32 : T_I64;
+        return T_U32;
+    }
+    return T_I32;
+}
+static int promote_unary(int t) { return (t == T_I8 || t == T_U8 || t == T_I16 || t == T_U16) ? T_I32 : t; }
+
+// Best common type of two operands of ?: / Math.Min / Math.Max / Math.Clamp.
+static int common_type(const Node& a, const Node& b) {
+    if (a.type == b.type) return a.type;
+    if (a.const_int && const_fits(a.cval, b.type)) return b.type;
+    if (b.const_int && const_fits(b.cval, a.type)) return a.type;
+    if (implicit_ok(a.type, b.type)) return b.type;
+    if (implicit_ok(b.type, a.type)) return a.type;
+    return T_NONE;
+}
+
+static std::string fmt_f32(float v) {
+    char buf[64];
+    if (std::isnan(v)) return "__int_as_float(0x7fc00000)";
+    if (std::isinf(v)) return v > 0 ? "__int_as_float(0x7f800000)" : "__int_as_float(0xff800000)";
+    snprintf(buf, sizeof buf, "%.9g", (double)v);
+    std::string s = buf;
+    if (s.find_first_of(".en") == std::string::npos) s += ".0";
+    return s + "f";
+}
+static std::string fmt_f64(double v) {
+    char buf[64];
+    if (std::isnan(v)) return "__longlong_as_double(0x7ff8000000000000LL)";
+    if (std::isinf(v)) return v > 0 ? "__longlong_as_double(0x7ff0000000000000LL)" : "__longlong_as_double(0xfff0000000000000LL)";
+    snprintf(buf, sizeof buf, "%.17g", v);
+    std::string s = buf;
+    if (s.find_first_of(".en") == std::string::npos) s += ".0";
+    return s;
+}
+
+// ---------------------------------------------------------------------------------------------- parser
+class Parser {
+  public:
+    Parser(const std::vector<Tok>& toks, const std::map<std::string, Node>& params) : t_(toks), params_(params) {}
+    bool parse(Node* out, std::string* err) {
+        bool ok = ternary(out) && expect_end();
+        if (!ok) *err = err_.empty() ? "syntax error" : err_;
+        return ok;
+    }
+    size_t pos_ = 0;
+
+  private:
+    const std::vector<Tok>& t_;
+    const std::map<std::string, Node>& params_;
+    std::string err_;
+
+    const Tok& peek(size_t k = 0) const { return t_[std::min(pos_ + k, t_.size() - 1)]; }
+    bool is_punct(const char* p, size_t k = 0) const { return peek(k).kind == Tok::PUNCT && peek(k).text == p; }
+    bool accept(const char* p) { if (is_punct(p)) { ++pos_; return true; } return false; }
+    bool fail(const std::string& m) { if (err_.empty()) err_ = m; return false; }
+    bool expect(const char* p) { return accept(p) ? true : fail(std::string("expected '") + p + "' near '" + peek().text + "'"); }
+    bool expect_end() { return peek().kind == Tok::END ? true : fail("unexpected '" + peek().text + "'"); }
+
+    static int type_keyword(const std::string& s) {
+        static const std::map<std::string, int> m = {
+            {"sbyte", T_I8}, {"byte", T_U8}, {"short", T_I16}, {"ushort", T_U16}, {"int", T_I32}, {"uint", T_U32},
+            {"long", T_I64}, {"ulong", T_U64}, {"float", T_F32}, {"double", T_F64}, {"bool", T_BOOL},
+            {"SByte", T_I8}, {"Byte", T_U8}, {"Int16", T_I16}, {"UInt16", T_U16}, {"Int32", T_I32}, {"UInt32", T_U32},
+            {"Int64", T_I64}, {"UInt64", T_U64}, {"Single", T_F32}, {"Double", T_F64}, {"Boolean", T_BOOL}};
+        auto it = m.find(s);
+        return it == m.end() ? T_NONE : it->second;
+    }
+
+    bool ternary(Node* out) {
+        Node c;
+        if (!binary(0, &c)) return false;
+        if (!accept("?")) { *out = c; return true; }
+        if (c.type != T_BOOL) return fail("condition of ?: must be bool");
+        Node a, b;
+        if (!ternary(&a) || !expect(":") || !ternary(&b)) return false;
+        int t = common_type(a, b);
+        if (t == T_NONE) return fail(std::string("no common type for ?: between ") + csharp_name(a.type) + " and " + csharp_name(b.type));
+        out->type = t;
+        out->code = "(" + c.code + " ? " + conv(a, t) + " : " + conv(b, t) + ")";
+        return true;
+    }
+
+    static int prec_of(const std::string& op) {
+        if (op == "||") return 1; if (op == "&&") return 2; if (op == "|") return 3; if (op == "^") return 4; if (op == "&") return 5;
+        if (op == "==" || op == "!=") return 6;
+        if (op == "<" || op == ">" || op == "<=" || op == ">=") return 7;
+        if (op == "<<" || op == ">>" || op == ">>>") return 8;
+        if (op == "+" || op == "-") return 9;
+        if (op == "*" || op == "/" || op == "%") return 10;
+        return -1;
+    }
+
+    bool binary(int min_prec, Node* out) {
+        Node lhs;
+        if (!unary(&lhs)) return false;
+        while (peek().kind == Tok::PUNCT) {
+            std::string op = peek().text;
+            int p = prec_of(op);
+            if (p < 0 || p < min_prec) break;
+            ++pos_;
+            Node rhs;
+            if (!binary(p + 1, &rhs)) return false;
+            Node r;
+            if (!apply_binary(op, lhs, rhs, &r)) return false;
+            lhs = r;
+        }
+        *out = lhs;
+        return true;
+    }
+
+    bool apply_binary(const std::string& op, const Node& a, const Node& b, Node* r) {
+        if (op == "&&" || op == "||") {
+            if (a.type != T_BOOL || b.type != T_BOOL) return fail("operands of " + op + " must be bool");
+            r->type = T_BOOL; r->code = "(" + a.code + " " + op + " " + b.code + ")";
+            return true;
+        }
+        if ((op == "&" || op == "|" || op == "^") && a.type == T_BOOL && b.type == T_BOOL) {
+            r->type = T_BOOL; r->code = "((bool)(" + a.code + " " + op + " " + b.code + "))";
+            return true;
+        }
+        if ((op == "==" || op == "!=") && a.type == T_BOOL && b.type == T_BOOL) {
+            r->type = T_BOOL; r->code = "(" + a.code + " " + op + " " + b.code + ")";
+            return true;
+        }
+        if (op == "<<" || op == ">>" || op == ">>>") {
+            if (!is_integral(a.type) || !is_integral(b.type)) return fail("shift needs integral operands");
+            int t = promote_unary(a.type);
+            if (!(implicit_ok(b.type, T_I32) || (b.const_int))) return fail("shift count must convert to int");
+            const char* mask = (t == T_I64 || t == T_U64) ? "63" : "31";
+            std::string cnt = "(((int)(" + b.code + ")) & " + mask + ")";
+            std::string ut = cuda_name(unsigned_of(t));
+            r->type = t;
+            if (op == "<<" || op == ">>>" )
+                r->code = std::string("((") + cuda_name(t) + ")((" + ut + ")(" + conv(a, t) + ") " + (op == "<<" ? "<<" : ">>") + " " + cnt + "))";
+            else
+                r->code = "(" + conv(a, t) + " >> " + cnt + ")";
+            return true;
+        }
+        int t = promote_binary(a, b);
+        if (t == T_NONE) return fail(std::string("operator ") + op + " cannot be applied to " + csharp_name(a.type) + " and " + csharp_name(b.type));
+        std::string ca = conv(a, t), cb = conv(b, t);
+        if (op == "==" || op == "!=" || op == "<" || op == ">" || op == "<=" || op == ">=") {
+            r->type = T_BOOL; r->code = "(" + ca + " " + op + " " + cb + ")";
+            return true;
+        }
+        if (op == "&" || op == "|" || op == "^") {
+            if (!is_integral(t)) return fail("operator " + op + " needs integral operands");
+            r->type = t; r->code = "(" + ca + " " + op + " " + cb + ")";
+            return true;
+        }
+        r->type = t;
+        if (op == "%" && is_float(t)) {
+            r->code = std::string(t == T_F32 ? "fmodf(" : "fmod(") + ca + ", " + cb + ")";
+        } else if ((op == "+" || op == "-" || op == "*") && is_signed_int(t)) {
+            // C# integer arithmetic wraps (unchecked context); do it in the unsigned type so C++ agrees.
+            std::string ut = cuda_name(unsigned_of(t));
+            r->code = std::string("((") + cuda_name(t) + ")((" + ut + ")(" + ca + ") " + op + " (" + ut + ")(" + cb + ")))";
+        } else {
+            r->code = "(" + ca + " " + op + " " + cb + ")";
+        }
+        if (a.const_int && b.const_int && t == T_I32) {   // fold int constants so narrowing rules keep working
+            long long v = 0; bool ok = true;
+            if (op == "+") v = a.cval + b.cval; else if (op == "-") v = a.cval - b.cval; else if (op == "*") v = a.cval * b.cval;
+            else if (op == "/" && b.cval != 0) v = a.cval / b.cval; else if (op == "%" && b.cval != 0) v = a.cval % b.cval; else ok = false;
+            if (ok && v >= -2147483648LL && v <= 2147483647LL) { r->const_int = true; r->cval = v; }
+        }
+        return true;
+    }
+
+    bool unary(Node* out) {
+        if (peek().kind == Tok::PUNCT) {
+            const std::string op = peek().text;
+            if (op == "-" || op == "+" || op == "!" || op == "~") {
+                ++pos_;
+                // -2147483648 and -9223372036854775808 are int / long literals.
+                if (op == "-" && peek().kind == Tok::NUM) {
+                    std::string raw = peek().text; std::string digits;
+                    for (char ch : raw) if (ch != '_') digits += ch;
+                    if (digits == "2147483648") { ++pos_; out->type = T_I32; out->code = "(-2147483647 - 1)"; out->const_int = true; out->cval = -2147483648LL; return postfix(out); }
+                    if (digits == "9223372036854775808" || digits == "9223372036854775808L" || digits == "9223372036854775808l") {
+                        ++pos_; out->type = T_I64; out->code = "(-9223372036854775807LL - 1LL)"; return postfix(out);
+                    }
+                }
+                Node a;
+                if (!unary(&a)) return false;
+                if (op == "!") {
+                    if (a.type != T_BOOL) return fail("operand of ! must be bool");
+                    out->type = T_BOOL; out->code = "(!" + a.code + ")"; return true;
+                }
+                if (!is_numeric(a.type)) return fail("operand of unary " + op + " must be numeric");
+                int t = promote_unary(a.type);
+                if (op == "~") {
+                    if (!is_integral(t)) return fail("operand of ~ must be integral");
+                    out->type = t; out->code = "(~" + conv(a, t) + ")"; return true;
+                }
+                if (op == "+") { out->type = t; out->code = conv(a, t); out->const_int = a.const_int; out->cval = a.cval; return true; }
+                if (t == T_U32) t = T_I64;
+                if (t == T_U64) return fail("unary minus cannot be applied to ulong");
+                out->type = t;
+                if (is_signed_int(t)) {
+                    std::string ut = cuda_name(unsigned_of(t));
+                    out->code = std::string("((") + cuda_name(t) + ")(0u - (" + ut + ")(" + conv(a, t) + ")))";
+                } else {
+                    out->code = "(-" + conv(a, t) + ")";
+                }
+                if (a.const_int) { out->const_int = true; out->cval = -a.cval; }
+                return true;
+            }
+            // cast: '(' type ')' unary
+            if (op == "(" && peek(1).kind == Tok::IDENT && type_keyword(peek(1).text) != T_NONE && is_punct(")", 2)) {
+                int to = type_keyword(peek(1).text);
+                pos_ += 3;
+                Node a;
+                if (!unary(&a)) return false;
+                if (to == T_BOOL) {
+                    if (a.type != T_BOOL) return fail("cannot cast to bool");
+                    *out = a; return true;
+                }
+                if (!is_numeric(a.type)) return fail(std::string("cannot cast ") + csharp_name(a.type) + " to " + csharp_name(to));
+                out->type = to; out->code = conv(a, to);
+                if (a.const_int && to == T_I32) { out->const_int = true; out->cval = a.cval; }
+                return true;
+            }
+        }
+        Node p;
+        if (!primary(&p)) return false;
+        *out = p;
+        return postfix(out);
+    }
+
+    bool postfix(Node* out) { (void)out; return true; }
+
+    bool number(const std::string& raw, Node* out) {
+        std::string s;
+        for (char c : raw) if (c != '_') s += c;
+        std::string body = s, suf;
+        bool hex = s.size() > 2 && s[0] == '0' && (s[1] == 'x' || s[1] == 'X');
+        bool bin = s.size() > 2 && s[0] == '0' && (s[1] == 'b' || s[1] == 'B');
+        size_t e = s.size();
+        if (hex) { while (e > 2 && (s[e - 1] == 'u' || s[e - 1] == 'U' || s[e - 1] == 'l' || s[e - 1] == 'L')) --e; }
+        else { while (e > 0 && isalpha((unsigned char)s[e - 1])) --e; }   // an exponent's 'e' is always followed by digits
+        body = s.substr(0, e); suf = s.substr(e);
+        for (auto& ch : suf) ch = (char)tolower((unsigned char)ch);
+        bool real = !hex && !bin && (body.find('.') != std::string::npos || body.find('e') != std::string::npos || body.find('E') != std::string::npos);
+        if (suf == "m") return fail("decimal literals are not supported");
+        if (suf == "f") { float v = strtof(body.c_str(), nullptr); out->type = T_F32; out->code = fmt_f32(v); return true; }
+        if (suf == "d" || (real && suf.empty())) { double v = strtod(body.c_str(), nullptr); out->type = T_F64; out->code = fmt_f64(v); return true; }
+        if (real) return fail("bad numeric suffix '" + suf + "'");
+        unsigned long long v = 0;
+        errno = 0;
+        if (bin) v = strtoull(body.c_str() + 2, nullptr, 2); else v = strtoull(body.c_str(), nullptr, hex ? 16 : 10);
+        if (errno != 0) return fail("integer literal out of range");
+        bool has_u = suf.find('u') != std::string::npos, has_l = suf.find('l') != std::string::npos;
+        if (!suf.empty() && !(suf == "u" || suf == "l" || suf == "ul" || suf == "lu")) return fail("bad numeric suffix '" + suf + "'");
+        int t;
+        if (has_u && has_l) t = T_U64;
+        else if (has_u) t = v <= 0xffffffffull ? T_U32 : T_U64;
+        else if (has_l) t = v <= 0x7fffffffffffffffull ? T_I64 : T_U64;
+        else t = v <= 0x7fffffffull ? T_I32 : v <= 0xffffffffull ? T_U32 : v <= 0x7fffffffffffffffull ? T_I64 : T_U64;
+        out->type = t;
+        char buf[48];
+        switch (t) {
+            case T_I32: snprintf(buf, sizeof buf, "%llu", v); out->const_int = true; out->cval = (long long)v; break;
+            case T_U32: snprintf(buf, sizeof buf, "%lluu", v); break;
+            case T_I64: snprintf(buf, sizeof buf, "%lluLL", v); break;
+            default: snprintf(buf, sizeof buf, "%lluULL", v); break;
+        }
+        out->code = buf;
+        return true;
+    }
+
+    bool args(std::vector<Node>* out) {
+        if (!expect("(")) return false;
+        if (accept(")")) return true;
+        while (true) {
+            Node a;
+            if (!ternary(&a)) return false;
+            out->push_back(a);
+            if (accept(")")) return true;
+            if (!expect(",")) return false;
+        }
+    }
+
+    bool primary(Node* out) {
+        const Tok& t = peek();
+        if (t.kind == Tok::NUM) { ++pos_; return number(t.text, out); }
+        if (t.kind == Tok::PUNCT && t.text == "(") {
+            ++pos_;
+            Node a;
+            if (!ternary(&a) || !expect(")")) return false;
+            *out = a; out->code = a.code;
+            return true;
+        }
+        if (t.kind != Tok::IDENT) return fail("unexpected '" + t.text + "'");
+        std::string id = t.text;
+        ++pos_;
+        if (id == "true" || id == "false") { out->type = T_BOOL; out->code = id; return true; }
+        auto it = params_.find(id);
+        if (it != params_.end() && !is_punct(".")) { *out = it->second; return true; }
+        if (id == "System" && is_punct(".")) { ++pos_; if (peek().kind != Tok::IDENT) return fail("bad qualified name"); id = peek().text; ++pos_; }
+        if (is_punct(".") && peek(1).kind == Tok::IDENT) {
+            std::string member = peek(1).text;
+            pos_ += 2;
+            if (is_punct("(")) {
+                std::vector<Node> a;
+                if (!args(&a)) return false;
+                return call(id, member, a, out);
+            }
+            return static_member(id, member, out);
+        }
+        return fail("unknown identifier '" + id + "' (only lambda parameters, literals, Math/MathF and numeric type members are translatable)");
+    }
+
+    bool static_member(const std::string& cls, const std::string& m, Node* out) {
+        int t = type_keyword(cls);
+        auto set = [&](int ty, const std::string& code) { out->type = ty; out->code = code; return true; };
+        if (cls == "Math") {
+            if (m == "PI") return set(T_F64, "3.1415926535897931");
+            if (m == "E") return set(T_F64, "2.7182818284590451");
+            if (m == "Tau") return set(T_F64, "6.2831853071795862");
+        } else if (cls == "MathF") {
+            if (m == "PI") return set(T_F32, "3.14159274f");
+            if (m == "E") return set(T_F32, "2.71828175f");
+            if (m == "Tau") return set(T_F32, "6.28318548f");
+        } else if (t == T_F32) {
+            if (m == "MaxValue") return set(T_F32, "3.40282347e+38f");
+            if (m == "MinValue") return set(T_F32, "(-3.40282347e+38f)");
+            if (m == "Epsilon") return set(T_F32, "__int_as_float(1)");
+            if (m == "NaN") return set(T_F32, "__int_as_float(0xffc00000)");
+            if (m == "PositiveInfinity") return set(T_F32, "__int_as_float(0x7f800000)");
+            if (m == "NegativeInfinity") return set(T_F32, "__int_as_float(0xff800000)");
+        } else if (t == T_F64) {
+            if (m == "MaxValue") return set(T_F64, "1.7976931348623157e+308");
+            if (m == "MinValue") return set(T_F64, "(-1.7976931348623157e+308)");
+            if (m == "Epsilon") return set(T_F64, "__longlong_as_double(1LL)");
+            if (m == "NaN") return set(T_F64, "__longlong_as_double(0xfff8000000000000LL)");
+            if (m == "PositiveInfinity") return set(T_F64, "__longlong_as_double(0x7ff0000000000000LL)");
+            if (m == "NegativeInfinity") return set(T_F64, "__longlong_as_double(0xfff0000000000000LL)");
+        } else if (is_integral(t)) {
+            static const char* maxv[] = {"", "((signed char)127)", "((unsigned char)255)", "((short)32767)", "((unsigned short)65535)",
+                                         "2147483647", "4294967295u", "9223372036854775807LL", "18446744073709551615ULL"};
+            static const char* minv[] = {"", "((signed char)(-128))", "((unsigned char)0)", "((short)(-32768))", "((unsigned short)0)",
+                                         "(-2147483647 - 1)", "0u", "(-9223372036854775807LL - 1LL)", "0ULL"};
+            if (m == "MaxValue") return set(t, maxv[t]);
+            if (m == "MinValue") return set(t, minv[t]);
+        }
+        return fail("unknown member " + cls + "." + m);
+    }
+
+    bool call(const std::string& cls, const std::string& m, std::vector<Node>& a, Node* out) {
+        auto need = [&](size_t k) { return a.size() == k ? true : fail(cls + "." + m + " takes " + std::to_string(k) + " argument(s)"); };
+        for (const Node& n : a) if (!is_numeric(n.type)) return fail("argument of " + cls + "." + m + " must be numeric");
+        int tk = type_keyword(cls);
+        if (is_float(tk) && (m == "IsNaN" || m == "IsInfinity" || m == "IsFinite" || m == "IsPositiveInfinity" || m == "IsNegativeInfinity" || m == "IsNegative")) {
+            if (!need(1) || !implicit_ok(a[0].type, tk)) return fail("bad argument for " + cls + "." + m);
+            std::string x = conv(a[0], tk);
+            out->type = T_BOOL;
+            if (m == "IsNaN") out->code = "(" + x + " != " + x + ")";
+            else if (m == "IsInfinity") out->code = "(isinf(" + x + ") != 0)";
+            else if (m == "IsFinite") out->code = "(isfinite(" + x + ") != 0)";
+            else if (m == "IsPositiveInfinity") out->code = "(isinf(" + x + ") != 0 && " + x + " > 0)";
+            else if (m == "IsNegativeInfinity") out->code = "(isinf(" + x + ") != 0 && " + x + " < 0)";
+            else out->code = "(signbit(" + x + ") != 0)";
+            return true;
+        }
+        if (cls != "Math" && cls != "MathF") return fail("calls to " + cls + "." + m + " are not translatable");
+        const bool f = (cls == "MathF");
+        const int ft = f ? T_F32 : T_F64;
+        struct Fn { const char* cs; const char* cu; int nargs; };
+        static const Fn fns[] = {
+            {"Sqrt", "sqrt", 1}, {"Cbrt", "cbrt", 1}, {"Sin", "sin", 1}, {"Cos", "cos", 1}, {"Tan", "tan", 1}, {"Asin", "asin", 1},
+            {"Acos", "acos", 1}, {"Atan", "atan", 1}, {"Sinh", "sinh", 1}, {"Cosh", "cosh", 1}, {"Tanh", "tanh", 1}, {"Exp", "exp", 1},
+            {"Log", "log", 1}, {"Log10", "log10", 1}, {"Log2", "log2", 1}, {"Floor", "floor", 1}, {"Ceiling", "ceil", 1},
+            {"Truncate", "trunc", 1}, {"Round", "rint", 1} /* C# rounds half to even */, {"Pow", "pow", 2}, {"Atan2", "atan2", 2},
+            {"FusedMultiplyAdd", "fma", 3}, {"IEEERemainder", "remainder", 2}, {nullptr, nullptr, 0}};
+        for (const Fn* fn = fns; fn->cs; ++fn) {
+            if (m != fn->cs) continue;
+            if (!need((size_t)fn->nargs)) return false;
+            std::string code = std::string(fn->cu) + (f ? "f(" : "(");
+            for (size_t i = 0; i < a.size(); ++i) {
+                if (!implicit_ok(a[i].type, ft) && !a[i].const_int) return fail(std::string("argument of ") + cls + "." + m + " must convert to " + csharp_name(ft));
+                code += (i ? ", " : "") + conv(a[i], ft);
+            }
+            out->type = ft; out->code = code + ")";
+            return true;
+        }
+        if (m == "Abs") {
+            if (!need(1)) return false;
+            int t = a[0].type;
+            if (f) { if (!implicit_ok(t, T_F32)) return fail("bad argument for MathF.Abs"); out->type = T_F32; out->code = "fabsf(" + conv(a[0], T_F32) + ")"; return true; }
+            if (t == T_U8) t = T_I16; else if (t == T_U16) t = T_I32; else if (t == T_U32) t = T_I64; else if (t == T_U64) return fail("Math.Abs(ulong) is ambiguous in C#");
+            out->type = t;
+            std::string x = conv(a[0], t);
+            if (t == T_F32) out->code = "fabsf(" + x + ")";
+            else if (t == T_F64) out->code = "fabs(" + x + ")";
+            else out->code = std::string("((") + cuda_name(t) + ")(" + x + " < 0 ? -" + x + " : " + x + "))";
+            return true;
+        }
+        if (m == "Min" || m == "Max") {
+            if (!need(2)) return false;
+            int t = f ? T_F32 : common_type(a[0], a[1]);
+            if (t == T_NONE) return fail("no common type for " + cls + "." + m);
+            std::string x = conv(a[0], t), y = conv(a[1], t);
+            out->type = t;
+            if (is_float(t)) out->code = std::string(m == "Min" ? "dcb_net_min(" : "dcb_net_max(") + x + ", " + y + ")";
+            else out->code = std::string("((") + cuda_name(t) + ")(" + x + (m == "Min" ? " < " : " > ") + y + " ? " + x + " : " + y + "))";
+            return true;
+        }
+        if (m == "Clamp") {
+            if (!need(3)) return false;
+            Node ab; ab.type = f ? T_F32 : common_type(a[0], a[1]);
+            int t = f ? T_F32 : (ab.type == T_NONE ? T_NONE : common_type(ab, a[2]));
+            if (t == T_NONE) return fail("no common type for Clamp");
+            std::string v = conv(a[0], t), lo = conv(a[1], t), hi = conv(a[2], t);
+            out->type = t;
+            out->code = std::string("((") + cuda_name(t) + ")(" + v + " < " + lo + " ? " + lo + " : (" + v + " > " + hi + " ? " + hi + " : " + v + ")))";
+            return true;
+        }
+        if (m == "Sign") {
+            if (!need(1)) return false;
+            std::string x = a[0].code;
+            out->type = T_I32; out->code = "((" + x + " > 0) - (" + x + " < 0))";
+            return true;
+        }
+        return fail(cls + "." + m + " is not translatable");
+    }
+};
+
+bool translate_lambda(const std::string& lambda, const std::vector<std::string>& args, const std::vector<int>& arg_types,
+                      std::string* code, int* result_type, std::string* err) {
+    std::vector<Tok> toks;
+    if (!lex(lambda, &toks, err)) return false;
+    // header: ident | ( [type] ident {, [type] ident} ) then =>
+    size_t i = 0;
+    std::vector<std::string> names;
+    auto is_p = [&](size_t k, const char* p) { return k < toks.size() && toks[k].kind == Tok::PUNCT && toks[k].text == p; };
+    if (toks[i].kind == Tok::IDENT) { names.push_back(toks[i].text); ++i; }
+    else if (is_p(i, "(")) {
+        ++i;
+        while (true) {
+            if (toks[i].kind != Tok::IDENT) { *err = "bad lambda parameter list"; return false; }
+            if (toks[i + 1].kind == Tok::IDENT) ++i;   // explicit parameter type: skip it, the element type rules
+            names.push_back(toks[i].text); ++i;
+            if (is_p(i, ")")) { ++i; break; }
+            if (!is_p(i, ",")) { *err = "bad lambda parameter list"; return false; }
+            ++i;
+        }
+    } else { *err = "lambda must start with its parameter list"; return false; }
+    if (!is_p(i, "=>")) { *err = "expected '=>' after the lambda parameters"; return false; }
+    ++i;
+    if (names.size() != args.size()) {
+        *err = "lambda takes " + std::to_string(names.size()) + " parameter(s), the operator supplies " + std::to_string(args.size());
+        return false;
+    }
+    std::map<std::string, Node> params;
+    for (size_t k = 0; k < names.size(); ++k) { Node n; n.code = args[k]; n.type = arg_types[k]; params[names[k]] = n; }
+    std::vector<Tok> body(toks.begin() + i, toks.end());
+    Parser p(body, params);
+    Node r;
+    if (!p.parse(&r, err)) return false;
+    *code = r.code; *result_type = r.type;
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------- chains
+bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info, std::string* err, int* status) {
+    *status = ST_INVALID_ARGUMENT;
+    if (!(t0 >= T_I8 && t0 <= T_BOOL)) { *err = "bad source element type"; return false; }
+    if (ops.empty()) { *err = "a query needs a terminal operator"; return false; }
+    info->in0 = t0; info->in1 = T_NONE; info->n_in = 1; info->has_filter = false;
+    std::string body, key = std::string(csharp_name(t0));
+    int cur = t0;
+    std::string cur_var = "p0";
+    int nvar = 0;
+    size_t nops = ops.size();
+    for (size_t i = 0; i + 1 < nops; ++i) {
+        const OpSpec& op = ops[i];
+        std::string code; int rt = T_NONE; std::string e;
+        if (op.kind == OP_ZIP) {
+            if (i != 0) { *err = "Zip must be the first operator"; *status = ST_NOT_SUPPORTED; return false; }
+            if (!(t1 >= T_I8 && t1 <= T_BOOL)) { *err = "Zip needs the element type of the second sequence"; return false; }
+            info->in1 = t1; info->n_in = 2;
+            if (!translate_lambda(op.lambda, {"p0", "p1"}, {t0, t1}, &code, &rt, &e)) { *err = "Zip: " + e; *status = ST_NOT_SUPPORTED; return false; }
+            key += std::string("|Z(") + csharp_name(t1) + "):" + code;
+        } else if (op.kind == OP_SELECT) {
+            if (!translate_lambda(op.lambda, {cur_var}, {cur}, &code, &rt, &e)) { *err = "Select: " + e; *status = ST_NOT_SUPPORTED; return false; }
+            key += "|S:" + code;
+        } else if (op.kind == OP_WHERE) {
+            if (!translate_lambda(op.lambda, {cur_var}, {cur}, &code, &rt, &e)) { *err = "Where: " + e; *status = ST_NOT_SUPPORTED; return false; }
+            if (rt != T_BOOL) { *err = "Where: predicate must return bool"; *status = ST_NOT_SUPPORTED; return false; }
+            body += "        if (!" + code + ") return false;\n";
+            info->has_filter = true;
+            key += "|W:" + code;
+            continue;
+        } else {
+            *err = "only Select, Where and Zip may precede the terminal operator"; *status = ST_NOT_SUPPORTED; return false;
+        }
+        std::string v = "v" + std::to_string(nvar++);
+        body += std::string("        const ") + cuda_name(rt) + " " + v + " = " + code + ";\n";
+        cur = rt; cur_var = v;
+    }
+    // The canonical key names intermediate variables; make it independent of them by construction (v0, v1, ... are
+    // assigned in order), so equal queries give equal keys.
+    const OpSpec& term = ops.back();
+    info->terminal = term.kind; info->out_type = cur; info->is_identity = (nops == 1);
+    switch (term.kind) {
+        case OP_TOARRAY: info->result_type = cur; info->red_mask = 0; key += "|ToArray"; break;
+        case OP_COUNT: info->result_type = T_I64; info->red_mask = RED_COUNT; key += "|Count"; break;
+        case OP_MIN: case OP_MAX:
+            if (!is_numeric(cur)) { *err = "Min/Max need a numeric element type"; *status = ST_NOT_SUPPORTED; return false; }
+            info->result_type = cur; info->red_mask = term.kind == OP_MIN ? RED_MIN : RED_MAX; key += term.kind == OP_MIN ? "|Min" : "|Max"; break;
+        case OP_SUM: case OP_AVERAGE:
+            // System.Linq defines Sum and Average for int, long, float, double only.
+            if (!(cur == T_I32 || cur == T_I64 || cur == T_F32 || cur == T_F64)) {
+                *err = std::string("Sum/Average are defined for int, long, float and double, not ") + csharp_name(cur) + " (project with Select first)";
+                *status = ST_NOT_SUPPORTED; return false;
+            }
+            info->red_mask = term.kind == OP_SUM ? RED_SUM : (RED_SUM | RED_COUNT);
+            if (term.kind == OP_SUM) { info->result_type = cur; key += "|Sum"; }
+            else { info->result_type = (cur == T_F32) ? T_F32 : T_F64; key += "|Average"; }
+            break;
+        default: *err = "the last operator must be ToArray, Sum, Min, Max, Average or Count"; return false;
+    }
+    std::string s;
+    s += "struct dcb_chain@ {\n";
+    s += std::string("    typedef ") + cuda_name(t0) + " in0_t;\n";
+    s += std::string("    typedef ") + cuda_name(info->n_in == 2 ? info->in1 : t0) + " in1_t;\n";
+    s += std::string("    typedef ") + cuda_name(cur) + " out_t;\n";
+    s += std::string("    static constexpr int n_in = ") + (info->n_in == 2 ? "2" : "1") + ";\n";
+    s += std::string("    static constexpr bool has_filter = ") + (info->has_filter ? "true" : "false") + ";\n";
+    s += "    static __device__ __forceinline__ bool apply(const in0_t& p0, const in1_t& p1, out_t& out) {\n";
+    s += body;
+    s += "        out = " + cur_var + ";\n        return true;\n    }\n};\n";
+    info->chain_src = s;
+    info->key = key;
+    *status = 0;
+    return true;
+}
+
+static std::string replace_all(std::string s, const std::string& a, const std::string& b) {
+    size_t pos = 0;
+    while ((pos = s.find(a, pos)) != std::string::npos) { s.replace(pos, a.size(), b); pos += b.size(); }
+    return s;
+}
+
+std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
+                          int block, int unroll, bool with_prelude) {
+    std::string s;
+    if (with_prelude) {
+        s += "// generated by libdcb200: fused LINQ pipeline\n// key: " + info.key + "\n";
+        if (kernels_header.empty()) s += "#include \"dcb_kernels.cuh\"\n"; else s += kernels_header;
+        s += "\n#ifndef DCB_PRELUDE\n#define DCB_PRELUDE\n"
+             "// Math.Min / Math.Max of .NET: NaN wins, and -0 orders below +0.\n"
+             "template <typename T> __device__ __forceinline__ T dcb_net_min(T a, T b) {\n"
+             "    if (a != b) return (a == a) ? (a < b ? a : b) : a;\n"
+             "    return signbit(a) ? a : b;\n}\n"
+             "template <typename T> __device__ __forceinline__ T dcb_net_max(T a, T b) {\n"
+             "    if (a != b) return (a == a) ? (b < a ? a : b) : a;\n"
+             "    return signbit(b) ? a : b;\n}\n#endif\n\n";
+    }
+    s += replace_all(info.chain_src, "@", suffix);
+    const std::string C = "dcb_chain" + suffix;
+    const std::string B = std::to_string(block), U = std::to_string(unroll);
+    auto cast_in = [&]() { return "(const " + C + "::in0_t*)in0, (const " + C + "::in1_t*)in1"; };
+    const char* variants[2] = {"vec", "scalar"};
+    for (int v = 0; v < 2; ++v) {
+        const std::string vec = v == 0 ? "true" : "false";
+        const std::string u = v == 0 ? U : std::to_string(unroll * 2);
+        if (info.terminal == OP_TOARRAY && !info.has_filter) {
+            s += "extern \"C\" __global__ void __launch_bounds__(" + B + ") dcb_map_" + variants[v] + suffix +
+                 "(const void* in0, const void* in1, long long n, void* out) {\n    dcb::map_body<" + C + ", " + B + ", " + u + ", " + vec + ">(" +
+                 cast_in() + ", n, (" + C + "::out_t*)out);\n}\n";
+        } else if (info.terminal == OP_TOARRAY) {
+            const std::string rows = "dcb::compact_rows<" + C + ", " + B + ", " + vec + ">::value";
+            s += "extern \"C\" __global__ void __launch_bounds__(" + B + ") dcb_compact_" + variants[v] + suffix +
+                 "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, unsigned int* counter, "
+                 "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag) {\n"
+                 "    dcb::compact_body<" + C + ", " + B + ", " + rows + ", " + vec + ">(" + cast_in() + ", n, (" + C +
+                 "::out_t*)out, out_cap, desc, counter, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
+        } else {
+            s += "extern \"C\" __global__ void __launch_bounds__(" + B + ") dcb_reduce_" + variants[v] + suffix +
+                 "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res) {\n    dcb::reduce_body<" + C + ", " +
+                 std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">(" + cast_in() +
+                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res);\n}\n";
+        }
+    }
+    return s;
+}
+
+}  // namespace dcbt

@@ -1,0 +1,57 @@
+// dcb_translate.h — C# lambda text -> CUDA C "chain" functor.
+//
+// Takes the place of the reference's expression-to-CUDA printers
+// (src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:1254-1416 and the wider vocabulary of
+// src/Extensions/DotCompute.Linq/CodeGeneration/GpuExpressionTranslator.cs:130-342). The reference prints the
+// operators as written and lets C++ typing rules decide the arithmetic; this translator types every
+// sub-expression by the C# rules (binary numeric promotion, constant-expression narrowing, shift-count
+// masking, wrapping integer arithmetic) and prints the conversions explicitly, so the kernel computes what the
+// C# lambda computes.
+#ifndef DCB_TRANSLATE_H
+#define DCB_TRANSLATE_H
+
+#include <string>
+#include <vector>
+
+namespace dcbt {
+
+// Values equal DCB_T_* of the C ABI.
+enum Type { T_NONE = 0, T_I8, T_U8, T_I16, T_U16, T_I32, T_U32, T_I64, T_U64, T_F32, T_F64, T_BOOL };
+
+const char* cuda_name(int type);    // "float", "long long", ...
+const char* csharp_name(int type);  // "float", "long", ...
+int type_size(int type);
+bool is_numeric(int type);
+
+// Translate `lambda` ("x => x * 2f + 1f", "(a, b) => a * b"). `args[i]` is the CUDA expression that stands for
+// parameter i and `arg_types[i]` its type. Returns false and fills `err` when the text is outside the grammar.
+bool translate_lambda(const std::string& lambda, const std::vector<std::string>& args, const std::vector<int>& arg_types,
+                      std::string* code, int* result_type, std::string* err);
+
+struct OpSpec { int kind; std::string lambda; };   // kind = DCB_OP_*
+
+struct ChainInfo {
+    int in0 = T_NONE, in1 = T_NONE;   // input element types
+    int n_in = 1;
+    int out_type = T_NONE;            // element type reaching the terminal
+    int terminal = 0;                 // DCB_OP_*
+    int result_type = T_NONE;         // scalar type a reduction returns
+    int red_mask = 0;                 // RED_* bits the kernel needs
+    bool has_filter = false;
+    bool is_identity = false;         // no Select/Where/Zip at all
+    std::string chain_src;            // struct dcb_chain { ... };
+    std::string key;                  // canonical text identifying the pipeline (types + ops + translated code)
+};
+
+// Build the chain of a whole query. Checks operator order and the terminal's type rules.
+bool build_chain(int elem_type0, int elem_type1, const std::vector<OpSpec>& ops, ChainInfo* info, std::string* err, int* status);
+
+// Complete translation unit for NVRTC or nvcc: prelude + chain + extern "C" kernels whose names end in `suffix`.
+// `kernels_header` is the text of dcb_kernels.cuh, or empty to emit an #include of it instead.
+std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
+                          int block, int unroll, bool wrap_namespace);
+
+unsigned long long fnv1a(const std::string& s);
+
+}  // namespace dcbt
+#endif

@@ -1,0 +1,369 @@
+"""The LINQ provider surface: AsComputeQueryable / ComputeSelect / ComputeWhere / ToComputeArray and the
+standard operators, executed as ONE fused sm_100a kernel per query.
+
+Mirrors src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:19-68 (extension methods) and :105-443
+(ComputeQueryProvider). The reference walks a C# expression tree; with no C# compiler in this build the lambdas
+arrive as C# text ("x => x * x + 3f") and are typed and translated by the native library. What the reference
+evaluates for these queries is System.Linq over the same lambdas (ComputeQueryableExtensions.cs:240-267, 344-352,
+628-633); the results here follow those semantics: Where keeps order, Sum(float) accumulates in double, integer Sum
+is checked, Min/Max/Average of nothing throw.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import errors, native as N
+from .accelerator import CudaAccelerator, PinnedArray, UnifiedBuffer, dcb_type, np_dtype
+
+_TERMINAL_NAMES = {N.OP_TOARRAY: "ToArray", N.OP_SUM: "Sum", N.OP_MIN: "Min", N.OP_MAX: "Max",
+                   N.OP_AVERAGE: "Average", N.OP_COUNT: "Count"}
+
+
+class CompiledPipeline:
+    """A compiled query shape (operators + lambdas + element types), reusable over any data of those types."""
+
+    def __init__(self, acc: CudaAccelerator, elem_type0: int, elem_type1: int, ops, force_jit: bool = False):
+        self.acc = acc
+        self._keep = []
+        arr = (N.Op * len(ops))()
+        for i, (kind, lam) in enumerate(ops):
+            arr[i].kind = kind
+            if lam is not None:
+                b = lam.encode("utf-8")
+                self._keep.append(b)
+                arr[i].lambda_ = b
+        desc = N.PipelineDesc(elem_type0, elem_type1, len(ops), arr, N.PIPE_FORCE_JIT if force_jit else 0)
+        self._h = C.c_void_p()
+        N.check(N.lib().dcb_pipeline_compile(acc.handle, C.byref(desc), C.byref(self._h)), acc.handle)
+        info = N.PipelineInfo()
+        N.check(N.lib().dcb_pipeline_info_get(self._h, C.byref(info)), acc.handle)
+        self.info = info
+        self.terminal = info.terminal
+        self.out_dtype = np_dtype(info.out_type)
+        self.result_dtype = np_dtype(info.result_type)
+        self.has_filter = bool(info.has_filter)
+        self.precompiled = bool(info.precompiled)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def Source(self) -> str:
+        need = C.c_size_t()
+        N.check(N.lib().dcb_pipeline_source(self._h, None, 0, C.byref(need)), self.acc.handle)
+        buf = C.create_string_buffer(need.value)
+        N.check(N.lib().dcb_pipeline_source(self._h, buf, need.value, None), self.acc.handle)
+        return buf.value.decode()
+
+    def scalar(self, res: N.Result):
+        """The value a reduction returns, in the type System.Linq would return."""
+        t = self.info.result_type
+        if self.terminal == N.OP_COUNT:
+            return int(res.count)
+        if t == N.T_F32:
+            return np.float32(res.f64)
+        if t == N.T_F64:
+            return float(res.f64)
+        if t == N.T_U64:
+            return int(res.u64)
+        if t == N.T_BOOL:
+            return bool(res.i64)
+        return int(res.i64)
+
+    def finalize(self, host_record: np.ndarray):
+        """Apply the terminal's semantics to a 16-slot record (for instance one combined across GPUs)."""
+        rec = np.ascontiguousarray(host_record).view(np.uint8)
+        assert rec.nbytes == N.DEVICE_RESULT_BYTES
+        res = N.Result()
+        N.check(N.lib().dcb_result_finalize(self._h, rec.ctypes.data_as(C.c_void_p), C.byref(res)), self.acc.handle)
+        return res
+
+
+def generate_source(elem_type0, ops, elem_type1=None) -> str:
+    """CUDA source the generator emits for a query; needs no GPU (used to test the generator anywhere)."""
+    arr = (N.Op * len(ops))()
+    keep = []
+    for i, (kind, lam) in enumerate(ops):
+        arr[i].kind = kind
+        if lam is not None:
+            keep.append(lam.encode())
+            arr[i].lambda_ = keep[-1]
+    desc = N.PipelineDesc(dcb_type(elem_type0), dcb_type(elem_type1) if elem_type1 is not None else 0, len(ops), arr, 0)
+    need = C.c_size_t()
+    err = C.create_string_buffer(512)
+    st = N.lib().dcb_pipeline_generate_source(C.byref(desc), None, 0, C.byref(need), err, 512)
+    if st:
+        raise errors.from_status(st, err.value.decode(), N.lib().dcb_status_name(st).decode())
+    buf = C.create_string_buffer(need.value)
+    N.lib().dcb_pipeline_generate_source(C.byref(desc), buf, need.value, None, err, 512)
+    return buf.value.decode()
+
+
+def translate_lambda(lambda_text: str, *param_dtypes):
+    """(CUDA expression, result dtype) of one C# lambda; needs no GPU."""
+    types = (C.c_int32 * len(param_dtypes))(*[dcb_type(d) for d in param_dtypes])
+    out = C.create_string_buffer(8192)
+    err = C.create_string_buffer(512)
+    rt = C.c_int32()
+    st = N.lib().dcb_translate_lambda(lambda_text.encode(), types, len(param_dtypes), out, 8192, C.byref(rt), err, 512)
+    if st:
+        raise errors.from_status(st, err.value.decode(), N.lib().dcb_status_name(st).decode())
+    return out.value.decode(), np_dtype(rt.value)
+
+
+def _split_lambda(text: str):
+    head, sep, body = text.partition("=>")
+    if not sep:
+        raise errors.NotSupportedException(f"not a lambda: {text!r}")
+    return head.strip(), body.strip()
+
+
+class ComputeQueryable:
+    """IQueryable<T> bound to the compute provider. Operators only record themselves; a terminal runs the query."""
+
+    def __init__(self, source, accelerator: CudaAccelerator | None = None, ops=(), second=None, force_jit=False):
+        if source is None:
+            raise errors.ArgumentNullException("source")
+        self._source = source
+        self._second = second
+        self._ops = tuple(ops)
+        self._acc = accelerator
+        self._force_jit = force_jit
+
+    # ------------------------------------------------------------------ plumbing
+    @property
+    def Accelerator(self) -> CudaAccelerator:
+        if self._acc is None:
+            src = self._source
+            self._acc = src.Accelerator if isinstance(src, UnifiedBuffer) else CudaAccelerator.Default()
+        return self._acc
+
+    @staticmethod
+    def _dtype_of(src) -> np.dtype:
+        if isinstance(src, (UnifiedBuffer, PinnedArray)):
+            return src.dtype
+        return np.asarray(src).dtype
+
+    @staticmethod
+    def _len_of(src) -> int:
+        if isinstance(src, (UnifiedBuffer, PinnedArray)):
+            return src.Length
+        return int(np.asarray(src).size)
+
+    def _with(self, kind, lam, second=None):
+        return ComputeQueryable(self._source, self._acc, self._ops + ((kind, lam),), second if second is not None else self._second,
+                                self._force_jit)
+
+    def _compile(self, terminal: int) -> CompiledPipeline:
+        t0 = dcb_type(self._dtype_of(self._source))
+        t1 = dcb_type(self._dtype_of(self._second)) if self._second is not None else N.T_NONE
+        ops = self._ops + ((terminal, None),)
+        return CompiledPipeline(self.Accelerator, t0, t1, ops, self._force_jit)
+
+    def _length(self) -> int:
+        n = self._len_of(self._source)
+        if self._second is not None:
+            n = min(n, self._len_of(self._second))   # Zip stops at the shorter sequence
+        return n
+
+    @staticmethod
+    def _host_ptr(src, n):
+        if isinstance(src, PinnedArray):
+            return src.array, C.c_void_p(src.ptr)
+        a = np.ascontiguousarray(src).reshape(-1)
+        return a, a.ctypes.data_as(C.c_void_p)
+
+    def _run(self, terminal: int):
+        """Run the query; returns (pipeline, Result, output array or None)."""
+        pipe = self._compile(terminal)
+        acc = self.Accelerator
+        n = self._length()
+        res = N.Result()
+        on_device = isinstance(self._source, UnifiedBuffer)
+        if self._second is not None and isinstance(self._second, UnifiedBuffer) != on_device:
+            raise errors.ArgumentException("both Zip inputs must live on the same side (host arrays or device buffers)")
+        to_array = terminal == N.OP_TOARRAY
+        out = None
+        if on_device:
+            in0 = C.c_void_p(self._source.GetDeviceMemory())
+            in1 = C.c_void_p(self._second.GetDeviceMemory()) if self._second is not None else None
+            if to_array:
+                dbuf = acc.Memory.AllocateAsync(max(n, 1), pipe.out_dtype)
+                try:
+                    N.check(N.lib().dcb_pipeline_run(pipe.handle, in0, in1, n, C.c_void_p(dbuf.GetDeviceMemory()), n, C.byref(res), None), acc.handle)
+                    out = dbuf.CopyToAsync(count=int(res.count)) if res.count else np.empty(0, pipe.out_dtype)
+                finally:
+                    dbuf.Dispose()
+            else:
+                N.check(N.lib().dcb_pipeline_run(pipe.handle, in0, in1, n, None, 0, C.byref(res), None), acc.handle)
+        else:
+            a0, p0 = self._host_ptr(self._source, n)
+            a1, p1 = (None, None)
+            if self._second is not None:
+                a1, p1 = self._host_ptr(self._second, n)
+            if to_array:
+                out = np.empty(n, dtype=pipe.out_dtype)
+                N.check(N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n, out.ctypes.data_as(C.c_void_p), n, C.byref(res)), acc.handle)
+                out = out[: int(res.count)]
+                if out.base is not None and res.count < n:
+                    out = out.copy()
+            else:
+                N.check(N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n, None, 0, C.byref(res)), acc.handle)
+            del a0, a1
+        self.LastResult = res
+        return pipe, res, out
+
+    # ------------------------------------------------------------------ operators (deferred)
+    def Select(self, selector: str) -> "ComputeQueryable":
+        if selector is None:
+            raise errors.ArgumentNullException("selector")
+        return self._with(N.OP_SELECT, selector)
+
+    def Where(self, predicate: str) -> "ComputeQueryable":
+        if predicate is None:
+            raise errors.ArgumentNullException("predicate")
+        return self._with(N.OP_WHERE, predicate)
+
+    def Zip(self, second, resultSelector: str) -> "ComputeQueryable":
+        if second is None:
+            raise errors.ArgumentNullException("second")
+        if resultSelector is None:
+            raise errors.ArgumentNullException("resultSelector")
+        if self._ops:
+            raise errors.NotSupportedException("Zip must be applied to the source sequence, before Select/Where")
+        if isinstance(second, ComputeQueryable):
+            if second._ops:
+                raise errors.NotSupportedException("the second Zip operand must be a plain source")
+            second = second._source
+        return self._with(N.OP_ZIP, resultSelector, second=second)
+
+    ComputeSelect = Select
+    ComputeWhere = Where
+
+    def Skip(self, count: int) -> "ComputeQueryable":
+        if self._ops:
+            raise errors.NotSupportedException("Skip after Select/Where is not fused; materialise with ToArray first")
+        n = self._length()
+        k = min(max(int(count), 0), n)
+        return ComputeQueryable(_slice(self._source, k, n - k), self._acc, (), None, self._force_jit)
+
+    def Take(self, count: int):
+        n = self._length()
+        k = min(max(int(count), 0), n)
+        if self._ops:
+            # Take after a filter needs the first k survivors: run, then cut (the kernel keeps order).
+            return _Materialized(self.ToArray()[:k])
+        return ComputeQueryable(_slice(self._source, 0, k), self._acc, (), None, self._force_jit)
+
+    # ------------------------------------------------------------------ terminals
+    def ToArray(self) -> np.ndarray:
+        if not self._ops:   # AsComputeQueryable().ToArray(): round trip of the source
+            src = self._source
+            if isinstance(src, UnifiedBuffer):
+                return src.ToArray()
+            return np.array(src.array if isinstance(src, PinnedArray) else src, copy=True).reshape(-1)
+        _, _, out = self._run(N.OP_TOARRAY)
+        return out
+
+    ToComputeArray = ToArray
+
+    def ToList(self) -> list:
+        return self.ToArray().tolist()
+
+    def __iter__(self):
+        return iter(self.ToArray())
+
+    def Sum(self, selector: str | None = None):
+        q = self.Select(selector) if selector is not None else self
+        pipe, res, _ = q._run(N.OP_SUM)
+        return pipe.scalar(res)
+
+    def Average(self, selector: str | None = None):
+        q = self.Select(selector) if selector is not None else self
+        pipe, res, _ = q._run(N.OP_AVERAGE)
+        return pipe.scalar(res)
+
+    def Min(self, selector: str | None = None):
+        q = self.Select(selector) if selector is not None else self
+        pipe, res, _ = q._run(N.OP_MIN)
+        return pipe.out_dtype.type(pipe.scalar(res))
+
+    def Max(self, selector: str | None = None):
+        q = self.Select(selector) if selector is not None else self
+        pipe, res, _ = q._run(N.OP_MAX)
+        return pipe.out_dtype.type(pipe.scalar(res))
+
+    def Count(self, predicate: str | None = None) -> int:
+        q = self.Where(predicate) if predicate is not None else self
+        if not q._ops:
+            return q._length()
+        pipe, res, _ = q._run(N.OP_COUNT)
+        return int(res.count)
+
+    LongCount = Count
+
+    def Any(self, predicate: str | None = None) -> bool:
+        return self.Count(predicate) > 0
+
+    def All(self, predicate: str) -> bool:
+        if predicate is None:
+            raise errors.ArgumentNullException("predicate")
+        head, body = _split_lambda(predicate)
+        return self.Count(f"{head} => !({body})") == 0
+
+
+class _Materialized:
+    """Result of an operator that had to run the query (Take after Where): a host array with ToArray()."""
+
+    def __init__(self, arr):
+        self._arr = arr
+
+    def ToArray(self):
+        return self._arr
+
+    ToComputeArray = ToArray
+
+    def __iter__(self):
+        return iter(self._arr)
+
+
+def _slice(src, offset, length):
+    if isinstance(src, UnifiedBuffer):
+        return src.Slice(offset, length)
+    a = src.array if isinstance(src, PinnedArray) else np.asarray(src).reshape(-1)
+    return a[offset: offset + length]
+
+
+def AsComputeQueryable(source, accelerator: CudaAccelerator | None = None, force_jit: bool = False) -> ComputeQueryable:
+    """`source.AsQueryable().AsComputeQueryable()`: source is a host array, a PinnedArray or a device UnifiedBuffer."""
+    if source is None:
+        raise errors.ArgumentNullException("source")
+    if isinstance(source, ComputeQueryable):
+        return source
+    return ComputeQueryable(source, accelerator, force_jit=force_jit)
+
+
+def ToComputeArray(source) -> np.ndarray:
+    """ToComputeArray on a non-compute source is a plain ToArray (ComputeQueryableExtensions.cs:34-41)."""
+    if source is None:
+        raise errors.ArgumentNullException("source")
+    if isinstance(source, (ComputeQueryable, _Materialized)):
+        return source.ToArray()
+    return np.array(source, copy=True).reshape(-1)
+
+
+class ComputeLinqProvider:
+    """IComputeLinqProvider (src/Extensions/DotCompute.Linq/ServiceCollectionExtensions.cs:16-38)."""
+
+    def __init__(self, accelerator: CudaAccelerator | None = None):
+        self._acc = accelerator
+
+    def CreateComputeQueryable(self, source) -> ComputeQueryable:
+        if source is None:
+            raise errors.ArgumentNullException("source")
+        if not isinstance(source, (np.ndarray, UnifiedBuffer, PinnedArray)):
+            source = np.asarray(list(source))
+        return ComputeQueryable(source, self._acc)

@@ -1,0 +1,312 @@
+/*
+ * dcb200.h — C ABI of libdcb200.so, the B200 (sm_100a) engine behind DotCompute's
+ * data-parallel LINQ hot path: fused Select / Zip / Where pipelines ending in
+ * ToArray, Sum, Min, Max, Average or Count.
+ *
+ * The managed side binds these entry points with [LibraryImport("dcb200")]. Each
+ * declaration names the reference code (path inside the DotCompute source tree,
+ * file:line) whose job it takes over.
+ *
+ * Conventions
+ *   - Every function returns a dcb_status (int32). 0 is success. No exception and no
+ *     callback crosses this boundary. The text of the last failure on a context is
+ *     read with dcb_last_error().
+ *   - One dcb_ctx drives one GPU. Every entry point makes that GPU current itself, so
+ *     it may be called from any thread (managed continuations hop threads; the
+ *     reference calls cuCtxSetCurrent before each native call for the same reason,
+ *     src/Backends/DotCompute.Backends.CUDA/Kernels/CudaKernelLauncher.cs:220).
+ *   - Sizes and element counts are int64_t / size_t throughout. The reference uses
+ *     int lengths (src/Core/DotCompute.Abstractions/Interfaces/IUnifiedMemoryBuffer.cs:20,
+ *     src/Extensions/DotCompute.Linq/CodeGeneration/RuntimeExecutor.cs:275), which
+ *     overflow at 2^28 floats; this ABI does not.
+ *   - A `stream` argument is a cudaStream_t passed as void*; NULL means the context's
+ *     own stream.
+ *   - There is no CPU fallback behind any of these calls. If the GPU, the driver or
+ *     NVRTC is missing the call fails with a status; it never computes on the host.
+ */
+#ifndef DCB200_H
+#define DCB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DCB_ABI_VERSION 1
+
+/* ------------------------------------------------------------------------- status */
+
+typedef int32_t dcb_status;
+
+/* Status codes. The hundreds digit is the class, mirroring CudaErrorClass
+ * (src/Backends/DotCompute.Backends.CUDA/ErrorHandling/CudaErrorClassification.cs:17-46):
+ * 1xx transient, 2xx resource, 3xx programmer, 4xx fatal, 5xx query semantics. */
+enum {
+    DCB_OK = 0,
+    DCB_ERR_NOT_READY = 101,        /* transient: work still in flight */
+    DCB_ERR_TIMEOUT = 102,          /* transient: a bounded device-side wait ran out */
+    DCB_ERR_OUT_OF_MEMORY = 201,    /* resource: device or pinned allocation failed */
+    DCB_ERR_OUTPUT_TOO_SMALL = 202, /* resource: ToArray output capacity below survivor count */
+    DCB_ERR_INVALID_ARGUMENT = 301, /* programmer: null / negative / mismatched argument (ArgumentException) */
+    DCB_ERR_NOT_SUPPORTED = 302,    /* programmer: lambda or type outside the translator's grammar (NotSupportedException) */
+    DCB_ERR_COMPILE = 303,          /* programmer: NVRTC rejected generated or user source */
+    DCB_ERR_DISPOSED = 304,         /* programmer: handle used after destroy (ObjectDisposedException) */
+    DCB_ERR_NO_DEVICE = 401,        /* fatal: no usable CUDA device / driver */
+    DCB_ERR_CUDA = 402,             /* fatal: a CUDA call failed; text in dcb_last_error */
+    DCB_ERR_EMPTY_SEQUENCE = 501,   /* Min/Max/Average of zero elements (InvalidOperationException in System.Linq) */
+    DCB_ERR_OVERFLOW = 502          /* checked integer Sum left its type's range (OverflowException) */
+};
+
+enum { DCB_CLASS_NONE = 0, DCB_CLASS_TRANSIENT = 1, DCB_CLASS_RESOURCE = 2,
+       DCB_CLASS_PROGRAMMER = 3, DCB_CLASS_FATAL = 4, DCB_CLASS_QUERY = 5 };
+
+/* Replaces CudaErrorClassification.Classify (ErrorHandling/CudaErrorClassification.cs:17-46). */
+int32_t dcb_status_class(dcb_status s);
+const char* dcb_status_name(dcb_status s);
+int32_t dcb_abi_version(void);
+
+/* -------------------------------------------------------------------------- types */
+
+/* Element types: the unmanaged primitives the reference maps to CUDA C
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:1399-1416). */
+enum {
+    DCB_T_NONE = 0,
+    DCB_T_I8 = 1,  /* sbyte  */
+    DCB_T_U8 = 2,  /* byte   */
+    DCB_T_I16 = 3, /* short  */
+    DCB_T_U16 = 4, /* ushort */
+    DCB_T_I32 = 5, /* int    */
+    DCB_T_U32 = 6, /* uint   */
+    DCB_T_I64 = 7, /* long   */
+    DCB_T_U64 = 8, /* ulong  */
+    DCB_T_F32 = 9, /* float  */
+    DCB_T_F64 = 10, /* double */
+    DCB_T_BOOL = 11 /* bool, one byte */
+};
+int32_t dcb_type_size(int32_t type);
+
+/* Operators of a query, in call order. Same vocabulary as the reference's expression
+ * visitor (src/Extensions/DotCompute.Linq/Compilation/ExpressionTreeVisitor.cs:234-272),
+ * plus Zip, which the reference rejects (ExpressionTreeVisitor.cs:268). */
+enum {
+    DCB_OP_SELECT = 1,   /* lambda: one parameter, any result type                 */
+    DCB_OP_WHERE = 2,    /* lambda: one parameter, bool result; order is preserved  */
+    DCB_OP_ZIP = 3,      /* lambda: two parameters; must be the first operator      */
+    DCB_OP_TOARRAY = 16, /* terminal: materialise the surviving elements in order   */
+    DCB_OP_SUM = 17,     /* terminal: int / long (checked) or float / double (fp64 accumulation) */
+    DCB_OP_MIN = 18,
+    DCB_OP_MAX = 19,
+    DCB_OP_AVERAGE = 20,
+    DCB_OP_COUNT = 21    /* also LongCount */
+};
+
+typedef struct dcb_op {
+    int32_t kind;       /* DCB_OP_* */
+    const char* lambda; /* C# lambda text, e.g. "x => x * x + 3f"; NULL for terminals */
+} dcb_op;
+
+typedef struct dcb_pipeline_desc {
+    int32_t elem_type0; /* element type of the source sequence                     */
+    int32_t elem_type1; /* element type of Zip's second sequence, else DCB_T_NONE   */
+    int32_t n_ops;
+    const dcb_op* ops;  /* zero or more SELECT/WHERE/ZIP followed by one terminal   */
+    uint32_t flags;     /* DCB_PIPE_* */
+} dcb_pipeline_desc;
+
+enum {
+    DCB_PIPE_FORCE_JIT = 1u /* ignore the precompiled kernel table, always go through NVRTC */
+};
+
+typedef struct dcb_pipeline_info {
+    int32_t terminal;     /* DCB_OP_* of the terminal                              */
+    int32_t out_type;     /* element type reaching the terminal (ToArray element type) */
+    int32_t result_type;  /* type of the scalar a reduction returns (Average(int) is double) */
+    int32_t has_filter;   /* 1 if any Where is present                             */
+    int32_t n_inputs;     /* 1, or 2 with Zip                                      */
+    int32_t precompiled;  /* 1 if served from the ahead-of-time kernel table, 0 if NVRTC built it */
+    int64_t tile_elems;   /* elements one compaction tile covers (0 if not a compaction) */
+    double  compile_ms;   /* wall time dcb_pipeline_compile spent                   */
+} dcb_pipeline_info;
+
+/* What a run produced. For reductions the fields not named by the terminal are zero. */
+typedef struct dcb_result {
+    int64_t count;     /* elements that reached the terminal (survivors)           */
+    double  f64;       /* Sum / Average / Min / Max when result_type is F32 or F64 (already rounded to
+                          float precision for F32) */
+    int64_t i64;       /* Sum / Min / Max / Count when result_type is an integer type up to I64 */
+    uint64_t u64;      /* the same for U64                                          */
+    uint32_t flags;    /* DCB_RES_* */
+    uint32_t launches; /* kernels launched by this call                             */
+    float   kernel_ms; /* device time of those kernels (CUDA events), 0 if not timed */
+    float   total_ms;  /* device time including copies for the *_host call, else kernel_ms */
+} dcb_result;
+
+enum {
+    DCB_RES_SAW_NAN = 1u,
+    DCB_RES_TRUNCATED = 2u,
+    DCB_RES_TIMEOUT = 4u,
+    DCB_RES_OVERFLOW = 8u
+};
+
+/* Raw per-run record the kernels write in device memory: 16 eight-byte slots. A sharded
+ * query combines these across GPUs with NCCL before dcb_result_finalize(). */
+enum {
+    DCB_SLOT_FSUM = 0,   /* double: floating Sum accumulator                       */
+    DCB_SLOT_COUNT_F = 1,/* double: count (exact below 2^53), so {sum,count} is one fp64 all-reduce */
+    DCB_SLOT_ISUM_LO = 2,/* int64: low word of the integer Sum                     */
+    DCB_SLOT_ISUM_HI = 3,/* int64: high word (sign-extended), non-trivial only for 64-bit elements */
+    DCB_SLOT_COUNT = 4,  /* int64: survivors                                        */
+    DCB_SLOT_FMIN = 5,   /* double                                                  */
+    DCB_SLOT_FMAX = 6,   /* double                                                  */
+    DCB_SLOT_IMIN = 7,   /* int64 (raw bits of the element for U64)                 */
+    DCB_SLOT_IMAX = 8,   /* int64                                                   */
+    DCB_SLOT_FLAGS = 9,  /* uint64: DCB_RES_* bits plus NaN bookkeeping             */
+    DCB_SLOT_NSLOTS = 16
+};
+#define DCB_DEVICE_RESULT_BYTES 128
+
+typedef struct dcb_ctx dcb_ctx;
+typedef struct dcb_buf dcb_buf;
+typedef struct dcb_pipeline dcb_pipeline;
+typedef struct dcb_kernel dcb_kernel;
+
+/* ---------------------------------------------------------------------- lifecycle */
+
+/* Opens GPU `device`, creates its stream and scratch. Replaces `new CudaAccelerator(deviceId: 0)`
+ * + CudaContext (src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:184-194,
+ * src/Backends/DotCompute.Backends.CUDA/CudaAccelerator.cs:59,192-195). */
+dcb_status dcb_init(int32_t device, dcb_ctx** out_ctx);
+dcb_status dcb_shutdown(dcb_ctx* ctx);
+/* Copies the last error text of `ctx` (or of the calling thread when ctx is NULL) into buf. */
+dcb_status dcb_last_error(dcb_ctx* ctx, char* buf, size_t cap);
+/* Number of CUDA devices visible; 0 with DCB_ERR_NO_DEVICE when there is none. */
+dcb_status dcb_device_count(int32_t* out_count);
+/* Name, SM count, memory in bytes of the context's GPU. Replaces IComputeOrchestrator.GetDeviceInfo
+ * (src/Core/DotCompute.Abstractions/Interfaces/IComputeOrchestrator.cs:21-104). */
+dcb_status dcb_device_info(dcb_ctx* ctx, char* name, size_t name_cap, int32_t* sm_count,
+                           int64_t* total_mem, int32_t* cc_major, int32_t* cc_minor);
+/* Use `stream` (a cudaStream_t) as the context's stream from now on; NULL restores its own. */
+dcb_status dcb_set_stream(dcb_ctx* ctx, void* stream);
+dcb_status dcb_stream_sync(dcb_ctx* ctx, void* stream);
+/* Upper bound on polls of one look-back wait inside the compaction kernel before it gives up
+ * and reports DCB_ERR_TIMEOUT (default 1<<22). */
+dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls);
+
+/* ------------------------------------------------------------------------- memory */
+
+/* Device buffers. Replace CudaMemoryManager.AllocateAsync / FreeAsync
+ * (src/Backends/DotCompute.Backends.CUDA/Memory/CudaMemoryManager.cs:140-292) and back the
+ * IUnifiedMemoryBuffer<T> contract (src/Core/DotCompute.Abstractions/Interfaces/IUnifiedMemoryBuffer.cs:13-261).
+ * Allocation comes from the device's stream-ordered pool, not one cudaMalloc per buffer. */
+dcb_status dcb_alloc(dcb_ctx* ctx, size_t bytes, dcb_buf** out_buf);
+dcb_status dcb_free(dcb_ctx* ctx, dcb_buf* buf);
+/* Wrap memory somebody else owns (for instance a tensor) without taking ownership. */
+dcb_status dcb_buf_wrap(dcb_ctx* ctx, void* device_ptr, size_t bytes, dcb_buf** out_buf);
+/* Zero-copy sub-range: Slice(offset,length) / AsType<T>() of IUnifiedMemoryBuffer (IUnifiedMemoryBuffer.cs:13-200). */
+dcb_status dcb_buf_slice(dcb_ctx* ctx, dcb_buf* parent, size_t byte_offset, size_t bytes, dcb_buf** out_buf);
+void*  dcb_devptr(const dcb_buf* buf);
+size_t dcb_buf_bytes(const dcb_buf* buf);
+
+/* Copies. Replace the blocking cudaMemcpy calls of CudaMemoryManager (CudaMemoryManager.cs:605-664)
+ * with stream-ordered ones; `host` should be pinned for the copy to be truly asynchronous. */
+dcb_status dcb_h2d_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const void* host, size_t bytes, void* stream);
+dcb_status dcb_d2h_async(dcb_ctx* ctx, void* host, const dcb_buf* src, size_t src_off, size_t bytes, void* stream);
+dcb_status dcb_d2d_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const dcb_buf* src, size_t src_off, size_t bytes, void* stream);
+/* FillAsync of IUnifiedMemoryBuffer<T>: repeats a 1/2/4/8-byte pattern. */
+dcb_status dcb_fill_async(dcb_ctx* ctx, dcb_buf* dst, size_t dst_off, const void* pattern, int32_t pattern_bytes, size_t count, void* stream);
+
+/* Pinned host memory. Replace CudaPinnedMemoryAllocator (src/Backends/DotCompute.Backends.CUDA/Memory/CudaPinnedMemoryAllocator.cs:104). */
+dcb_status dcb_host_alloc_pinned(dcb_ctx* ctx, size_t bytes, void** out_host);
+dcb_status dcb_host_free_pinned(dcb_ctx* ctx, void* host);
+dcb_status dcb_pin_host(dcb_ctx* ctx, void* host, size_t bytes);   /* cudaHostRegister of caller memory */
+dcb_status dcb_unpin_host(dcb_ctx* ctx, void* host);
+
+/* Bytes currently allocated / peak / number of allocations served (CudaMemoryManager.Analytics.cs). */
+dcb_status dcb_memory_stats(dcb_ctx* ctx, int64_t* bytes_in_use, int64_t* peak_bytes, int64_t* n_allocs);
+
+/* ------------------------------------------------------------------------ compile */
+
+/* Translate one C# lambda to the CUDA C statements it becomes inside a fused kernel. Replaces
+ * CudaKernelGenerator.ExpressionToCode / FormatConstant / GetOperator / GenerateMethodCall
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:1254-1391) and covers the wider
+ * vocabulary of GpuExpressionTranslator (bitwise, shifts, ?:, casts, Math.*). `param_types` gives the
+ * DCB_T_* type of each lambda parameter. On success *result_type is the C# type of the body. */
+dcb_status dcb_translate_lambda(const char* lambda, const int32_t* param_types, int32_t n_params,
+                                char* out_code, size_t out_cap, int32_t* result_type,
+                                char* err, size_t err_cap);
+
+/* Build the fused kernels of a query. Replaces CompilationPipeline.CompileToGpuKernelAsync ->
+ * CudaRuntimeKernelCompiler.CompileFromGraphAsync -> CudaKernelGenerator.GenerateCudaKernel -> NVRTC
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/CompilationPipeline.cs:914-965,
+ * src/Extensions/DotCompute.Linq/Compilation/CudaRuntimeKernelCompiler.cs:80-189,
+ * src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:81-125,
+ * src/Backends/DotCompute.Backends.CUDA/Compilation/PTXCompiler.cs:83-273). Compiled pipelines are cached per
+ * context under a key that contains the full lambda text (the reference's key leaves it out,
+ * src/Extensions/DotCompute.Linq/CodeGeneration/KernelCache.cs:297-351). */
+dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc* desc, dcb_pipeline** out_pipeline);
+dcb_status dcb_pipeline_destroy(dcb_pipeline* p);
+dcb_status dcb_pipeline_info_get(const dcb_pipeline* p, dcb_pipeline_info* out_info);
+/* The generated CUDA source (the text NVRTC saw, or would see for a precompiled pipeline). */
+dcb_status dcb_pipeline_source(const dcb_pipeline* p, char* buf, size_t cap, size_t* needed);
+/* Generate that source without a GPU or a context (used to test the generator on any machine). */
+dcb_status dcb_pipeline_generate_source(const dcb_pipeline_desc* desc, char* buf, size_t cap, size_t* needed,
+                                        char* err, size_t err_cap);
+
+/* ---------------------------------------------------------------------------- run */
+
+/* Run a compiled query on device-resident inputs. Replaces RuntimeExecutor.ExecuteGpuOnCudaAsync's launch
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/RuntimeExecutor.cs:245-312) and
+ * CudaCompiledKernel.ExecuteAsync / CudaKernelLauncher (src/Backends/DotCompute.Backends.CUDA/Kernels/CudaCompiledKernel.cs:495-547,
+ * Kernels/CudaKernelLauncher.cs:204-347).
+ *   in0, in1   device pointers to n elements each (in1 NULL unless Zip)
+ *   out        device pointer with room for out_cap elements of out_type (ToArray only, else NULL)
+ *   d_result   device pointer to DCB_DEVICE_RESULT_BYTES the kernels fill; NULL uses context scratch
+ *   d_prev     device pointer to an earlier run's record whose count is the output offset of this run
+ *              (chains chunked compactions without a host round trip); normally NULL
+ * The call only enqueues work on `stream`. */
+dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, const void* in1, int64_t n,
+                                  void* out, int64_t out_cap, void* d_result, const void* d_prev, void* stream);
+/* Same, then waits, reads the record back and applies the terminal's semantics
+ * (empty-sequence and overflow errors, Average division, rounding to float). */
+dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const void* in1, int64_t n,
+                            void* out, int64_t out_cap, dcb_result* result, void* stream);
+/* Turn a (possibly NCCL-combined) 16-slot record held in HOST memory into a dcb_result. */
+dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* host_record, dcb_result* result);
+
+/* The call a host-array user makes: inputs and output are HOST buffers (pinned for full speed). Copies go
+ * through the chunked, double-buffered staging path overlapped with the kernels. Replaces the whole of
+ * RuntimeExecutor.ExecuteGpuOnCudaAsync (alloc, H2D, launch, D2H, free; RuntimeExecutor.cs:245-312) and
+ * BaseMemoryManager.AllocateAndCopyAsync (src/Core/DotCompute.Core/Memory/BaseMemoryManager.cs:104-112).
+ * For ToArray, host_out receives result->count elements (capacity host_out_cap). */
+dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
+                                 void* host_out, int64_t host_out_cap, dcb_result* result);
+
+/* ---------------------------------------------------------- [Kernel] source kernels */
+
+/* Compile CUDA C text produced by the [Kernel] generator and launch it. Replace
+ * CudaAccelerator.CompileKernelAsync + CudaCompiledKernel.LoadModule + cuLaunchKernel as used by
+ * KernelExecutionService.ExecuteAsync (src/Runtime/DotCompute.Runtime/Services/KernelExecutionService.cs:291-328,
+ * src/Backends/DotCompute.Backends.CUDA/Kernels/CudaCompiledKernel.cs:151-225). NVRTC runs with
+ * --gpu-architecture=sm_100a and without --use_fast_math (the reference passes it, PTXCompiler.cs:263-264). */
+dcb_status dcb_kernel_compile(dcb_ctx* ctx, const char* cuda_source, const char* entry_point, dcb_kernel** out_kernel);
+dcb_status dcb_kernel_launch(dcb_kernel* k, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_bytes,
+                             void** args, void* stream);
+dcb_status dcb_kernel_destroy(dcb_kernel* k);
+
+/* ------------------------------------------------------------------------- timing */
+
+/* CUDA events on the context's stream. Replace the ExecutionMetrics timers of the LINQ executor
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/ExecutionMetrics.cs:11-60). */
+dcb_status dcb_event_create(dcb_ctx* ctx, void** out_event);
+dcb_status dcb_event_record(dcb_ctx* ctx, void* event, void* stream);
+dcb_status dcb_event_elapsed_ms(dcb_ctx* ctx, void* start, void* stop, float* out_ms);
+dcb_status dcb_event_destroy(dcb_ctx* ctx, void* event);
+/* Kernels launched by this context since dcb_init (the library's own counter). */
+dcb_status dcb_launch_count(dcb_ctx* ctx, int64_t* out_launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DCB200_H */

@@ -1,0 +1,116 @@
+"""linq_oracle — TEST INFRASTRUCTURE ONLY: a generic CPU Enumerable with System.Linq semantics.
+
+The reference evaluates AsComputeQueryable() queries with System.Linq (ExecuteFallback<T>,
+src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:628-633; scalar results :240-267). This module restates
+those operators over numpy arrays so a test can write the same query twice: once as C# text for the GPU, once as a
+Python callable here. Callables receive numpy arrays (or numpy scalars) of the element dtype, so `x * np.float32(2)
++ np.float32(1)` rounds after each operation exactly as the C# float expression does (numpy never contracts to FMA).
+
+Sum(float) follows the BCL: sequential accumulation in double, one rounding to float (np.cumsum is sequential).
+Integer Sum is checked. Min / Max / Average of an empty sequence raise. Float Min returns NaN if any element is NaN;
+Max returns NaN only when every element is NaN.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+class InvalidOperationError(Exception):
+    pass
+
+
+class Enumerable:
+    def __init__(self, data):
+        self.data = np.asarray(data).reshape(-1)
+
+    # deferred operators ------------------------------------------------------------------------------
+    def Select(self, f):
+        out = f(self.data) if self.data.size else f(self.data[:0]) if True else None
+        return Enumerable(np.asarray(out))
+
+    def Where(self, pred):
+        if self.data.size == 0:
+            return Enumerable(self.data)
+        mask = np.asarray(pred(self.data), dtype=bool)
+        if mask.shape == ():                       # predicate ignored its argument (x => true)
+            mask = np.full(self.data.shape, bool(mask))
+        return Enumerable(self.data[mask])
+
+    def Zip(self, other, f):
+        b = other.data if isinstance(other, Enumerable) else np.asarray(other).reshape(-1)
+        n = min(self.data.size, b.size)
+        return Enumerable(np.asarray(f(self.data[:n], b[:n])))
+
+    def Take(self, n):
+        return Enumerable(self.data[: max(n, 0)])
+
+    def Skip(self, n):
+        return Enumerable(self.data[max(n, 0):])
+
+    # terminals -----------------------------------------------------------------------------------------
+    def ToArray(self):
+        return self.data.copy()
+
+    def Count(self, pred=None):
+        return int((self.Where(pred) if pred else self).data.size)
+
+    def Any(self, pred=None):
+        return self.Count(pred) > 0
+
+    def All(self, pred):
+        return self.Where(pred).data.size == self.data.size
+
+    def Sum(self):
+        d = self.data
+        if d.dtype in (np.float32, np.float64):
+            s = np.cumsum(d.astype(np.float64))[-1] if d.size else np.float64(0)
+            return d.dtype.type(s)
+        if d.dtype in (np.int32, np.int64):
+            info = np.iinfo(d.dtype)
+            if d.dtype == np.int32:
+                pref = np.cumsum(d.astype(np.int64))
+                if pref.size and (pref.max() > info.max or pref.min() < info.min):
+                    raise OverflowError("Arithmetic operation resulted in an overflow.")
+                return int(pref[-1]) if pref.size else 0
+            total = 0
+            for v in d.tolist():               # Python ints: exact, checked against the long range
+                total += v
+                if total > info.max or total < info.min:
+                    raise OverflowError("Arithmetic operation resulted in an overflow.")
+            return total
+        raise TypeError(f"Sum is not defined for {d.dtype}")
+
+    def Average(self):
+        d = self.data
+        if d.size == 0:
+            raise InvalidOperationError("Sequence contains no elements")
+        if d.dtype == np.float32:
+            return np.float32(np.cumsum(d.astype(np.float64))[-1] / d.size)
+        if d.dtype == np.float64:
+            return float(np.cumsum(d)[-1] / d.size)
+        return float(int(np.sum(d.astype(object))) / d.size) if d.dtype == np.int64 else float(np.sum(d.astype(np.int64)) / d.size)
+
+    def Min(self):
+        d = self.data
+        if d.size == 0:
+            raise InvalidOperationError("Sequence contains no elements")
+        if d.dtype.kind == "f":
+            return d.dtype.type(np.nan) if np.isnan(d).any() else d.min()
+        return d.min()
+
+    def Max(self):
+        d = self.data
+        if d.size == 0:
+            raise InvalidOperationError("Sequence contains no elements")
+        if d.dtype.kind == "f":
+            return d.dtype.type(np.nan) if np.isnan(d).all() else np.nanmax(d)
+        return d.max()
+
+
+def scalar_enumerable_where_select(data, pred, sel):
+    """Pure-Python element-by-element loop (small inputs): the literal shape of Enumerable.Where(...).Select(...)."""
+    out = []
+    for x in np.asarray(data).reshape(-1):
+        if pred(x):
+            out.append(sel(x))
+    return out

