@@ -774,11 +774,10 @@ float round_f32(double v) { return (float)v; }
 
 }  // namespace
 
-extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* host_record, dcb_result* r) {
-    if (!p || !host_record || !r) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "null argument");
-    dcb_ctx* ctx = p->ctx;
+extern "C" dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, const void* host_record, dcb_result* r) {
+    if (!host_record || !r) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "null argument");
+    dcb_ctx* ctx = nullptr;
     const dcb::DeviceResult* d = (const dcb::DeviceResult*)host_record;
-    const dcbt::ChainInfo& I = p->info;
     const uint32_t keep_launches = r->launches;
     const float km = r->kernel_ms, tm = r->total_ms;
     memset(r, 0, sizeof *r);
@@ -786,8 +785,8 @@ extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* hos
     r->count = d->count;
     const uint64_t fl = d->flags;
     if (fl & dcb::FLAG_SAW_NAN) r->flags |= DCB_RES_SAW_NAN;
-    const int rt = I.result_type;
-    switch (I.terminal) {
+    const bool fp = out_type == DCB_T_F32 || out_type == DCB_T_F64;
+    switch (terminal) {
         case DCB_OP_TOARRAY:
             if (fl & dcb::FLAG_TIMEOUT) { r->flags |= DCB_RES_TIMEOUT; return set_err(ctx, DCB_ERR_TIMEOUT, "a look-back wait in the compaction kernel ran out"); }
             if (fl & dcb::FLAG_TRUNCATED) { r->flags |= DCB_RES_TRUNCATED; return set_err(ctx, DCB_ERR_OUTPUT_TOO_SMALL, "%lld elements survive, the output holds fewer", (long long)d->count); }
@@ -797,27 +796,27 @@ extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* hos
             return DCB_OK;
         case DCB_OP_SUM:
         case DCB_OP_AVERAGE: {
-            const bool avg = I.terminal == DCB_OP_AVERAGE;
+            const bool avg = terminal == DCB_OP_AVERAGE;
+            if (!(out_type == DCB_T_I32 || out_type == DCB_T_I64 || fp)) return set_err(ctx, DCB_ERR_NOT_SUPPORTED, "Sum/Average are defined for int, long, float, double");
             if (avg && d->count == 0) return set_err(ctx, DCB_ERR_EMPTY_SEQUENCE, "Average of an empty sequence");
-            if (I.out_type == DCB_T_F32 || I.out_type == DCB_T_F64) {
-                double v = avg ? d->fsum / (double)d->count : d->fsum;
-                r->f64 = (rt == DCB_T_F32) ? (double)round_f32(v) : v;
+            if (fp) {
+                const double v = avg ? d->fsum / (double)d->count : d->fsum;
+                r->f64 = (out_type == DCB_T_F32) ? (double)round_f32(v) : v;   // one rounding, as (float)sum in the BCL
                 return DCB_OK;
             }
             // integer Sum is checked in System.Linq: leaving the element type's range is an error
-            const bool hi_ok = d->isum_hi == ((d->isum_lo < 0) ? -1 : 0);
-            bool overflow = !hi_ok;
-            if (I.out_type == DCB_T_I32 && !avg) overflow = overflow || d->isum_lo > 2147483647LL || d->isum_lo < -2147483648LL;
-            if (overflow) { r->flags |= DCB_RES_OVERFLOW; return set_err(ctx, DCB_ERR_OVERFLOW, "integer Sum overflowed %s", dcbt::csharp_name(I.out_type)); }
+            bool overflow = d->isum_hi != ((d->isum_lo < 0) ? -1 : 0);
+            if (out_type == DCB_T_I32 && !avg) overflow = overflow || d->isum_lo > 2147483647LL || d->isum_lo < -2147483648LL;
+            if (overflow) { r->flags |= DCB_RES_OVERFLOW; return set_err(ctx, DCB_ERR_OVERFLOW, "integer Sum overflowed %s", dcbt::csharp_name(out_type)); }
             if (avg) r->f64 = (double)d->isum_lo / (double)d->count;
             else { r->i64 = d->isum_lo; r->u64 = (uint64_t)d->isum_lo; }
             return DCB_OK;
         }
         case DCB_OP_MIN:
         case DCB_OP_MAX: {
-            if (d->count == 0) return set_err(ctx, DCB_ERR_EMPTY_SEQUENCE, "%s of an empty sequence", I.terminal == DCB_OP_MIN ? "Min" : "Max");
-            const bool mn = I.terminal == DCB_OP_MIN;
-            if (rt == DCB_T_F32 || rt == DCB_T_F64) {
+            const bool mn = terminal == DCB_OP_MIN;
+            if (d->count == 0) return set_err(ctx, DCB_ERR_EMPTY_SEQUENCE, "%s of an empty sequence", mn ? "Min" : "Max");
+            if (fp) {
                 // Enumerable.Min returns NaN if any element is NaN; Enumerable.Max only if all are.
                 const double nan = std::numeric_limits<double>::quiet_NaN();
                 if (mn) r->f64 = (fl & dcb::FLAG_SAW_NAN) ? nan : d->fmin;
@@ -828,8 +827,15 @@ extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* hos
             }
             return DCB_OK;
         }
-        default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "pipeline has no terminal");
+        default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "unknown terminal operator %d", terminal);
     }
+}
+
+extern "C" dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* host_record, dcb_result* r) {
+    if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
+    dcb_status st = dcb_record_finalize(p->info.terminal, p->info.out_type, host_record, r);
+    if (st != DCB_OK) snprintf(p->ctx->err, sizeof p->ctx->err, "%s", tl_error);
+    return st;
 }
 
 extern "C" dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,

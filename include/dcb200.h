@@ -272,8 +272,12 @@ dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, const void* 
  * (empty-sequence and overflow errors, Average division, rounding to float). */
 dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const void* in1, int64_t n,
                             void* out, int64_t out_cap, dcb_result* result, void* stream);
-/* Turn a (possibly NCCL-combined) 16-slot record held in HOST memory into a dcb_result. */
+/* Turn a (possibly NCCL-combined) 16-slot record held in HOST memory into a dcb_result: applies what System.Linq's
+ * terminal does after its loop (the scalar branch of ComputeQueryProvider.Execute,
+ * src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:240-267). */
 dcb_status dcb_result_finalize(const dcb_pipeline* p, const void* host_record, dcb_result* result);
+/* The same without a pipeline or a GPU: terminal is a DCB_OP_*, out_type the element type that reached it. */
+dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, const void* host_record, dcb_result* result);
 
 /* The call a host-array user makes: inputs and output are HOST buffers (pinned for full speed). Copies go
  * through the chunked, double-buffered staging path overlapped with the kernels. Replaces the whole of
