@@ -84,9 +84,9 @@ class ClockSampler:
     def __init__(self, gpu_uuid: str | None):
         self.rows = []
         self.proc = None
-        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"]
+        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"]
         if gpu_uuid:
-            cmd += ["-i", gpu_uuid]
+            cmd += ["-i", gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid]
         try:
             self.proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
@@ -121,7 +121,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm),
+                "window": "0.7 s of the same steps run untimed immediately before, plus the timed region (50 ms sampling)"}
 
 
 def measured_peak_gbs():
@@ -243,8 +244,17 @@ def main() -> int:
         for _ in range(args.warmup):
             q.enqueue_reduce(N.OP_SUM, sh)
         barrier()
+        # The timed region lasts milliseconds, far less than nvidia-smi's sampling period. So the sampler starts here, the
+        # same step is repeated untimed for about 0.7 s (clocks settle under this load), and the timed region follows at
+        # once; the clock record covers that window up to the end of the timed region.
+        sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
+        spin_until = time.perf_counter() + 0.7
+        while time.perf_counter() < spin_until:
+            for _ in range(8):
+                q.enqueue_reduce(N.OP_SUM, sh)
+            stream.synchronize()
+        barrier()
         # ---- timed region: K steps, device-resident; events around the whole region and around every kernel
-        sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid) if rank == 0 else None) if rank == 0 else None
         k_start = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         k_stop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
