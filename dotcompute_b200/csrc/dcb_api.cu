@@ -21,6 +21,7 @@
 
 #include "../../include/dcb200.h"
 #include "dcb_builtin.h"
+#include "dcb_internal.h"
 #include "dcb_kernels.cuh"
 #include "dcb_translate.h"
 
@@ -267,6 +268,8 @@ dcb_status desc_to_ops(const dcb_pipeline_desc* desc, std::vector<dcbt::OpSpec>*
 }
 
 }  // namespace
+
+void dcb_set_thread_error(const char* msg) { snprintf(tl_error, sizeof tl_error, "%s", msg ? msg : ""); }
 
 // ============================================================================================ status
 extern "C" int32_t dcb_abi_version(void) { return DCB_ABI_VERSION; }

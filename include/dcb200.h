@@ -287,6 +287,32 @@ dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, const void* h
 dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
                                  void* host_out, int64_t host_out_cap, dcb_result* result);
 
+/* ------------------------------------------------------------- no device allocation */
+
+/* Tiles the fixed scratch of dcb_compact_noalloc holds. A tile is 4096 elements for 4-byte inputs and outputs
+ * (2048 for 8-byte ones), so float queries up to 2^28 elements fit. */
+#define DCB_NOALLOC_MAX_TILES 65536
+
+/* Stable Where [-> Select] -> ToArray for callers that must not allocate device memory. (No counterpart in the
+ * reference: its backend allocates per call.) Think of a host process that handed all of HBM to its own buffer pool
+ * at start-up, where a cudaMalloc from inside a native library fails or falsifies the pool's accounting, or of a
+ * latency-critical loop that cannot afford the implicit synchronisation of an allocation.
+ *
+ * This call allocates nothing: no cudaMalloc / cudaFree / pool allocation, no NVRTC, no module load. The look-back
+ * descriptors live in a fixed device array inside the library image (DCB_NOALLOC_MAX_TILES * 8 + 256 bytes, held by
+ * every GPU that loads the library until the process exits). Therefore:
+ *   - only queries of the precompiled table are accepted (others: DCB_ERR_NOT_SUPPORTED);
+ *   - n may not need more than DCB_NOALLOC_MAX_TILES tiles (else DCB_ERR_INVALID_ARGUMENT, text via dcb_last_error(NULL,..));
+ *   - all calls on one GPU share the array, which still holds the previous call's contents (the call clears what must
+ *     start at zero on `stream` itself); calls that overlap on the same GPU race and must be serialised by the caller;
+ *   - the first call on each device looks up the array's device address; make that first call outside any stream
+ *     capture.
+ * in0 / in1 / out / d_record are device pointers supplied by the caller; d_record receives DCB_DEVICE_RESULT_BYTES
+ * (survivor count in slot DCB_SLOT_COUNT, DCB_RES_* bits in slot DCB_SLOT_FLAGS). The call only enqueues work on `stream`
+ * (NULL = the default stream). There is no dcb_ctx: `device` is the CUDA device ordinal. */
+dcb_status dcb_compact_noalloc(int32_t device, const dcb_pipeline_desc* desc, const void* in0, const void* in1,
+                               int64_t n, void* out, int64_t out_cap, void* d_record, void* stream);
+
 /* ---------------------------------------------------------- [Kernel] source kernels */
 
 /* Compile CUDA C text produced by the [Kernel] generator and launch it. Replace
