@@ -292,3 +292,17 @@ def test_csharp_promotion_rules(acc):
     assert d.dtype == np.float64 and d.tolist() == [1.0, 2.0, 3.0]
     r = AsComputeQueryable(np.array([0.5, 1.5, 2.5, -0.5], dtype=np.float64), acc).Select("x => Math.Round(x)").ToArray()
     assert r.tolist() == [0.0, 2.0, 2.0, -0.0]                                                             # banker's rounding
+
+
+# --------------------------------------------------------------------------- every reference fixture, through the GPU
+from tests.fixture_util import check_expectation, fixture_input, load_fixtures  # noqa: E402
+
+
+@pytest.mark.parametrize("fx", load_fixtures(), ids=lambda f: f["name"])
+def test_reference_fixture_on_gpu(acc, fx):
+    q = AsComputeQueryable(fixture_input(fx), acc)
+    for op, arg in fx["ops"]:
+        q = getattr(q, op)(arg)
+    term = fx["terminal"]
+    got = getattr(q, term[0])(term[1]) if isinstance(term, list) else getattr(q, term)()
+    check_expectation(fx, got)
