@@ -37,6 +37,102 @@ SEED = 31
 BYTES_PER_ELEM = 4   # algorithmic: one float read per element, nothing written
 
 
+def _rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+# The other BASELINE configurations, measured kernel-only on one GPU (device-resident inputs). Each entry:
+# default log2(n), input generator(s), operators, terminal, algorithmic bytes per element as a function of selectivity.
+CONFIG_WORKLOADS = {
+    "c1-map": dict(log2n=20, gen=lambda n: [_rng(42).random(n, dtype=np.float32)], ops=[("S", "x => x * 2f + 1f")], term="ToArray",
+                   bytes=lambda s: 8.0, what="C1 Select(x*2f+1f).ToArray() f32"),
+    "c2-sum-f32": dict(log2n=24, gen=lambda n: [_rng(7).standard_normal(n, dtype=np.float32)], ops=[], term="Sum", bytes=lambda s: 4.0,
+                       what="C2 Sum f32"),
+    "c2-min-f32": dict(log2n=24, gen=lambda n: [_rng(7).standard_normal(n, dtype=np.float32)], ops=[], term="Min", bytes=lambda s: 4.0,
+                       what="C2 Min f32"),
+    "c2-avg-f32": dict(log2n=24, gen=lambda n: [_rng(7).standard_normal(n, dtype=np.float32)], ops=[], term="Average", bytes=lambda s: 4.0,
+                       what="C2 Average f32"),
+    "c2-sum-i32": dict(log2n=24, gen=lambda n: [_rng(8).integers(-1000, 1001, n, dtype=np.int32)], ops=[], term="Sum", bytes=lambda s: 4.0,
+                       what="C2 Sum i32"),
+    "c3-toarray-50": dict(log2n=26, gen=lambda n: [_rng(11).random(n, dtype=np.float32)], ops=[("W", "x => x > 0.5f"), ("S", "x => x * x + 3f")],
+                          term="ToArray", bytes=lambda s: 4.0 + 4.0 * s, what="C3 Where(x>0.5f).Select(x*x+3f).ToArray() f32"),
+    "c3-toarray-01": dict(log2n=26, gen=lambda n: [_rng(11).random(n, dtype=np.float32)], ops=[("W", "x => x > 0.99f"), ("S", "x => x * x + 3f")],
+                          term="ToArray", bytes=lambda s: 4.0 + 4.0 * s, what="C3 Where(x>0.99f)...ToArray() f32"),
+    "c3-toarray-99": dict(log2n=26, gen=lambda n: [_rng(11).random(n, dtype=np.float32)], ops=[("W", "x => x > 0.01f"), ("S", "x => x * x + 3f")],
+                          term="ToArray", bytes=lambda s: 4.0 + 4.0 * s, what="C3 Where(x>0.01f)...ToArray() f32"),
+    "c3-sum": dict(log2n=26, gen=lambda n: [_rng(11).random(n, dtype=np.float32)], ops=[("W", "x => x > 0.5f"), ("S", "x => x * x + 3f")],
+                   term="Sum", bytes=lambda s: 4.0, what="C3 Where(x>0.5f).Select(x*x+3f).Sum() f32"),
+    "headline-2p28": dict(log2n=28, gen=lambda n: [gen_shard(0, n)], ops=[("W", "x => x > 0.5f"), ("S", "x => x * x + 3f")],
+                          term="Sum", bytes=lambda s: 4.0, what="headline Where(x>0.5f).Select(x*x+3f).Sum() f32 2^28"),
+    "c4-zipdot": dict(log2n=28, gen=lambda n: [_rng(21).standard_normal(n, dtype=np.float32), _rng(22).standard_normal(n, dtype=np.float32)],
+                      ops=[("Z", "(x, y) => x * y")], term="Sum", bytes=lambda s: 8.0, what="C4 a.Zip(b,(x,y)=>x*y).Sum() f32"),
+    "c4-i64-where": dict(log2n=28, gen=lambda n: [_rng(23).integers(-2**63, 2**63 - 1, n, dtype=np.int64, endpoint=True)],
+                         ops=[("W", "k => (k & 0xF) == 3")], term="ToArray", bytes=lambda s: 8.0 + 8.0 * s,
+                         what="C4 keys.Where(k=>(k&0xF)==3).ToArray() i64"),
+}
+
+
+def run_config(args) -> int:
+    """One of the secondary configurations: K launches of its fused kernel on device-resident input, one JSON line."""
+    import torch
+    from dotcompute_b200 import CudaAccelerator, native as N
+    from dotcompute_b200.linq import CompiledPipeline
+    from dotcompute_b200.accelerator import dcb_type
+
+    spec = CONFIG_WORKLOADS[args.workload]
+    log2n = args.log2n if args.log2n != 30 else spec["log2n"]
+    n = 1 << log2n
+    acc = CudaAccelerator(0)
+    host = spec["gen"](n)
+    bufs = [acc.Memory.AllocateAndCopyAsync(h) for h in host]
+    kinds = {"S": N.OP_SELECT, "W": N.OP_WHERE, "Z": N.OP_ZIP}
+    terms = {"ToArray": N.OP_TOARRAY, "Sum": N.OP_SUM, "Min": N.OP_MIN, "Max": N.OP_MAX, "Average": N.OP_AVERAGE, "Count": N.OP_COUNT}
+    ops = tuple((kinds[k], lam) for k, lam in spec["ops"]) + ((terms[spec["term"]], None),)
+    pipe = CompiledPipeline(acc, dcb_type(host[0].dtype), dcb_type(host[1].dtype) if len(host) > 1 else 0, ops)
+    out = acc.Memory.AllocateAsync(n, pipe.out_dtype) if spec["term"] == "ToArray" else None
+    rec = acc.Memory.AllocateAsync(16, np.int64)
+    in0 = C.c_void_p(bufs[0].GetDeviceMemory())
+    in1 = C.c_void_p(bufs[1].GetDeviceMemory()) if len(bufs) > 1 else None
+    outp = C.c_void_p(out.GetDeviceMemory()) if out else None
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if n * host[0].itemsize < (256 << 20) else None
+
+    def step():
+        N.check(N.lib().dcb_pipeline_run_async(pipe.handle, in0, in1, n, outp, n if out else 0, C.c_void_p(rec.GetDeviceMemory()), None,
+                                               C.c_void_p(sh)), acc.handle)
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        l0 = acc.LaunchCount
+        times = []
+        for _ in range(args.steps):
+            if flush is not None:
+                flush.fill_(1)              # inputs smaller than L2 would otherwise be served from it
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); step(); b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        launches = acc.LaunchCount - l0
+    count = int(rec.ToArray()[N.SLOT_COUNT]) if spec["term"] in ("ToArray", "Count", "Average", "Min", "Max") else n
+    sel = count / n if spec["term"] == "ToArray" else 1.0
+    ms = statistics.median(times)
+    peak, kind = measured_peak_gbs()
+    gbs = n * spec["bytes"](sel) / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "kernel elements/s, device-resident (secondary configuration)", "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "ms_best": min(times), "higher_is_better": True,
+        "scaling": "n/a", "vs_baseline": None, "dtype": str(host[0].dtype), "data": "synthetic",
+        "config": {"workload": spec["what"], "n_elements": n, "selectivity": sel,
+                   "l2": "L2 flushed between launches (256 MiB write)" if flush is not None else "input larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_kind": kind, "bytes_per_element": spec["bytes"](sel)},
+        "gpu_launches": int(launches), "precompiled_kernel": bool(pipe.precompiled)}))
+    return 0
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -48,7 +144,14 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the result")
-    return ap.parse_args()
+    ap.add_argument("--profile", action="store_true",
+                    help="minimal run for a profiler: no clock spin, no e2e, no CPU baseline, no oracle check")
+    ap.add_argument("--workload", default="c5-sum", choices=sorted(CONFIG_WORKLOADS) + ["c5-sum"],
+                    help="c5-sum (default, the headline) or one of the other BASELINE configurations, 1 GPU, kernel-only")
+    args = ap.parse_args()
+    if args.profile:
+        args.no_e2e = args.no_cpu_baseline = args.no_check = True
+    return args
 
 
 def gen_shard(start: int, stop: int, out: np.ndarray | None = None) -> np.ndarray:
@@ -196,6 +299,8 @@ def main() -> int:
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload != "c5-sum":
+        return run_config(args)
 
     import torch
     import torch.distributed as dist
@@ -247,8 +352,8 @@ def main() -> int:
         # The timed region lasts milliseconds, far less than nvidia-smi's sampling period. So the sampler starts here, the
         # same step is repeated untimed for about 0.7 s (clocks settle under this load), and the timed region follows at
         # once; the clock record covers that window up to the end of the timed region.
-        sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if rank == 0 else None
-        spin_until = time.perf_counter() + 0.7
+        sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if (rank == 0 and not args.profile) else None
+        spin_until = time.perf_counter() + (0.0 if args.profile else 0.7)
         while time.perf_counter() < spin_until:
             for _ in range(8):
                 q.enqueue_reduce(N.OP_SUM, sh)
