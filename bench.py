@@ -144,6 +144,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the result")
+    ap.add_argument("--combine", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU exchange of partial sums: inside the reduce kernel over NVLink peer stores (fused) or an NCCL all-reduce")
     ap.add_argument("--profile", action="store_true",
                     help="minimal run for a profiler: no clock spin, no e2e, no CPU baseline, no oracle check")
     ap.add_argument("--workload", default="c5-sum", choices=sorted(CONFIG_WORKLOADS) + ["c5-sum"],
@@ -306,7 +308,7 @@ def main() -> int:
     import torch.distributed as dist
 
     from dotcompute_b200 import CudaAccelerator, native as N
-    from dotcompute_b200.sharded import ShardedQuery, finalize_record, shard_bounds, _stream_handle
+    from dotcompute_b200.sharded import ShardedQuery, connect_peers, finalize_record, shard_bounds, _stream_handle
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -333,6 +335,7 @@ def main() -> int:
     N.check(N.lib().dcb_h2d_async(acc.handle, dev.handle, 0, C.c_void_p(pinned.ptr), n_local * 4, None), acc.handle)
     acc.Synchronize()
 
+    fused = world > 1 and args.combine == "fused" and connect_peers(acc)
     ops = ((N.OP_WHERE, WHERE), (N.OP_SELECT, SELECT))
     q = ShardedQuery(acc, dev, ops)
     pipe = q.pipeline(N.OP_SUM)
@@ -353,8 +356,19 @@ def main() -> int:
         # same step is repeated untimed for about 0.7 s (clocks settle under this load), and the timed region follows at
         # once; the clock record covers that window up to the end of the timed region.
         sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid)) if (rank == 0 and not args.profile) else None
-        spin_until = time.perf_counter() + (0.0 if args.profile else 0.7)
-        while time.perf_counter() < spin_until:
+        # Every rank must run the SAME number of steps (each step ends in a collective), so the length of this untimed
+        # run is agreed on first: time one batch, take the slowest rank's figure, derive the count from it.
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(8):
+            q.enqueue_reduce(N.OP_SUM, sh)
+        e1.record(stream)
+        stream.synchronize()
+        bt = torch.tensor([max(e0.elapsed_time(e1), 1e-3)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+        n_batches = 0 if args.profile else int(min(max(700.0 / float(bt[0]), 1), 2000))
+        for _ in range(n_batches):
             for _ in range(8):
                 q.enqueue_reduce(N.OP_SUM, sh)
             stream.synchronize()
@@ -374,7 +388,8 @@ def main() -> int:
             k_start[i].record(stream)
             N.check(N.lib().dcb_pipeline_run_async(pipe.handle, in0, None, n_local, None, 0, recp, None, C.c_void_p(sh)), acc.handle)
             k_stop[i].record(stream)
-            combine_record(rec, N.OP_SUM, out_type)
+            if not fused:
+                combine_record(rec, N.OP_SUM, out_type)
         t_end.record(stream)
         barrier()
         launches = acc.LaunchCount - launches0
@@ -449,7 +464,9 @@ def main() -> int:
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"C5: Where(x>0.5f).Select(x*x+3f).Sum() over 2^{args.log2n} float32 uniform[0,1) seed 31, contiguous shards",
                        "n_elements": n_total, "elements_per_gpu": n_local, "l2": "inputs larger than L2 (shard >= 512 MiB)",
-                       "combine": "NCCL all-reduce of one fp64 partial per GPU" if world > 1 else "none (1 GPU)",
+                       "combine": ("none (1 GPU)" if world == 1 else
+                                   "fused: the reduce kernel's last block exchanges fp64 partials over NVLink peer stores" if fused else
+                                   "NCCL all-reduce of one fp64 partial per GPU"),
                        "precompiled_kernel": bool(pipe.precompiled)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_kind": peak_kind, "kernel": "dcb_reduce_vec (fused Where->Select->Sum)",

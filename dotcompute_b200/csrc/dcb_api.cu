@@ -40,7 +40,7 @@ thread_local char tl_error[1024] = "";
 
 struct Scratch {
     dcb::Partial* partials = nullptr;
-    unsigned int* words = nullptr;      // [0] reduce ticket, [1] compaction tile counter, [2] abort flag
+    unsigned int* words = nullptr;      // 512 bytes: [0] reduce ticket, [64] compaction abort flag (separate 128-byte lines)
     unsigned long long* desc = nullptr; // look-back descriptors
     size_t desc_cap = 0;
     unsigned int epoch = 0;
@@ -55,6 +55,7 @@ struct dcb_ctx {
     cudaStream_t own_stream = nullptr, stream = nullptr, copy_stream = nullptr, out_stream = nullptr;
     cudaMemPool_t pool = nullptr;
     uint32_t spin_limit = 1u << 22;
+    uint32_t peer_spin_limit = 1u << 20;   // polls of one wait for a peer's partial (about a second with the back-off)
     char err[1024] = "";
     std::mutex mu;
     std::map<std::string, dcb_pipeline*> cache;
@@ -64,6 +65,10 @@ struct dcb_ctx {
     void* stage_out = nullptr;
     size_t stage_out_cap = 0;
     bool alive = true;
+    // exchange of partials between GPUs (see PeerTable in dcb_kernels.cuh)
+    dcb::PeerTable peers = {};
+    void* peer_area = nullptr;             // this GPU's exchange area (cudaMalloc, exported over CUDA IPC)
+    std::vector<void*> peer_opened;        // areas of other ranks opened here
 };
 
 struct dcb_buf {
@@ -84,6 +89,8 @@ struct dcb_pipeline {
     int unroll = 4;
     int occ_vec = 1, occ_scalar = 1;     // resident blocks per SM
     int rows_vec = 1, rows_scalar = 1;   // compaction rows per warp
+    int jit_rows = 0;                    // rows forced by a tuning experiment (0 = automatic)
+    int compact_block = 256;             // threads per block of the compaction kernels
     Scratch sc;
     dcb::DeviceResult* d_result = nullptr;
     void* h_record = nullptr;            // pinned, DCB_DEVICE_RESULT_BYTES * kMaxChunks
@@ -162,19 +169,15 @@ __global__ void fill_kernel(unsigned char* dst, size_t count, unsigned long long
 // Bytes a pointer must be aligned to for the vector variant: one pack of E elements, at most 16.
 size_t pack_align(int elems, int type) { return (size_t)std::min(16, elems * dcbt::type_size(type)); }
 
-int compact_rows(int block, int elems, int out_type) {
-    const int per_row = block * elems * dcbt::type_size(out_type);
-    const int fit = 32768 / per_row;
-    return fit < 1 ? 1 : (fit > 4 ? 4 : fit);
-}
+int compact_rows(int block, int elems, int out_type) { return dcb::compact_rows_for(block, elems, dcbt::type_size(out_type)); }
 
 dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
     dcb_ctx* ctx = p->ctx;
     Scratch& sc = p->sc;
     if (!sc.partials) {
         CU(ctx, cudaMalloc(&sc.partials, sizeof(dcb::Partial) * kMaxPartials));
-        CU(ctx, cudaMalloc(&sc.words, 64));
-        CU(ctx, cudaMemset(sc.words, 0, 64));
+        CU(ctx, cudaMalloc(&sc.words, 512));
+        CU(ctx, cudaMemset(sc.words, 0, 512));
     }
     if ((size_t)num_tiles > sc.desc_cap) {
         size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
@@ -189,15 +192,32 @@ dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
 }
 
 dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
-    const int unroll = env_int("DCB200_UNROLL", 4);
-    p->unroll = unroll;
-    p->source = dcbt::build_program(p->info, "", kKernelsHeaderText, kBlock, unroll, true);
+    dcbt::Tuning tuning;   // the defaults, unless a tuning experiment overrides them through the environment
+    tuning.unroll = env_int("DCB200_UNROLL", tuning.unroll);
+    tuning.compact_block = env_int("DCB200_COMPACT_BLOCK", tuning.compact_block);
+    tuning.compact_rows = env_int("DCB200_COMPACT_ROWS", 0);
+    tuning.compact_min_blocks = env_int("DCB200_COMPACT_MINBLOCKS", tuning.compact_min_blocks);
+    p->compact_block = tuning.compact_block;
+    p->unroll = tuning.unroll;
+    p->jit_rows = tuning.compact_rows;
+    p->source = dcbt::build_program(p->info, "", kKernelsHeaderText, tuning, true);
     nvrtcProgram prog = nullptr;
     if (nvrtcCreateProgram(&prog, p->source.c_str(), "dcb_pipeline.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
         return set_err(ctx, DCB_ERR_COMPILE, "nvrtcCreateProgram failed");
     // No --use_fast_math and no FMA contraction: a Select must round exactly like the C# lambda does.
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-fmad=false", "-lineinfo"};
-    nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+    // Extra options for tuning experiments, space separated (the counterpart of CompilationOptions.AdditionalFlags,
+    // consumed by the reference at src/Backends/DotCompute.Backends.CUDA/Compilation/PTXCompiler.cs:251-270).
+    std::vector<std::string> extra;
+    if (const char* ev = getenv("DCB200_NVRTC_FLAGS")) {
+        std::string cur;
+        for (const char* c = ev;; ++c) {
+            if (*c == ' ' || *c == '\0') { if (!cur.empty()) extra.push_back(cur); cur.clear(); if (!*c) break; }
+            else cur += *c;
+        }
+    }
+    std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-fmad=false", "-lineinfo"};
+    for (const auto& e : extra) opts.push_back(e.c_str());
+    nvrtcResult r = nvrtcCompileProgram(prog, (int)opts.size(), opts.data());
     if (r != NVRTC_SUCCESS) {
         size_t n = 0;
         nvrtcGetProgramLogSize(prog, &n);
@@ -223,12 +243,13 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
 
 dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
     const int e_vec = 16 / dcbt::type_size(p->info.in0);
-    p->rows_vec = compact_rows(kBlock, e_vec, p->info.out_type);
-    p->rows_scalar = compact_rows(kBlock, 1, p->info.out_type);
+    p->rows_vec = p->jit_rows > 0 ? p->jit_rows : compact_rows(p->compact_block, e_vec, p->info.out_type);
+    p->rows_scalar = p->jit_rows > 0 ? p->jit_rows : compact_rows(p->compact_block, 1, p->info.out_type);
+    const int blk = (p->info.terminal == DCB_OP_TOARRAY && p->info.has_filter) ? p->compact_block : kBlock;
     int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_vec, kBlock, 0) == cudaSuccess && occ > 0) p->occ_vec = occ;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_vec, blk, 0) == cudaSuccess && occ > 0) p->occ_vec = occ;
     else { (void)cudaGetLastError(); p->occ_vec = 4; }
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_scalar, kBlock, 0) == cudaSuccess && occ > 0) p->occ_scalar = occ;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_scalar, blk, 0) == cudaSuccess && occ > 0) p->occ_scalar = occ;
     else { (void)cudaGetLastError(); p->occ_scalar = 4; }
     const int cap = env_int("DCB200_BLOCKS_PER_SM", 0);
     if (cap > 0) { p->occ_vec = std::min(p->occ_vec, cap); p->occ_scalar = std::min(p->occ_scalar, cap); }
@@ -359,6 +380,8 @@ extern "C" dcb_status dcb_shutdown(dcb_ctx* ctx) {
     cudaDeviceSynchronize();
     for (auto& kv : ctx->cache) free_pipeline(kv.second);
     ctx->cache.clear();
+    for (void* p : ctx->peer_opened) cudaIpcCloseMemHandle(p);
+    if (ctx->peer_area) cudaFree(ctx->peer_area);
     for (int i = 0; i < 2; ++i) if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
     if (ctx->stage_out) cudaFree(ctx->stage_out);
     cudaStreamDestroy(ctx->own_stream);
@@ -603,7 +626,7 @@ extern "C" dcb_status dcb_pipeline_generate_source(const dcb_pipeline_desc* desc
         if (err && err_cap) snprintf(err, err_cap, "%s", e);
         return set_err(nullptr, st, "%s", e);
     }
-    std::string src = dcbt::build_program(info, "", "", kBlock, 4, true);
+    std::string src = dcbt::build_program(info, "", "", dcbt::Tuning(), true);
     if (needed) *needed = src.size() + 1;
     if (buf && cap) { snprintf(buf, cap, "%s", src.c_str()); }
     return DCB_OK;
@@ -641,7 +664,8 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->k_vec = b->k_vec;
         p->k_scalar = b->k_scalar;
         p->unroll = b->unroll;
-        p->source = dcbt::build_program(info, "", "", kBlock, b->unroll, true);
+        p->compact_block = b->compact_block;
+        p->source.clear();
     } else if ((st = load_jit(ctx, p)) != DCB_OK) {
         free_pipeline(p);
         return st;
@@ -670,7 +694,7 @@ extern "C" dcb_status dcb_pipeline_info_get(const dcb_pipeline* p, dcb_pipeline_
     out->n_inputs = p->info.n_in;
     out->precompiled = p->precompiled ? 1 : 0;
     out->tile_elems = (p->info.terminal == DCB_OP_TOARRAY && p->info.has_filter)
-                          ? (int64_t)(kBlock / 32) * p->rows_vec * 32 * (16 / dcbt::type_size(p->info.in0)) : 0;
+                          ? (int64_t)(p->compact_block / 32) * p->rows_vec * 32 * (16 / dcbt::type_size(p->info.in0)) : 0;
     out->compile_ms = p->compile_ms;
     return DCB_OK;
 }
@@ -678,7 +702,11 @@ extern "C" dcb_status dcb_pipeline_info_get(const dcb_pipeline* p, dcb_pipeline_
 extern "C" dcb_status dcb_pipeline_source(const dcb_pipeline* p, char* buf, size_t cap, size_t* needed) {
     if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
     // Only the generated part is returned (chain + kernel entry points), not the template header in front of it.
-    const std::string src = dcbt::build_program(p->info, "", "", kBlock, p->unroll, true);
+    dcbt::Tuning tuning;
+    tuning.unroll = p->unroll;
+    tuning.compact_rows = p->jit_rows;
+    tuning.compact_block = p->compact_block;
+    const std::string src = dcbt::build_program(p->info, "", "", tuning, true);
     if (needed) *needed = src.size() + 1;
     if (buf && cap) snprintf(buf, cap, "%s", src.c_str());
     return DCB_OK;
@@ -689,8 +717,8 @@ namespace {
 
 bool aligned_to(const void* p, size_t a) { return a <= 1 || ((uintptr_t)p % a) == 0; }
 
-dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cudaStream_t s) {
-    CU(ctx, cudaLaunchKernel(fn, dim3(grid), dim3(kBlock), args, 0, s));
+dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cudaStream_t s, int block = kBlock) {
+    CU(ctx, cudaLaunchKernel(fn, dim3(grid), dim3(block), args, 0, s));
     ctx->launches += 1;
     return DCB_OK;
 }
@@ -730,7 +758,7 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
     }
     if (to_array) {
         const int rows = vec ? p->rows_vec : p->rows_scalar;
-        const int64_t tile = (int64_t)(kBlock / 32) * rows * 32 * E;
+        const int64_t tile = (int64_t)(p->compact_block / 32) * rows * 32 * E;
         long long num_tiles = (n + tile - 1) / tile;
         if (num_tiles == 0) {
             // Nothing to scan: the record is the previous one (or zero).
@@ -745,17 +773,16 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         sc.epoch += 1;
         if (sc.epoch >= 0x3fffu) {   // epoch field is 14 bits: wipe the descriptors before reusing a value
             CU(ctx, cudaMemsetAsync(sc.desc, 0, sc.desc_cap * sizeof(unsigned long long), s));
-            CU(ctx, cudaMemsetAsync(sc.words, 0, 64, s));
+            CU(ctx, cudaMemsetAsync(sc.words, 0, 512, s));
             sc.epoch = 1;
         }
         unsigned int epoch = sc.epoch, spin = ctx->spin_limit;
-        unsigned int* counter = sc.words + 1;
-        unsigned int* abort_flag = sc.words + 2;
+        unsigned int* abort_flag = sc.words + 64;
         long long cap = out_cap;
-        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&counter,
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc,
                         (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag};
         if (launches) *launches += 1;
-        return launch(ctx, fn, (unsigned)num_tiles, args, s);
+        return launch(ctx, fn, (unsigned)num_tiles, args, s, p->compact_block);   // one tile per block, ids in dispatch order
     }
     // reductions
     {
@@ -767,7 +794,12 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         max_grid = std::min<int64_t>(max_grid, kMaxPartials);
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
         unsigned int* ticket = p->sc.words;
-        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res};
+        dcb::PeerTable peers = ctx->peers;            // world <= 1 unless dcb_peer_connect() was called
+        if (peers.world > 1) {
+            ctx->peers.seq += 1;                      // every rank runs the same sequence of sharded reductions
+            peers.seq = ctx->peers.seq;
+        }
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res, (void*)&peers};
         if (launches) *launches += 1;
         return launch(ctx, fn, grid, args, s);
     }
@@ -1016,6 +1048,55 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     result->launches = launches; result->total_ms = ms; result->kernel_ms = 0;
     if (plain_map) { result->count = n; return DCB_OK; }
     return dcb_result_finalize(p, &total, result);
+}
+
+// ===================================================================================== peer exchange
+extern "C" dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_t handle_cap) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, handle_out != nullptr && handle_cap >= sizeof(cudaIpcMemHandle_t), "handle buffer must hold 64 bytes");
+    if (!ctx->peer_area) {
+        const size_t bytes = sizeof(dcb::PeerSlot) * 2 * dcb::PEER_MAX;
+        CU(ctx, cudaMalloc(&ctx->peer_area, bytes));
+        CU(ctx, cudaMemset(ctx->peer_area, 0, bytes));
+        CU(ctx, cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t h;
+    CU(ctx, cudaIpcGetMemHandle(&h, ctx->peer_area));
+    memcpy(handle_out, &h, sizeof h);
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank, const void* handles, size_t handle_stride) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, world >= 1 && world <= dcb::PEER_MAX, "world must be between 1 and 8");
+    NEED(ctx, rank >= 0 && rank < world, "rank outside the world");
+    NEED(ctx, ctx->peer_area != nullptr, "call dcb_peer_area_create first");
+    NEED(ctx, handles != nullptr && handle_stride >= sizeof(cudaIpcMemHandle_t), "bad handle table");
+    dcb::PeerTable t = {};
+    t.world = world; t.rank = rank; t.seq = 0; t.spin_limit = ctx->peer_spin_limit;
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) { t.area[r] = (dcb::PeerSlot*)ctx->peer_area; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)r * handle_stride, sizeof h);
+        void* p = nullptr;
+        CU(ctx, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        ctx->peer_opened.push_back(p);
+        t.area[r] = (dcb::PeerSlot*)p;
+    }
+    ctx->peers = t;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_peer_disconnect(dcb_ctx* ctx) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    CU(ctx, cudaDeviceSynchronize());
+    for (void* p : ctx->peer_opened) cudaIpcCloseMemHandle(p);
+    ctx->peer_opened.clear();
+    ctx->peers = {};
+    return DCB_OK;
 }
 
 // ============================================================================== [Kernel] source kernels

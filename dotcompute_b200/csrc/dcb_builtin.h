@@ -8,6 +8,7 @@ struct dcb_builtin_entry {
     const void* k_vec;      // kernel taking 16-byte aligned pointers
     const void* k_scalar;   // kernel for any alignment
     int unroll;             // packs per thread per tile the kernels were built with
+    int compact_block;      // threads per block of the compaction kernels
 };
 
 const dcb_builtin_entry* dcb_builtin_find(const char* key);

@@ -326,17 +326,44 @@ __device__ __forceinline__ void map_body(const typename C::in0_t* __restrict__ i
     }
 }
 
+// ------------------------------------------------------------------ exchange of partials between GPUs
+// A sharded reduction ends with every GPU holding the total. Instead of a separate collective launch, the last block
+// of the reduce kernel stores this GPU's partial straight into an exchange area in every peer's memory (plain NVLink
+// peer stores), then waits - with a bounded poll - for the peers' partials to land in its own area and folds them in
+// rank order, so all GPUs compute bit-identical totals. Slots are double-buffered by the parity of a launch sequence
+// number; a slot is valid when its stamp equals that number.
+struct __align__(16) PeerSlot {   // 64 bytes
+    double fsum; u64 isum_lo; i64 isum_hi; i64 count; i64 mn_bits; i64 mx_bits; u64 flags; u64 stamp;
+};
+enum : int { PEER_MAX = 8 };
+struct PeerTable {                // passed by value as a kernel parameter; world <= 1 means "no exchange"
+    int world, rank;
+    u64 seq;                      // launch sequence number, the same on every rank, never 0
+    u32 spin_limit, pad;
+    PeerSlot* area[PEER_MAX];     // area[r]: base of rank r's exchange area = PeerSlot[2][PEER_MAX], peer-mapped
+};
+__device__ __forceinline__ void st_release_sys(u64* p, u64 v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ u64 ld_acquire_sys(const u64* p) {
+    u64 v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------ reduce: chain + Sum/Min/Max/Count in one read
 // Persistent grid. Each block leaves its partial in slot blockIdx.x; the block that takes the last
 // ticket combines the slots in index order. Nothing depends on which block finishes first.
 template <class C, int RED, int BLOCK, int UNROLL, bool VEC>
 __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
                                             i64 n, Partial* __restrict__ partials, unsigned int* __restrict__ ticket,
-                                            DeviceResult* __restrict__ res) {
+                                            DeviceResult* __restrict__ res, const PeerTable& peers) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     constexpr int E = pack_elems<C, VEC>::value;
     __shared__ Partial s_part[BLOCK / 32];
     __shared__ bool s_last;
+    __shared__ PeerSlot s_peer[PEER_MAX];
+    __shared__ int s_peer_failed;
 
     Acc<O, RED> acc; acc.init();
     const i64 nitems = n / E;
@@ -398,8 +425,56 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         tot.merge(o);
     }
     tot = block_reduce<O, RED, BLOCK>(tot, s_part);
+    u32 extra_flags = 0;
+    if (peers.world > 1) {
+        // Exchange with the other GPUs: thread r < world serves peer r.
+        const int par = (int)(peers.seq & 1ull);
+        if (threadIdx.x == 0) s_peer_failed = 0;
+        __syncthreads();
+        if (threadIdx.x < peers.world) {
+            const int r = threadIdx.x;
+            Partial mine; tot.to_partial(mine);                  // warp 0 holds the block total in every lane
+            PeerSlot* dst = peers.area[r] + par * PEER_MAX + peers.rank;
+            volatile PeerSlot* vd = dst;
+            vd->fsum = mine.fsum; vd->isum_lo = mine.isum_lo; vd->isum_hi = mine.isum_hi; vd->count = mine.count;
+            vd->mn_bits = mine.mn_bits; vd->mx_bits = mine.mx_bits; vd->flags = (u64)mine.flags;
+            __threadfence_system();
+            st_release_sys(&dst->stamp, peers.seq);
+            // wait for rank r's partial in my own area (bounded)
+            const PeerSlot* src = peers.area[peers.rank] + par * PEER_MAX + r;
+            u32 polls = 0; bool ok = true;
+            while (ld_acquire_sys(&src->stamp) != peers.seq) {
+                if (++polls > peers.spin_limit) { ok = false; break; }
+                if (polls > 256) __nanosleep(polls > 65536 ? 1000 : 100);
+            }
+            if (ok) {
+                const volatile PeerSlot* vs = src;
+                s_peer[r].fsum = vs->fsum; s_peer[r].isum_lo = vs->isum_lo; s_peer[r].isum_hi = vs->isum_hi; s_peer[r].count = vs->count;
+                s_peer[r].mn_bits = vs->mn_bits; s_peer[r].mx_bits = vs->mx_bits; s_peer[r].flags = vs->flags;
+            } else {
+                atomicExch(&s_peer_failed, 1);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (s_peer_failed) {
+                extra_flags = FLAG_TIMEOUT;                      // a peer never showed up: report, do not hang
+            } else {
+                Acc<O, RED> g; g.init();
+                for (int r = 0; r < peers.world; ++r) {          // rank order: the same sum on every GPU
+                    Partial p;
+                    p.fsum = s_peer[r].fsum; p.isum_lo = s_peer[r].isum_lo; p.isum_hi = s_peer[r].isum_hi; p.count = s_peer[r].count;
+                    p.mn_bits = s_peer[r].mn_bits; p.mx_bits = s_peer[r].mx_bits; p.flags = (u32)s_peer[r].flags; p.pad0 = 0; p.pad1 = 0;
+                    Acc<O, RED> o; o.from_partial(p);
+                    if (r == 0) g = o; else g.merge(o);
+                }
+                tot = g;
+            }
+        }
+    }
     if (threadIdx.x == 0) {
         Partial p; tot.to_partial(p);
+        p.flags |= extra_flags;
         res->fsum = p.fsum; res->count_f = (double)p.count;
         res->isum_lo = (i64)p.isum_lo; res->isum_hi = (sizeof(O) == 8) ? p.isum_hi : ((i64)p.isum_lo < 0 ? -1 : 0);
         res->count = p.count;
@@ -431,20 +506,27 @@ __device__ __forceinline__ u32 desc_status(u64 d, u32 epoch) {
     return ((u32)(d >> 50) & 0x3fffu) == (epoch & 0x3fffu) ? (u32)((d >> 48) & 3u) : (u32)ST_INVALID;
 }
 
-// Rows per warp: as many as keep the staging tile within 32 KB of shared memory, at most 4 (64 bytes in flight per thread).
+// Compaction tile shape: 256 threads, 8 rows per warp (128 bytes in flight per thread), fewer rows if the staging tile
+// would exceed 32 KB of shared memory; four such blocks share an SM. Of the shapes measured on B200 (128 / 256 threads,
+// 2 / 4 / 8 rows, 4 to 16 resident blocks) this one was fastest. One definition for device templates and host launch code.
+__host__ __device__ constexpr int compact_rows_for(int block, int elems_per_pack, int out_bytes) {
+    return 32768 / (block * elems_per_pack * out_bytes) < 1 ? 1
+         : (32768 / (block * elems_per_pack * out_bytes) > 8 ? 8 : 32768 / (block * elems_per_pack * out_bytes));
+}
 template <class C, int BLOCK, bool VEC> struct compact_rows {
-    static constexpr int per_row = BLOCK * pack_elems<C, VEC>::value * (int)sizeof(typename C::out_t);
-    static constexpr int fit = 32768 / per_row;
-    static constexpr int value = fit < 1 ? 1 : (fit > 4 ? 4 : fit);
+    static constexpr int value = compact_rows_for(BLOCK, pack_elems<C, VEC>::value, (int)sizeof(typename C::out_t));
 };
 
-// Tile = BLOCK threads, each warp owns ROWS rows of 32 packs (a contiguous run of ROWS*32*E elements).
-// Element order inside a warp's run is row, then lane, then position in the pack; ranks follow it.
+// Tile = BLOCK threads; each warp owns ROWS rows of 32 packs, a contiguous run of ROWS*32*E elements. Element order
+// inside a warp's run is row, then lane, then position in the pack; ranks follow it, so the output keeps source order.
+//
+// One tile per block, tile id = blockIdx.x. The look-back waits on tiles with smaller ids, i.e. on blocks the hardware
+// dispatched earlier (a 1-D grid is dispatched in index order; NVIDIA's own single-pass scan relies on the same). Should
+// that ever not hold, the bounded polls below end the launch with FLAG_TIMEOUT instead of hanging the GPU.
 template <class C, int BLOCK, int ROWS, bool VEC>
 __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
                                              i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
-                                             u64* __restrict__ desc, unsigned int* __restrict__ tile_counter,
-                                             u32 epoch, u32 spin_limit, i64 num_tiles,
+                                             u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
                                              const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
                                              unsigned int* __restrict__ abort_flag) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
@@ -452,26 +534,44 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
     constexpr int WARPS = BLOCK / 32;
     constexpr int WARP_ELEMS = ROWS * 32 * E;
     constexpr int TILE = WARPS * WARP_ELEMS;
+    // Per-row survivor counts of a lane are packed FIELD bits apiece into 32-bit words, so one shuffle scan ranks
+    // several rows at once. A row total is at most 32*E, which fits 8 bits up to E = 4 (128 = 0x80), else 16.
+    constexpr int FIELD = (32 * E <= 128) ? 8 : 16;
+    constexpr int PER_WORD = 32 / FIELD;
+    constexpr int WORDS = (ROWS + PER_WORD - 1) / PER_WORD;
+    constexpr u32 FMASK = (FIELD == 8) ? 0xffu : 0xffffu;
 
-    __shared__ O s_stage[TILE];
+    __shared__ O s_stage[TILE];           // warp w stages its survivors, compacted, at [w*WARP_ELEMS, ...)
     __shared__ int s_warp_tot[WARPS];
-    __shared__ i64 s_tile_prefix;
-    __shared__ i64 s_tile;
+    __shared__ i64 s_prefix;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        const unsigned int t = atomicAdd(tile_counter, 1u);   // ids in arrival order: a tile's predecessors already run
-        if ((i64)t == num_tiles - 1) *tile_counter = 0;       // every other tile has drawn its id by now
-        s_tile = (i64)t;
-    }
-    __syncthreads();
-    const i64 tile = s_tile;
+    const i64 tile = blockIdx.x;
     const i64 tile_base = tile * TILE;
     const i64 warp_base = tile_base + (i64)warp * WARP_ELEMS;
-
-    // 1. loads
-    Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
     const bool full = tile_base + TILE <= n;
+
+    // 0. Pull a tile far ahead of this one into L2. A tile's look-back cannot finish before every earlier tile has
+    //    counted its survivors, so one slow HBM access holds up all tiles behind it; with the input already in L2 the
+    //    loads of all tiles take about the same, short time (measured: 8 % faster at 8 MB ahead, no gain beyond).
+#ifndef DCB_COMPACT_AHEAD_BYTES
+#define DCB_COMPACT_AHEAD_BYTES (8 << 20)
+#endif
+    if (DCB_COMPACT_AHEAD_BYTES > 0) {
+        const i64 ahead = tile + (i64)(DCB_COMPACT_AHEAD_BYTES) / (i64)(TILE * sizeof(A)) + 1;
+        if ((ahead + 1) * TILE <= n) {
+            const char* p0 = reinterpret_cast<const char*>(in0 + ahead * TILE);
+            for (int l = threadIdx.x; l < (int)(TILE * sizeof(A) / 128); l += BLOCK)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + (i64)l * 128));
+            if constexpr (C::n_in == 2) {
+                const char* p1 = reinterpret_cast<const char*>(in1 + ahead * TILE);
+                for (int l = threadIdx.x; l < (int)(TILE * sizeof(B) / 128); l += BLOCK)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + (i64)l * 128));
+            }
+        }
+    }
+    // 1. loads: all rows of the thread are in flight before the first is used
+    Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
     if (full) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
@@ -496,31 +596,61 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
         }
     }
 
-    // 2. chain + ranks inside the warp (ballot / popc)
+    // 2. chain, per-lane survivor bits and counts
     O val[ROWS][E];
-    u64 keepbits = 0;                      // bit r*E+k
-    int rank[ROWS];                        // rank of this lane's first survivor in row r, within the warp run
-    int warp_run = 0;
-    const unsigned int lt_mask = (1u << lane) - 1u;
+    u32 keepbits[ROWS];
+    u32 packed[WORDS];
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) packed[w] = 0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        int before = 0, row_total = 0;
+        u32 bits = 0;
 #pragma unroll
         for (int k = 0; k < E; ++k) {
             bool keep;
             if constexpr (C::n_in == 2) keep = C::apply(a[r].e[k], b[r].e[k], val[r][k]);
             else keep = C::apply(a[r].e[k], B(), val[r][k]);
             if (!full) keep = keep && (warp_base + ((i64)r * 32 + lane) * E + k < n);
-            const unsigned int bal = __ballot_sync(0xffffffffu, keep);
-            before += __popc(bal & lt_mask);
-            row_total += __popc(bal);
-            keepbits |= (u64)(keep ? 1u : 0u) << (r * E + k);
+            bits |= (keep ? 1u : 0u) << k;
         }
-        rank[r] = warp_run + before;
-        warp_run += row_total;
+        keepbits[r] = bits;
+        packed[r / PER_WORD] |= (u32)__popc(bits) << ((r % PER_WORD) * FIELD);
     }
+    // 3. ranks: inclusive scan of the packed counts across the warp (fields cannot carry into each other)
+    u32 incl[WORDS];
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) {
+        u32 v = packed[w];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += t;
+        }
+        incl[w] = v;
+    }
+    int row_start = 0;
+    int rank[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int w = r / PER_WORD, sh = (r % PER_WORD) * FIELD;
+        const u32 tot_word = __shfl_sync(0xffffffffu, incl[w], 31);
+        const int before = (int)(((incl[w] - packed[w]) >> sh) & FMASK);
+        rank[r] = row_start + before;
+        row_start += (int)((tot_word >> sh) & FMASK);
+    }
+    const int warp_run = row_start;
     if (lane == 0) s_warp_tot[warp] = warp_run;
-    __syncthreads();
+    // 4. stage the survivors, compacted, in the warp's run
+    O* stage = s_stage + warp * WARP_ELEMS;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        int pos = rank[r];
+#pragma unroll
+        for (int k = 0; k < E; ++k) {
+            if ((keepbits[r] >> k) & 1u) { stage[pos] = val[r][k]; ++pos; }
+        }
+    }
+    __syncthreads();                                       // warp totals and staged runs are visible
     int warp_off = 0, tile_total = 0;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
@@ -529,76 +659,87 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
         tile_total += t;
     }
 
-    // 3. publish the aggregate, stage survivors, and let warp 0 look back meanwhile
-    if (threadIdx.x == 0) {
+    // 5. publish the aggregate, look back
+    if (warp == 0) {
         if (tile == 0) {
-            const i64 base0 = prev ? prev->count : 0;
-            desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)tile_total));
-            s_tile_prefix = base0;
+            if (lane == 0) {
+                desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)tile_total));
+                s_prefix = prev ? prev->count : 0;
+            }
         } else {
-            desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tile_total));
-        }
-    }
+            if (lane == 0) desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tile_total));
+            // One step inspects LOOK_WIN*32 predecessors, nearest first: sub-window j holds tiles look-32j-lane. All loads
+            // of a step are issued before the first is examined. The walk stops at the nearest tile whose inclusive
+            // prefix is known. Every poll loop is bounded.
+            constexpr int LOOK_WIN = 2;
+            i64 exclusive = 0;
+            i64 look = tile - 1;
+            bool failed = false, done = false;
+            while (!done && !failed) {
+
+                u64 d[LOOK_WIN];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        int pos = warp_off + rank[r];
+                for (int j = 0; j < LOOK_WIN; ++j) {
+                    const i64 idx = look - (i64)j * 32 - lane;
+                    d[j] = idx >= 0 ? desc_load(desc + idx) : desc_make(epoch, ST_INCLUSIVE, 0);   // before tile 0: empty, inclusive
+                }
 #pragma unroll
-        for (int k = 0; k < E; ++k) {
-            if ((keepbits >> (r * E + k)) & 1ull) { s_stage[pos] = val[r][k]; ++pos; }
-        }
-    }
-    if (warp == 0 && tile > 0) {
-        // Each lane inspects one predecessor; the window slides back 32 tiles at a time until a
-        // tile with an inclusive prefix is met.
-        i64 exclusive = 0;
-        i64 look = tile - 1;
-        bool failed = false;
-        while (true) {
-            const i64 idx = look - lane;
-            u64 d = 0; u32 st = ST_INCLUSIVE;
-            if (idx >= 0) {
-                u32 polls = 0;
-                d = desc_load(desc + idx);
-                st = desc_status(d, epoch);
-                while (st == ST_INVALID) {
-                    if (++polls > spin_limit || *(volatile unsigned int*)abort_flag == epoch) { failed = true; break; }
-                    if (polls > 16) __nanosleep(polls > 1024 ? 256 : 32);
-                    d = desc_load(desc + idx);
-                    st = desc_status(d, epoch);
+                for (int j = 0; j < LOOK_WIN; ++j) {
+                    if (done || failed) break;
+                    const i64 idx = look - (i64)j * 32 - lane;
+                    u32 st = desc_status(d[j], epoch);
+                    u32 polls = 0;
+                    while (st == ST_INVALID) {
+                        // the abort word is looked at every 16th poll only: every poller shares its L2 path
+                        if (++polls > spin_limit || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
+                        // Back off before asking again: a poll is an L2 round trip, and hundreds of warps share these lines.
+#ifndef DCB_POLL_SLEEP_NS
+#define DCB_POLL_SLEEP_NS 200
+#endif
+                        __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
+
+                        d[j] = desc_load(desc + idx);
+                        st = desc_status(d[j], epoch);
+                    }
+                    if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
+                    const unsigned int inc = __ballot_sync(0xffffffffu, st == ST_INCLUSIVE);
+                    const int first = inc ? (__ffs(inc) - 1) : 32;
+                    if (lane <= first) exclusive += (i64)(d[j] & DESC_VALUE_MASK);
+                    if (inc) done = true;
+                }
+                look -= 32 * LOOK_WIN;
+            }
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) exclusive += __shfl_xor_sync(0xffffffffu, exclusive, m);
+            if (lane == 0) {
+                if (failed) {
+                    // A wait ran out (or another tile's did). Tell the tiles still waiting, and leave a record that says
+                    // so; every tile after the stuck one ends here too, so the last tile cannot overwrite it with success.
+                    atomicExch(abort_flag, epoch);
+                    res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT;
+                    s_prefix = -1;
+                } else {
+                    desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)(exclusive + tile_total)));
+                    s_prefix = (prev ? prev->count : 0) + exclusive;
                 }
             }
-            if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
-            const unsigned int incl = __ballot_sync(0xffffffffu, st == ST_INCLUSIVE);
-            const int first = incl ? (__ffs(incl) - 1) : 32;
-            i64 contrib = (lane <= first && idx >= 0) ? (i64)(d & DESC_VALUE_MASK) : 0;
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, m);
-            exclusive += contrib;
-            if (incl) break;
-            look -= 32;
-        }
-        if (lane == 0) {
-            if (failed) {
-                // A wait ran out (or another tile's did). Tell the tiles still waiting, and leave a record that says
-                // so; every tile after the stuck one ends here too, so the last tile cannot overwrite it with success.
-                atomicExch(abort_flag, epoch);
-                res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT;
-                s_tile_prefix = -1;
-            } else {
-                const i64 base0 = prev ? prev->count : 0;
-                desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)(exclusive + tile_total)));
-                s_tile_prefix = base0 + exclusive;
-            }
         }
     }
-    __syncthreads();
-    const i64 prefix = s_tile_prefix;
-    if (prefix < 0) return;                 // a bounded wait ran out: leave without writing
+    __syncthreads();                                       // the tile's output offset is known
+    const i64 prefix = s_prefix;
+    if (prefix < 0) return;                                // a bounded wait ran out: leave without writing
 
-    // 4. coalesced write of the staged survivors
-    for (int i = threadIdx.x; i < tile_total; i += BLOCK) {
-        const i64 pos = prefix + i;
-        if (pos < out_cap) out[pos] = s_stage[i];
+    // 6. each warp copies its compacted run; consecutive lanes write consecutive elements
+    const i64 base = prefix + warp_off;
+    if (base + warp_run <= out_cap) {                      // the usual case: no per-element bound check
+        O* __restrict__ dst = out + base;
+#pragma unroll 4
+        for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
+    } else {
+        for (int i = lane; i < warp_run; i += 32) {
+            const i64 pos = base + i;
+            if (pos < out_cap) out[pos] = stage[i];
+        }
     }
     if (tile == num_tiles - 1 && threadIdx.x == 0) {
         const i64 total = prefix + tile_total;

@@ -21,15 +21,15 @@
 #include "../../include/dcb200.h"
 #include "dcb_builtin.h"
 #include "dcb_internal.h"
+#include "dcb_kernels.cuh"
 #include "dcb_translate.h"
 
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kBlock = 256;
 
 // Look-back descriptors for DCB_NOALLOC_MAX_TILES tiles, followed by 256 bytes of control words
-// ([0] unused, [1] tile counter, [2] abort flag). File scope, device memory, lives as long as the module.
+// (word 32 is the abort flag; the rest is spare). File scope, device memory, lives as long as the module.
 static __device__ __align__(256) unsigned long long g_noalloc_scratch[DCB_NOALLOC_MAX_TILES + 32];
 
 struct DeviceState {
@@ -83,9 +83,9 @@ extern "C" dcb_status dcb_compact_noalloc(int32_t device, const dcb_pipeline_des
     bool vec = aligned(in0, 16) && aligned(out, (size_t)(e_vec * osz < 16 ? e_vec * osz : 16));
     if (info.n_in == 2) { const int b1 = e_vec * dcbt::type_size(info.in1); vec = vec && aligned(in1, (size_t)(b1 < 16 ? b1 : 16)); }
     const int E = vec ? e_vec : 1;
-    int rows = 32768 / (kBlock * E * osz);
-    rows = rows < 1 ? 1 : (rows > 4 ? 4 : rows);
-    const int64_t tile = (int64_t)(kBlock / 32) * rows * 32 * E;
+    const int block = b->compact_block;
+    const int rows = dcb::compact_rows_for(block, E, osz);
+    const int64_t tile = (int64_t)(block / 32) * rows * 32 * E;
     long long num_tiles = (n + tile - 1) / tile;
     if (num_tiles > DCB_NOALLOC_MAX_TILES) {
         char msg[512];
@@ -125,16 +125,15 @@ extern "C" dcb_status dcb_compact_noalloc(int32_t device, const dcb_pipeline_des
         return DCB_OK;
     }
     unsigned int* words = (unsigned int*)(scratch + DCB_NOALLOC_MAX_TILES);
-    e = cudaMemsetAsync(words, 0, 256, s);   // tile counter and abort flag must start at zero
+    e = cudaMemsetAsync(words, 0, 256, s);   // the abort flag must start at zero
     if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(DCB_ERR_CUDA, cudaGetErrorString(e)); }
-    unsigned int* counter = words + 1;
-    unsigned int* abort_flag = words + 2;
+    unsigned int* abort_flag = words + 32;
     unsigned int spin = 1u << 22;
     long long nn = n, cap = out_cap;
     const void* prev = nullptr;
-    void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&scratch, (void*)&counter,
+    void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&scratch,
                     (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&prev, (void*)&d_record, (void*)&abort_flag};
-    e = cudaLaunchKernel(vec ? b->k_vec : b->k_scalar, dim3((unsigned)num_tiles), dim3(kBlock), args, 0, s);
+    e = cudaLaunchKernel(vec ? b->k_vec : b->k_scalar, dim3((unsigned)num_tiles), dim3(block), args, 0, s);   // one tile per block
     if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(DCB_ERR_CUDA, cudaGetErrorString(e)); }
     return DCB_OK;
 }

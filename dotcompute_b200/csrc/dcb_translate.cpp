@@ -701,7 +701,8 @@ static std::string replace_all(std::string s, const std::string& a, const std::s
 }
 
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
-                          int block, int unroll, bool with_prelude) {
+                          const Tuning& tuning, bool with_prelude) {
+    const int block = tuning.block, unroll = tuning.unroll;
     std::string s;
     if (with_prelude) {
         s += "// generated by libdcb200: fused LINQ pipeline\n// key: " + info.key + "\n";
@@ -728,17 +729,20 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                  "(const void* in0, const void* in1, long long n, void* out) {\n    dcb::map_body<" + C + ", " + B + ", " + u + ", " + vec + ">(" +
                  cast_in() + ", n, (" + C + "::out_t*)out);\n}\n";
         } else if (info.terminal == OP_TOARRAY) {
-            const std::string rows = "dcb::compact_rows<" + C + ", " + B + ", " + vec + ">::value";
-            s += "extern \"C\" __global__ void __launch_bounds__(" + B + ") dcb_compact_" + variants[v] + suffix +
-                 "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, unsigned int* counter, "
+            const std::string CB = std::to_string(tuning.compact_block);
+            const std::string rows = tuning.compact_rows > 0 ? std::to_string(tuning.compact_rows)
+                                                             : "dcb::compact_rows<" + C + ", " + CB + ", " + vec + ">::value";
+            const std::string bounds = tuning.compact_min_blocks > 0 ? CB + ", " + std::to_string(tuning.compact_min_blocks) : CB;
+            s += "extern \"C\" __global__ void __launch_bounds__(" + bounds + ") dcb_compact_" + variants[v] + suffix +
+                 "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
                  "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag) {\n"
-                 "    dcb::compact_body<" + C + ", " + B + ", " + rows + ", " + vec + ">(" + cast_in() + ", n, (" + C +
-                 "::out_t*)out, out_cap, desc, counter, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
+                 "    dcb::compact_body<" + C + ", " + CB + ", " + rows + ", " + vec + ">(" + cast_in() + ", n, (" + C +
+                 "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
         } else {
             s += "extern \"C\" __global__ void __launch_bounds__(" + B + ") dcb_reduce_" + variants[v] + suffix +
-                 "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res) {\n    dcb::reduce_body<" + C + ", " +
-                 std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">(" + cast_in() +
-                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res);\n}\n";
+                 "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res, const __grid_constant__ dcb::PeerTable peers) {\n"
+                 "    dcb::reduce_body<" + C + ", " + std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">(" + cast_in() +
+                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res, peers);\n}\n";
         }
     }
     return s;

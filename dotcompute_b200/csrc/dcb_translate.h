@@ -48,8 +48,15 @@ bool build_chain(int elem_type0, int elem_type1, const std::vector<OpSpec>& ops,
 
 // Complete translation unit for NVRTC or nvcc: prelude + chain + extern "C" kernels whose names end in `suffix`.
 // `kernels_header` is the text of dcb_kernels.cuh, or empty to emit an #include of it instead.
+struct Tuning {
+    int block = 256;            // threads per block (the kernels assume 256)
+    int unroll = 4;             // 16-byte loads in flight per thread in map / reduce
+    int compact_block = 256;    // threads per block of the compaction kernels
+    int compact_rows = 0;       // rows per warp in the compaction tile; 0 = automatic (dcb::compact_rows_for)
+    int compact_min_blocks = 4; // second argument of __launch_bounds__ for the compaction kernels; 0 = none
+};
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
-                          int block, int unroll, bool wrap_namespace);
+                          const Tuning& tuning, bool with_prelude);
 
 unsigned long long fnv1a(const std::string& s);
 

@@ -91,6 +91,9 @@ PROTOTYPES = {
     "dcb_result_finalize": (_i32, [_vp, _vp, C.POINTER(Result)]),
     "dcb_record_finalize": (_i32, [_i32, _i32, _vp, C.POINTER(Result)]),
     "dcb_pipeline_run_host": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, C.POINTER(Result)]),
+    "dcb_peer_area_create": (_i32, [_vp, _vp, _sz]),
+    "dcb_peer_connect": (_i32, [_vp, _i32, _i32, _vp, _sz]),
+    "dcb_peer_disconnect": (_i32, [_vp]),
     "dcb_compact_noalloc": (_i32, [_i32, C.POINTER(PipelineDesc), _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "dcb_kernel_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, _pp]),
     "dcb_kernel_launch": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u32), _u32, _pp, _vp]),

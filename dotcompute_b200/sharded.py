@@ -139,6 +139,36 @@ def finalize_record(rec_host: np.ndarray, terminal: int, out_type: int) -> N.Res
     return res
 
 
+def connect_peers(acc: CudaAccelerator, group=None) -> bool:
+    """Set up the fused combine: every rank creates its exchange area, the CUDA IPC handles are all-gathered, and each
+    rank maps its peers' areas (dcb_peer_connect). From then on every reduction run on `acc` exchanges its partial with
+    the other GPUs inside the reduce kernel (NVLink peer stores) and its record holds the global result; no collective is
+    launched per query. Returns False (and leaves the NCCL path in place) when there is a single rank."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return False
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if world > 8:
+        raise errors.NotSupportedException("the fused combine serves up to 8 GPUs of one node")
+    handle = (C.c_ubyte * 64)()
+    N.check(N.lib().dcb_peer_area_create(acc.handle, handle, 64), acc.handle)
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device=f"cuda:{acc.DeviceId}")
+    allh = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
+    dist.all_gather_into_tensor(allh, mine, group=group)
+    table = np.ascontiguousarray(allh.cpu().numpy())
+    N.check(N.lib().dcb_peer_connect(acc.handle, world, rank, table.ctypes.data_as(C.c_void_p), 64), acc.handle)
+    dist.barrier(group)          # every rank has mapped every area before the first exchange
+    acc._peers_connected = True
+    return True
+
+
+def disconnect_peers(acc: CudaAccelerator) -> None:
+    N.check(N.lib().dcb_peer_disconnect(acc.handle), acc.handle)
+    acc._peers_connected = False
+
+
 class ShardedQuery:
     """One rank's part of a sharded query. `local` is this rank's shard (a device UnifiedBuffer), `ops` the
     (kind, lambda) list without the terminal. Collectives run on torch's current stream."""
@@ -176,6 +206,8 @@ class ShardedQuery:
         in1 = C.c_void_p(self.second.GetDeviceMemory()) if self.second is not None else None
         N.check(N.lib().dcb_pipeline_run_async(pipe.handle, C.c_void_p(self.local.GetDeviceMemory()), in1, n, None, 0,
                                                C.c_void_p(rec.data_ptr()), None, C.c_void_p(stream_ptr)), self.acc.handle)
+        if getattr(self.acc, "_peers_connected", False):
+            return rec           # the kernel's last block already exchanged partials with the peers
         return combine_record(rec, terminal, pipe.info.out_type, self.group)
 
     def reduce(self, terminal: int):

@@ -287,10 +287,26 @@ dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, const void* h
 dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
                                  void* host_out, int64_t host_out_cap, dcb_result* result);
 
+/* ------------------------------------------------------------------ peer exchange */
+
+/* Fused combine for sharded reductions (one process per GPU). After dcb_peer_connect, every reduction pipeline run on
+ * this context ends with the GPUs exchanging their partials inside the reduce kernel itself: its last block stores this
+ * GPU's partial into an exchange area in each peer's memory over NVLink, waits (bounded) for the peers' partials and folds
+ * them in rank order, so each rank's record already holds the global result and no separate collective is launched. All
+ * ranks must run the same sequence of reductions. A peer that never arrives ends the wait with DCB_ERR_TIMEOUT.
+ * The reference has no multi-GPU LINQ path (device 0 only, src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:188);
+ * its P2P manager only copies buffers (src/Backends/DotCompute.Backends.CUDA/P2P/CudaP2PManager.cs:137-242).
+ *   dcb_peer_area_create  allocates this GPU's 1 KiB exchange area and writes its 64-byte CUDA IPC handle to handle_out
+ *   dcb_peer_connect      handles = world handles, handle_stride bytes apart, gathered from all ranks (index = rank)
+ *   dcb_peer_disconnect   back to single-GPU behaviour */
+dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_t handle_cap);
+dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank, const void* handles, size_t handle_stride);
+dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
+
 /* ------------------------------------------------------------- no device allocation */
 
-/* Tiles the fixed scratch of dcb_compact_noalloc holds. A tile is 4096 elements for 4-byte inputs and outputs
- * (2048 for 8-byte ones), so float queries up to 2^28 elements fit. */
+/* Tiles the fixed scratch of dcb_compact_noalloc holds. A tile is 8192 elements for 4-byte inputs and outputs
+ * (4096 for 8-byte ones), so float queries up to 2^29 elements fit. */
 #define DCB_NOALLOC_MAX_TILES 65536
 
 /* Stable Where [-> Select] -> ToArray for callers that must not allocate device memory. (No counterpart in the

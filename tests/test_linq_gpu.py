@@ -306,3 +306,23 @@ def test_reference_fixture_on_gpu(acc, fx):
     term = fx["terminal"]
     got = getattr(q, term[0])(term[1]) if isinstance(term, list) else getattr(q, term)()
     check_expectation(fx, got)
+
+
+# --------------------------------------------------------------------------- in-kernel exchange, world of one
+def test_peer_exchange_world_of_one_is_transparent(built_library):
+    """dcb_peer_connect with a single rank must not change any result (the exchange is skipped for world <= 1); with a
+    real world the same code path is exercised by the multi-GPU bench. Runs on its own context so no other test is affected."""
+    import ctypes as C
+    from dotcompute_b200 import CudaAccelerator, native as N
+    acc2 = CudaAccelerator(0)
+    try:
+        handle = (C.c_ubyte * 64)()
+        N.check(N.lib().dcb_peer_area_create(acc2.handle, handle, 64), acc2.handle)
+        N.check(N.lib().dcb_peer_connect(acc2.handle, 1, 0, handle, 64), acc2.handle)
+        x = rng(3).random(300_001, dtype=F)
+        want = Enumerable(x).Where(lambda v: v > F(0.5)).Select(lambda v: v * v + F(3)).Sum()
+        assert AsComputeQueryable(x, acc2).Where("x => x > 0.5f").Select("x => x * x + 3f").Sum() == want
+        assert N.lib().dcb_peer_connect(acc2.handle, 9, 0, handle, 64) == 301      # more than 8 ranks is refused
+        N.check(N.lib().dcb_peer_disconnect(acc2.handle), acc2.handle)
+    finally:
+        acc2.Dispose()

@@ -78,7 +78,7 @@ def test_noalloc_rejects_what_it_cannot_hold(acc):
     L = N.lib()
     ops = [(N.OP_WHERE, "x => x > 0.5f"), (N.OP_SELECT, "x => x * x + 3f"), (N.OP_TOARRAY, None)]
     desc, keep = _desc(ops, N.T_F32)
-    too_many = 4096 * 65536 + 1
+    too_many = 8192 * 65536 + 1
     dummy = acc.Memory.AllocateAsync(64, np.float32)
     try:
         p = C.c_void_p(dummy.GetDeviceMemory())
