@@ -308,7 +308,7 @@ def main() -> int:
     import torch.distributed as dist
 
     from dotcompute_b200 import CudaAccelerator, native as N
-    from dotcompute_b200.sharded import ShardedQuery, connect_peers, finalize_record, shard_bounds, _stream_handle
+    from dotcompute_b200.sharded import ShardedQuery, connect_peers, finalize_record, flush_peers, shard_bounds, _stream_handle
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -390,6 +390,8 @@ def main() -> int:
             k_stop[i].record(stream)
             if not fused:
                 combine_record(rec, N.OP_SUM, out_type)
+        if fused:
+            flush_peers(acc, sh)          # completes the last step's record; earlier ones were completed by their successors
         t_end.record(stream)
         barrier()
         launches = acc.LaunchCount - launches0
@@ -465,7 +467,7 @@ def main() -> int:
             "config": {"workload": f"C5: Where(x>0.5f).Select(x*x+3f).Sum() over 2^{args.log2n} float32 uniform[0,1) seed 31, contiguous shards",
                        "n_elements": n_total, "elements_per_gpu": n_local, "l2": "inputs larger than L2 (shard >= 512 MiB)",
                        "combine": ("none (1 GPU)" if world == 1 else
-                                   "fused: the reduce kernel's last block exchanges fp64 partials over NVLink peer stores" if fused else
+                                   "fused: the reduce kernel's last block posts its fp64 partial to every peer over NVLink (peer stores) and completes the previous step's record; one flush kernel after the last step" if fused else
                                    "NCCL all-reduce of one fp64 partial per GPU"),
                        "precompiled_kernel": bool(pipe.precompiled)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -68,6 +68,7 @@ struct dcb_ctx {
     // exchange of partials between GPUs (see PeerTable in dcb_kernels.cuh)
     dcb::PeerTable peers = {};
     void* peer_area = nullptr;             // this GPU's exchange area (cudaMalloc, exported over CUDA IPC)
+    void* peer_state = nullptr;            // launch counter and pending record (device memory)
     std::vector<void*> peer_opened;        // areas of other ranks opened here
 };
 
@@ -194,6 +195,7 @@ dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
 dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     dcbt::Tuning tuning;   // the defaults, unless a tuning experiment overrides them through the environment
     tuning.unroll = env_int("DCB200_UNROLL", tuning.unroll);
+    tuning.reduce_min_blocks = env_int("DCB200_REDUCE_MINBLOCKS", 0);
     tuning.compact_block = env_int("DCB200_COMPACT_BLOCK", tuning.compact_block);
     tuning.compact_rows = env_int("DCB200_COMPACT_ROWS", 0);
     tuning.compact_min_blocks = env_int("DCB200_COMPACT_MINBLOCKS", tuning.compact_min_blocks);
@@ -382,6 +384,7 @@ extern "C" dcb_status dcb_shutdown(dcb_ctx* ctx) {
     ctx->cache.clear();
     for (void* p : ctx->peer_opened) cudaIpcCloseMemHandle(p);
     if (ctx->peer_area) cudaFree(ctx->peer_area);
+    if (ctx->peer_state) cudaFree(ctx->peer_state);
     for (int i = 0; i < 2; ++i) if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
     if (ctx->stage_out) cudaFree(ctx->stage_out);
     cudaStreamDestroy(ctx->own_stream);
@@ -724,7 +727,7 @@ dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cuda
 }
 
 dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
-                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches) {
+                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, bool exchange = true) {
     dcb_ctx* ctx = p->ctx;
     const dcbt::ChainInfo& I = p->info;
     NEED(ctx, n >= 0, "element count is negative");
@@ -795,10 +798,7 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
         unsigned int* ticket = p->sc.words;
         dcb::PeerTable peers = ctx->peers;            // world <= 1 unless dcb_peer_connect() was called
-        if (peers.world > 1) {
-            ctx->peers.seq += 1;                      // every rank runs the same sequence of sharded reductions
-            peers.seq = ctx->peers.seq;
-        }
+        if (!exchange) peers.world = 0;               // per-chunk launches of the host path keep their partials local
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res, (void*)&peers};
         if (launches) *launches += 1;
         return launch(ctx, fn, grid, args, s);
@@ -894,6 +894,10 @@ extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const v
     CU(ctx, cudaEventRecord(p->ev0, s));
     uint32_t launches = 0;
     if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches))) return st;
+    if (ctx->peers.world > 1 && p->info.terminal != DCB_OP_TOARRAY) {   // blocking call: complete the exchange now
+        if ((st = dcb_peer_flush(ctx, (void*)s))) return st;
+        launches += 1;
+    }
     CU(ctx, cudaEventRecord(p->ev1, s));
     if (!plain_map) CU(ctx, cudaMemcpyAsync(p->h_record, p->d_result, DCB_DEVICE_RESULT_BYTES, cudaMemcpyDeviceToHost, s));
     CU(ctx, cudaStreamSynchronize(s));
@@ -1013,7 +1017,7 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
                     ce = cudaMemcpyAsync((char*)host_out + off * szo, (const char*)ctx->stage_out + off * szo, (size_t)len * szo, cudaMemcpyDeviceToHost, os);
             }
         } else {
-            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches);
+            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches, false);
         }
     }
     if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
@@ -1056,9 +1060,11 @@ extern "C" dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_
     if (st) return st;
     NEED(ctx, handle_out != nullptr && handle_cap >= sizeof(cudaIpcMemHandle_t), "handle buffer must hold 64 bytes");
     if (!ctx->peer_area) {
-        const size_t bytes = sizeof(dcb::PeerSlot) * 2 * dcb::PEER_MAX;
+        const size_t bytes = sizeof(dcb::PeerSlot) * dcb::PEER_RING * dcb::PEER_MAX;
         CU(ctx, cudaMalloc(&ctx->peer_area, bytes));
         CU(ctx, cudaMemset(ctx->peer_area, 0, bytes));
+        CU(ctx, cudaMalloc(&ctx->peer_state, sizeof(dcb::PeerState)));
+        CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
         CU(ctx, cudaDeviceSynchronize());
     }
     cudaIpcMemHandle_t h;
@@ -1075,7 +1081,8 @@ extern "C" dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank
     NEED(ctx, ctx->peer_area != nullptr, "call dcb_peer_area_create first");
     NEED(ctx, handles != nullptr && handle_stride >= sizeof(cudaIpcMemHandle_t), "bad handle table");
     dcb::PeerTable t = {};
-    t.world = world; t.rank = rank; t.seq = 0; t.spin_limit = ctx->peer_spin_limit;
+    t.world = world; t.rank = rank; t.spin_limit = ctx->peer_spin_limit; t.state = (dcb::PeerState*)ctx->peer_state;
+    CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
     for (int r = 0; r < world; ++r) {
         if (r == rank) { t.area[r] = (dcb::PeerSlot*)ctx->peer_area; continue; }
         cudaIpcMemHandle_t h;
@@ -1086,6 +1093,18 @@ extern "C" dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank
         t.area[r] = (dcb::PeerSlot*)p;
     }
     ctx->peers = t;
+    return DCB_OK;
+}
+
+__global__ void peer_flush_kernel(const __grid_constant__ dcb::PeerTable pt) { dcb::peer_flush_body(pt); }
+
+extern "C" dcb_status dcb_peer_flush(dcb_ctx* ctx, void* stream) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    if (ctx->peers.world <= 1) return DCB_OK;
+    peer_flush_kernel<<<1, 32, 0, pick(ctx, stream)>>>(ctx->peers);
+    CU(ctx, cudaGetLastError());
+    ctx->launches += 1;
     return DCB_OK;
 }
 

@@ -237,6 +237,23 @@ struct Acc {
         if constexpr (is_fp<T>::value) { p.mn_bits = __double_as_longlong((double)mn); p.mx_bits = __double_as_longlong((double)mx); }
         else { p.mn_bits = (i64)mn; p.mx_bits = (i64)mx; }
     }
+    // Read from a block's slot only what this reduction accumulates (the slot was written by another block: via L2).
+    __device__ __forceinline__ void load_live(const Partial* p) {
+        if constexpr ((RED & RED_SUM) != 0) {
+            if constexpr (is_fp<T>::value) fsum = __ldcg(&p->fsum);
+            else { isum_lo = __ldcg(&p->isum_lo); if constexpr (sizeof(T) == 8) isum_hi = __ldcg(&p->isum_hi); }
+        }
+        if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX)) != 0) count = __ldcg(&p->count);
+        if constexpr ((RED & RED_MIN) != 0) {
+            const i64 b = __ldcg(&p->mn_bits);
+            if constexpr (is_fp<T>::value) mn = (T)__longlong_as_double(b); else mn = (T)b;
+        }
+        if constexpr ((RED & RED_MAX) != 0) {
+            const i64 b = __ldcg(&p->mx_bits);
+            if constexpr (is_fp<T>::value) mx = (T)__longlong_as_double(b); else mx = (T)b;
+        }
+        if constexpr ((RED & (RED_MIN | RED_MAX)) != 0 && is_fp<T>::value) flags = __ldcg(&p->flags);
+    }
     __device__ __forceinline__ void from_partial(const Partial& p) {
         fsum = p.fsum; isum_lo = p.isum_lo; isum_hi = p.isum_hi; count = p.count; cnt32 = 0; flags = p.flags;
         if constexpr (is_fp<T>::value) { mn = (T)__longlong_as_double(p.mn_bits); mx = (T)__longlong_as_double(p.mx_bits); }
@@ -329,18 +346,26 @@ __device__ __forceinline__ void map_body(const typename C::in0_t* __restrict__ i
 // ------------------------------------------------------------------ exchange of partials between GPUs
 // A sharded reduction ends with every GPU holding the total. Instead of a separate collective launch, the last block
 // of the reduce kernel stores this GPU's partial straight into an exchange area in every peer's memory (plain NVLink
-// peer stores), then waits - with a bounded poll - for the peers' partials to land in its own area and folds them in
-// rank order, so all GPUs compute bit-identical totals. Slots are double-buffered by the parity of a launch sequence
-// number; a slot is valid when its stamp equals that number.
-struct __align__(16) PeerSlot {   // 64 bytes
+// peer stores). It does not wait for the peers: the record of launch s is completed one launch later (or by the flush
+// kernel), when the partials of s have long arrived, so neither NVLink latency nor the skew between GPUs sits on the
+// critical path of a stream of queries. Waiting for launch s-1 before posting s+... also bounds how far ranks drift
+// apart (one launch), which is what makes a ring of PEER_RING slots per peer sufficient. Partials are folded in rank
+// order, so every GPU computes the bit-identical total. Every wait is a bounded poll.
+enum : int { PEER_MAX = 8, PEER_RING = 4 };
+struct __align__(16) PeerSlot {   // 64 bytes: one rank's partial for one launch; valid when stamp == launch number
     double fsum; u64 isum_lo; i64 isum_hi; i64 count; i64 mn_bits; i64 mx_bits; u64 flags; u64 stamp;
 };
-enum : int { PEER_MAX = 8 };
+enum : u64 { SLOT_IS_FP = 1ull << 32, SLOT_IS_U64 = 1ull << 33 };   // how to compare mn_bits / mx_bits
+struct PeerState {                // device memory, one per context
+    u64 seq;                      // launches posted so far (the same on every rank)
+    DeviceResult* pending;        // record of the newest launch, still holding the local partial only
+    u64 has_pending;
+};
 struct PeerTable {                // passed by value as a kernel parameter; world <= 1 means "no exchange"
     int world, rank;
-    u64 seq;                      // launch sequence number, the same on every rank, never 0
     u32 spin_limit, pad;
-    PeerSlot* area[PEER_MAX];     // area[r]: base of rank r's exchange area = PeerSlot[2][PEER_MAX], peer-mapped
+    PeerState* state;
+    PeerSlot* area[PEER_MAX];     // area[r]: base of rank r's exchange area = PeerSlot[PEER_RING][PEER_MAX], peer-mapped
 };
 __device__ __forceinline__ void st_release_sys(u64* p, u64 v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -349,6 +374,87 @@ __device__ __forceinline__ u64 ld_acquire_sys(const u64* p) {
     u64 v;
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
+}
+// Thread r < world stores `mine` into peer r's area, slot of launch `seq`.
+static __device__ __noinline__ void peer_post(const PeerTable& pt, u64 seq, const PeerSlot& mine) {
+    if ((int)threadIdx.x < pt.world) {
+        PeerSlot* dst = pt.area[threadIdx.x] + (seq % PEER_RING) * PEER_MAX + pt.rank;
+        volatile PeerSlot* vd = dst;
+        vd->fsum = mine.fsum; vd->isum_lo = mine.isum_lo; vd->isum_hi = mine.isum_hi; vd->count = mine.count;
+        vd->mn_bits = mine.mn_bits; vd->mx_bits = mine.mx_bits; vd->flags = mine.flags;
+        __threadfence_system();
+        st_release_sys(&dst->stamp, seq);
+    }
+}
+// Whole block: wait (bounded) for every rank's partial of launch `seq` in this GPU's own area, fold them in rank order
+// and write the global record to `out`. `slots` and `failed` are shared memory.
+static __device__ __noinline__ void peer_complete(const PeerTable& pt, u64 seq, DeviceResult* out, PeerSlot* slots, int* failed) {
+    if (threadIdx.x == 0) *failed = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < pt.world) {
+        const int r = threadIdx.x;
+        const PeerSlot* src = pt.area[pt.rank] + (seq % PEER_RING) * PEER_MAX + r;
+        u32 polls = 0; bool ok = true;
+        while (ld_acquire_sys(&src->stamp) != seq) {
+            if (++polls > pt.spin_limit) { ok = false; break; }
+            if (polls > 64) __nanosleep(polls > 65536 ? 1000 : 100);
+        }
+        if (ok) {
+            const volatile PeerSlot* vs = src;
+            slots[r].fsum = vs->fsum; slots[r].isum_lo = vs->isum_lo; slots[r].isum_hi = vs->isum_hi; slots[r].count = vs->count;
+            slots[r].mn_bits = vs->mn_bits; slots[r].mx_bits = vs->mx_bits; slots[r].flags = vs->flags;
+        } else {
+            atomicExch(failed, 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (*failed) {                                    // a peer never showed up: say so, keep the local partial
+            out->flags = out->flags | (u64)FLAG_TIMEOUT;
+        } else {
+            PeerSlot g = slots[0];
+            const bool fp = (g.flags & SLOT_IS_FP) != 0, u64cmp = (g.flags & SLOT_IS_U64) != 0;
+            for (int r = 1; r < pt.world; ++r) {          // rank order: the same arithmetic on every GPU
+                const PeerSlot& o = slots[r];
+                g.fsum += o.fsum;
+                const u64 lo = g.isum_lo + o.isum_lo;
+                g.isum_hi += o.isum_hi + (lo < o.isum_lo ? 1 : 0);
+                g.isum_lo = lo;
+                g.count += o.count;
+                if (fp) {
+                    if (__longlong_as_double(o.mn_bits) < __longlong_as_double(g.mn_bits)) g.mn_bits = o.mn_bits;
+                    if (__longlong_as_double(o.mx_bits) > __longlong_as_double(g.mx_bits)) g.mx_bits = o.mx_bits;
+                } else if (u64cmp) {
+                    if ((u64)o.mn_bits < (u64)g.mn_bits) g.mn_bits = o.mn_bits;
+                    if ((u64)o.mx_bits > (u64)g.mx_bits) g.mx_bits = o.mx_bits;
+                } else {
+                    if (o.mn_bits < g.mn_bits) g.mn_bits = o.mn_bits;
+                    if (o.mx_bits > g.mx_bits) g.mx_bits = o.mx_bits;
+                }
+                g.flags |= o.flags;
+            }
+            out->fsum = g.fsum; out->count_f = (double)g.count; out->isum_lo = (i64)g.isum_lo; out->isum_hi = g.isum_hi;
+            out->count = g.count;
+            if (fp) { out->fmin = __longlong_as_double(g.mn_bits); out->fmax = __longlong_as_double(g.mx_bits); out->imin = 0; out->imax = 0; }
+            else { out->fmin = 0; out->fmax = 0; out->imin = g.mn_bits; out->imax = g.mx_bits; }
+            out->flags = g.flags & 0xffffffffull;
+        }
+    }
+    __syncthreads();
+}
+// One block: complete the newest launch's record (used after the last query of a batch, and by the blocking API).
+__device__ __forceinline__ void peer_flush_body(const PeerTable& pt) {
+    __shared__ PeerSlot s_slots[PEER_MAX];
+    __shared__ int s_failed;
+    __shared__ u64 s_seq;
+    __shared__ DeviceResult* s_out;
+    if (threadIdx.x == 0) {
+        s_out = pt.state->has_pending ? pt.state->pending : nullptr;
+        s_seq = pt.state->seq;
+        pt.state->has_pending = 0;
+    }
+    __syncthreads();
+    if (s_out) peer_complete(pt, s_seq, s_out, s_slots, &s_failed);
 }
 
 // ------------------------------------------------------------------ reduce: chain + Sum/Min/Max/Count in one read
@@ -363,14 +469,20 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     __shared__ Partial s_part[BLOCK / 32];
     __shared__ bool s_last;
     __shared__ PeerSlot s_peer[PEER_MAX];
+    __shared__ PeerSlot s_mine;
     __shared__ int s_peer_failed;
+    __shared__ u64 s_seq;
+    __shared__ DeviceResult* s_prev;
 
     Acc<O, RED> acc; acc.init();
+    // Whole tiles of BLOCK*UNROLL packs are dealt round-robin, the same number to every block, so that at any moment all
+    // blocks read from one compact window that moves through the array (measured faster than giving each block its own
+    // distant range). What is left over, less than one tile per block, is split evenly so all blocks finish together.
     const i64 nitems = n / E;
     const i64 tile_items = (i64)BLOCK * UNROLL;
-    const i64 ntiles = nitems / tile_items;
-    for (i64 t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const i64 base = t * tile_items + threadIdx.x;
+    const i64 rounds = (nitems / tile_items) / gridDim.x;
+    for (i64 r = 0; r < rounds; ++r) {
+        const i64 base = (r * gridDim.x + blockIdx.x) * tile_items + threadIdx.x;
         Pack<A, E> a[UNROLL]; Pack<B, E> b[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -388,19 +500,36 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
             }
         }
     }
-    const i64 gtid = (i64)blockIdx.x * BLOCK + threadIdx.x, gsize = (i64)gridDim.x * BLOCK;
-    for (i64 it = ntiles * tile_items + gtid; it < nitems; it += gsize) {
-        Pack<A, E> a; Pack<B, E> b;
-        a.load(in0 + it * E);
-        if constexpr (C::n_in == 2) b.load(in1 + it * E);
+    const i64 rest_lo = rounds * gridDim.x * tile_items;
+    const i64 per_block = (nitems - rest_lo + gridDim.x - 1) / gridDim.x;          // < tile_items + 1
+    const i64 off = rest_lo + (i64)blockIdx.x * per_block < nitems ? rest_lo + (i64)blockIdx.x * per_block : nitems;
+    const i64 range_hi = off + per_block < nitems ? off + per_block : nitems;
+    {   // the block's share of the leftover: at most UNROLL packs per thread, still issued together
+        Pack<A, E> a[UNROLL]; Pack<B, E> b[UNROLL];
 #pragma unroll
-        for (int k = 0; k < E; ++k) {
-            O o; bool keep;
-            if constexpr (C::n_in == 2) keep = C::apply(a.e[k], b.e[k], o); else keep = C::apply(a.e[k], B(), o);
-            if (keep) acc.add(o);
+        for (int u = 0; u < UNROLL; ++u) {
+            const i64 it = off + threadIdx.x + (i64)u * BLOCK;
+            if (it < range_hi) {
+                a[u].load(in0 + it * E);
+                if constexpr (C::n_in == 2) b[u].load(in1 + it * E);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const i64 it = off + threadIdx.x + (i64)u * BLOCK;
+            if (it < range_hi) {
+#pragma unroll
+                for (int k = 0; k < E; ++k) {
+                    O o; bool keep;
+                    if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
+                    else keep = C::apply(a[u].e[k], B(), o);
+                    if (keep) acc.add(o);
+                }
+            }
         }
     }
-    for (i64 i = nitems * E + gtid; i < n; i += gsize) {
+    const i64 gtid = (i64)blockIdx.x * BLOCK + threadIdx.x, gsize = (i64)gridDim.x * BLOCK;
+    for (i64 i = nitems * E + gtid; i < n; i += gsize) {   // the last n % E elements
         O o; bool keep;
         if constexpr (C::n_in == 2) keep = C::apply(in0[i], in1[i], o); else keep = C::apply(in0[i], B(), o);
         if (keep) acc.add(o);
@@ -417,71 +546,48 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // Last block: thread k folds slots k, k+BLOCK, ... in increasing order, then the same block tree.
+    // Last block: thread k folds slots k, k+BLOCK, ... in increasing order, then the same block tree. Only the fields
+    // this reduction uses are read, FOLD slots at a time so that their loads are in flight together.
     Acc<O, RED> tot; tot.init();
-    for (unsigned int s = threadIdx.x; s < gridDim.x; s += BLOCK) {
-        Partial p; partial_load(p, partials + s);
-        Acc<O, RED> o; o.from_partial(p);
-        tot.merge(o);
+    constexpr int FOLD = 6;
+    for (unsigned int s0 = threadIdx.x; s0 < gridDim.x; s0 += BLOCK * FOLD) {
+        Acc<O, RED> o[FOLD];
+#pragma unroll
+        for (int f = 0; f < FOLD; ++f) {
+            o[f].init();
+            const unsigned int sl = s0 + (unsigned int)f * BLOCK;
+            if (sl < gridDim.x) o[f].load_live(partials + sl);
+        }
+#pragma unroll
+        for (int f = 0; f < FOLD; ++f) tot.merge(o[f]);
     }
     tot = block_reduce<O, RED, BLOCK>(tot, s_part);
-    u32 extra_flags = 0;
-    if (peers.world > 1) {
-        // Exchange with the other GPUs: thread r < world serves peer r.
-        const int par = (int)(peers.seq & 1ull);
-        if (threadIdx.x == 0) s_peer_failed = 0;
-        __syncthreads();
-        if (threadIdx.x < peers.world) {
-            const int r = threadIdx.x;
-            Partial mine; tot.to_partial(mine);                  // warp 0 holds the block total in every lane
-            PeerSlot* dst = peers.area[r] + par * PEER_MAX + peers.rank;
-            volatile PeerSlot* vd = dst;
-            vd->fsum = mine.fsum; vd->isum_lo = mine.isum_lo; vd->isum_hi = mine.isum_hi; vd->count = mine.count;
-            vd->mn_bits = mine.mn_bits; vd->mx_bits = mine.mx_bits; vd->flags = (u64)mine.flags;
-            __threadfence_system();
-            st_release_sys(&dst->stamp, peers.seq);
-            // wait for rank r's partial in my own area (bounded)
-            const PeerSlot* src = peers.area[peers.rank] + par * PEER_MAX + r;
-            u32 polls = 0; bool ok = true;
-            while (ld_acquire_sys(&src->stamp) != peers.seq) {
-                if (++polls > peers.spin_limit) { ok = false; break; }
-                if (polls > 256) __nanosleep(polls > 65536 ? 1000 : 100);
-            }
-            if (ok) {
-                const volatile PeerSlot* vs = src;
-                s_peer[r].fsum = vs->fsum; s_peer[r].isum_lo = vs->isum_lo; s_peer[r].isum_hi = vs->isum_hi; s_peer[r].count = vs->count;
-                s_peer[r].mn_bits = vs->mn_bits; s_peer[r].mx_bits = vs->mx_bits; s_peer[r].flags = vs->flags;
-            } else {
-                atomicExch(&s_peer_failed, 1);
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            if (s_peer_failed) {
-                extra_flags = FLAG_TIMEOUT;                      // a peer never showed up: report, do not hang
-            } else {
-                Acc<O, RED> g; g.init();
-                for (int r = 0; r < peers.world; ++r) {          // rank order: the same sum on every GPU
-                    Partial p;
-                    p.fsum = s_peer[r].fsum; p.isum_lo = s_peer[r].isum_lo; p.isum_hi = s_peer[r].isum_hi; p.count = s_peer[r].count;
-                    p.mn_bits = s_peer[r].mn_bits; p.mx_bits = s_peer[r].mx_bits; p.flags = (u32)s_peer[r].flags; p.pad0 = 0; p.pad1 = 0;
-                    Acc<O, RED> o; o.from_partial(p);
-                    if (r == 0) g = o; else g.merge(o);
-                }
-                tot = g;
-            }
-        }
-    }
     if (threadIdx.x == 0) {
         Partial p; tot.to_partial(p);
-        p.flags |= extra_flags;
         res->fsum = p.fsum; res->count_f = (double)p.count;
         res->isum_lo = (i64)p.isum_lo; res->isum_hi = (sizeof(O) == 8) ? p.isum_hi : ((i64)p.isum_lo < 0 ? -1 : 0);
         res->count = p.count;
         if constexpr (is_fp<O>::value) { res->fmin = __longlong_as_double(p.mn_bits); res->fmax = __longlong_as_double(p.mx_bits); res->imin = 0; res->imax = 0; }
         else { res->fmin = 0; res->fmax = 0; res->imin = p.mn_bits; res->imax = p.mx_bits; }
         res->flags = p.flags;
+        if (peers.world > 1) {
+            // Post this launch's partial; take over the completion of the previous launch's record.
+            PeerState* st = peers.state;
+            const u64 seq = st->seq + 1;
+            st->seq = seq;
+            s_seq = seq;
+            s_prev = st->has_pending ? st->pending : nullptr;
+            st->pending = res; st->has_pending = 1;
+            s_mine.fsum = p.fsum; s_mine.isum_lo = p.isum_lo; s_mine.isum_hi = res->isum_hi; s_mine.count = p.count;
+            s_mine.mn_bits = p.mn_bits; s_mine.mx_bits = p.mx_bits;
+            s_mine.flags = (u64)p.flags | (is_fp<O>::value ? SLOT_IS_FP : 0ull) | (same_t<O, u64>::value ? SLOT_IS_U64 : 0ull);
+        }
         *ticket = 0;   // ready for the next launch on this stream
+    }
+    if (peers.world > 1) {
+        __syncthreads();
+        peer_post(peers, s_seq, s_mine);
+        if (s_prev) peer_complete(peers, s_seq - 1, s_prev, s_peer, &s_peer_failed);
     }
 }
 

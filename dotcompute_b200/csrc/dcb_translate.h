@@ -51,6 +51,7 @@ bool build_chain(int elem_type0, int elem_type1, const std::vector<OpSpec>& ops,
 struct Tuning {
     int block = 256;            // threads per block (the kernels assume 256)
     int unroll = 4;             // 16-byte loads in flight per thread in map / reduce
+    int reduce_min_blocks = 0;  // second argument of __launch_bounds__ for the reduce kernels; 0 = 6 (one input) / 4 (Zip)
     int compact_block = 256;    // threads per block of the compaction kernels
     int compact_rows = 0;       // rows per warp in the compaction tile; 0 = automatic (dcb::compact_rows_for)
     int compact_min_blocks = 4; // second argument of __launch_bounds__ for the compaction kernels; 0 = none

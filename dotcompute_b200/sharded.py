@@ -164,6 +164,11 @@ def connect_peers(acc: CudaAccelerator, group=None) -> bool:
     return True
 
 
+def flush_peers(acc: CudaAccelerator, stream_ptr: int = 0) -> None:
+    """Enqueue the completion of the newest sharded reduction's record (a one-block kernel)."""
+    N.check(N.lib().dcb_peer_flush(acc.handle, C.c_void_p(stream_ptr)), acc.handle)
+
+
 def disconnect_peers(acc: CudaAccelerator) -> None:
     N.check(N.lib().dcb_peer_disconnect(acc.handle), acc.handle)
     acc._peers_connected = False
@@ -207,7 +212,9 @@ class ShardedQuery:
         N.check(N.lib().dcb_pipeline_run_async(pipe.handle, C.c_void_p(self.local.GetDeviceMemory()), in1, n, None, 0,
                                                C.c_void_p(rec.data_ptr()), None, C.c_void_p(stream_ptr)), self.acc.handle)
         if getattr(self.acc, "_peers_connected", False):
-            return rec           # the kernel's last block already exchanged partials with the peers
+            # The kernel's last block posted this GPU's partial to the peers. The record becomes the global result when the
+            # next reduction on this accelerator runs, or at flush_peers().
+            return rec
         return combine_record(rec, terminal, pipe.info.out_type, self.group)
 
     def reduce(self, terminal: int):
@@ -215,6 +222,8 @@ class ShardedQuery:
         import torch
         stream = torch.cuda.current_stream()
         rec = self.enqueue_reduce(terminal, _stream_handle(stream))
+        if getattr(self.acc, "_peers_connected", False):
+            flush_peers(self.acc, _stream_handle(stream))
         pipe = self.pipeline(terminal)
         res = finalize_record(rec.cpu().numpy(), terminal, pipe.info.out_type)
         return pipe.scalar(res)
