@@ -308,7 +308,7 @@ def main() -> int:
     import torch.distributed as dist
 
     from dotcompute_b200 import CudaAccelerator, native as N
-    from dotcompute_b200.sharded import ShardedQuery, connect_peers, finalize_record, flush_peers, shard_bounds, _stream_handle
+    from dotcompute_b200.sharded import ShardedQuery, connect_peers, finalize_record, shard_bounds, _stream_handle
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -350,7 +350,7 @@ def main() -> int:
     launches0 = None
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
-            q.enqueue_reduce(N.OP_SUM, sh)
+            q.enqueue_reduce(N.OP_SUM, stream)
         barrier()
         # The timed region lasts milliseconds, far less than nvidia-smi's sampling period. So the sampler starts here, the
         # same step is repeated untimed for about 0.7 s (clocks settle under this load), and the timed region follows at
@@ -361,7 +361,7 @@ def main() -> int:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(8):
-            q.enqueue_reduce(N.OP_SUM, sh)
+            q.enqueue_reduce(N.OP_SUM, stream)
         e1.record(stream)
         stream.synchronize()
         bt = torch.tensor([max(e0.elapsed_time(e1), 1e-3)], dtype=torch.float64, device=device)
@@ -370,7 +370,7 @@ def main() -> int:
         n_batches = 0 if args.profile else int(min(max(700.0 / float(bt[0]), 1), 2000))
         for _ in range(n_batches):
             for _ in range(8):
-                q.enqueue_reduce(N.OP_SUM, sh)
+                q.enqueue_reduce(N.OP_SUM, stream)
             stream.synchronize()
         barrier()
         # ---- timed region: K steps, device-resident; events around the whole region and around every kernel
@@ -378,20 +378,21 @@ def main() -> int:
         k_stop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = acc.LaunchCount
-        rec = q.record_tensor()
-        in0 = C.c_void_p(dev.GetDeviceMemory())
-        recp = C.c_void_p(rec.data_ptr())
-        from dotcompute_b200.sharded import combine_record
-        out_type = pipe.info.out_type
+        q._setup()
         t_begin.record(stream)
+        last = None
         for i in range(args.steps):
+            slot = q._step % q.RING
+            q._step += 1
+            rec = q._ring[slot]
+            if q._exchange_done[slot] is not None:
+                stream.wait_event(q._exchange_done[slot])
             k_start[i].record(stream)
-            N.check(N.lib().dcb_pipeline_run_async(pipe.handle, in0, None, n_local, None, 0, recp, None, C.c_void_p(sh)), acc.handle)
+            q.launch_local(N.OP_SUM, stream, rec)          # the fused Where->Select->Sum kernel over this rank's shard
             k_stop[i].record(stream)
-            if not fused:
-                combine_record(rec, N.OP_SUM, out_type)
-        if fused:
-            flush_peers(acc, sh)          # completes the last step's record; earlier ones were completed by their successors
+            last = q.exchange(N.OP_SUM, stream, rec, slot)  # side-stream NVLink exchange (fused) or NCCL all-reduce
+        if last is not None:
+            stream.wait_event(last)                         # the timed region ends when the last record is global
         t_end.record(stream)
         barrier()
         launches = acc.LaunchCount - launches0
@@ -467,7 +468,7 @@ def main() -> int:
             "config": {"workload": f"C5: Where(x>0.5f).Select(x*x+3f).Sum() over 2^{args.log2n} float32 uniform[0,1) seed 31, contiguous shards",
                        "n_elements": n_total, "elements_per_gpu": n_local, "l2": "inputs larger than L2 (shard >= 512 MiB)",
                        "combine": ("none (1 GPU)" if world == 1 else
-                                   "fused: the reduce kernel's last block posts its fp64 partial to every peer over NVLink (peer stores) and completes the previous step's record; one flush kernel after the last step" if fused else
+                                   "one-warp exchange kernel on a side stream: NVLink peer stores of the fp64 partials, fold in rank order, overlapped with the next step's kernel" if fused else
                                    "NCCL all-reduce of one fp64 partial per GPU"),
                        "precompiled_kernel": bool(pipe.precompiled)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

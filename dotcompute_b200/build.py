@@ -55,7 +55,7 @@ def _stale(target, paths):
 
 def sources():
     names = ["dcb_kernels.cuh", "dcb_translate.h", "dcb_translate.cpp", "dcb_api.cu", "dcb_builtin.h",
-             "dcb_builtin_pipelines.txt", "dcb_gen.cpp", "dcb_noalloc.cu"]
+             "dcb_builtin_pipelines.txt", "dcb_gen.cpp", "dcb_noalloc.cu", "dcb_peer.cuh", "dcb_internal.h"]
     out = [os.path.join(CSRC, n) for n in names if os.path.exists(os.path.join(CSRC, n))]
     out.append(os.path.join(HERE, "..", "include", "dcb200.h"))
     out.append(os.path.abspath(__file__))

@@ -23,6 +23,7 @@
 #include "dcb_builtin.h"
 #include "dcb_internal.h"
 #include "dcb_kernels.cuh"
+#include "dcb_peer.cuh"
 #include "dcb_translate.h"
 
 // Text of dcb_kernels.cuh, generated at build time, handed to NVRTC in front of every chain.
@@ -727,7 +728,7 @@ dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cuda
 }
 
 dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
-                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, bool exchange = true) {
+                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches) {
     dcb_ctx* ctx = p->ctx;
     const dcbt::ChainInfo& I = p->info;
     NEED(ctx, n >= 0, "element count is negative");
@@ -797,9 +798,7 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         max_grid = std::min<int64_t>(max_grid, kMaxPartials);
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
         unsigned int* ticket = p->sc.words;
-        dcb::PeerTable peers = ctx->peers;            // world <= 1 unless dcb_peer_connect() was called
-        if (!exchange) peers.world = 0;               // per-chunk launches of the host path keep their partials local
-        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res, (void*)&peers};
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res};
         if (launches) *launches += 1;
         return launch(ctx, fn, grid, args, s);
     }
@@ -894,8 +893,8 @@ extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const v
     CU(ctx, cudaEventRecord(p->ev0, s));
     uint32_t launches = 0;
     if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches))) return st;
-    if (ctx->peers.world > 1 && p->info.terminal != DCB_OP_TOARRAY) {   // blocking call: complete the exchange now
-        if ((st = dcb_peer_flush(ctx, (void*)s))) return st;
+    if (ctx->peers.world > 1 && p->info.terminal != DCB_OP_TOARRAY) {   // blocking call: exchange on the same stream
+        if ((st = dcb_peer_exchange_async(ctx, p->d_result, p->info.out_type, (void*)s))) return st;
         launches += 1;
     }
     CU(ctx, cudaEventRecord(p->ev1, s));
@@ -1017,7 +1016,7 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
                     ce = cudaMemcpyAsync((char*)host_out + off * szo, (const char*)ctx->stage_out + off * szo, (size_t)len * szo, cudaMemcpyDeviceToHost, os);
             }
         } else {
-            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches, false);
+            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches);
         }
     }
     if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
@@ -1096,13 +1095,19 @@ extern "C" dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank
     return DCB_OK;
 }
 
-__global__ void peer_flush_kernel(const __grid_constant__ dcb::PeerTable pt) { dcb::peer_flush_body(pt); }
+__global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant__ dcb::PeerTable pt, dcb::DeviceResult* rec, unsigned long long tag) {
+    dcb::peer_exchange_body(pt, rec, tag);
+}
 
-extern "C" dcb_status dcb_peer_flush(dcb_ctx* ctx, void* stream) {
+extern "C" dcb_status dcb_peer_exchange_async(dcb_ctx* ctx, void* d_record, int32_t out_type, void* stream) {
     dcb_status st = use(ctx);
     if (st) return st;
+    NEED(ctx, d_record != nullptr, "d_record is null");
     if (ctx->peers.world <= 1) return DCB_OK;
-    peer_flush_kernel<<<1, 32, 0, pick(ctx, stream)>>>(ctx->peers);
+    unsigned long long tag = 0;
+    if (out_type == DCB_T_F32 || out_type == DCB_T_F64) tag |= dcb::SLOT_IS_FP;
+    if (out_type == DCB_T_U64) tag |= dcb::SLOT_IS_U64;
+    peer_exchange_kernel<<<1, 32, 0, pick(ctx, stream)>>>(ctx->peers, (dcb::DeviceResult*)d_record, tag);
     CU(ctx, cudaGetLastError());
     ctx->launches += 1;
     return DCB_OK;

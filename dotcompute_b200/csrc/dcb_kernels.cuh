@@ -343,136 +343,17 @@ __device__ __forceinline__ void map_body(const typename C::in0_t* __restrict__ i
     }
 }
 
-// ------------------------------------------------------------------ exchange of partials between GPUs
-// A sharded reduction ends with every GPU holding the total. Instead of a separate collective launch, the last block
-// of the reduce kernel stores this GPU's partial straight into an exchange area in every peer's memory (plain NVLink
-// peer stores). It does not wait for the peers: the record of launch s is completed one launch later (or by the flush
-// kernel), when the partials of s have long arrived, so neither NVLink latency nor the skew between GPUs sits on the
-// critical path of a stream of queries. Waiting for launch s-1 before posting s+... also bounds how far ranks drift
-// apart (one launch), which is what makes a ring of PEER_RING slots per peer sufficient. Partials are folded in rank
-// order, so every GPU computes the bit-identical total. Every wait is a bounded poll.
-enum : int { PEER_MAX = 8, PEER_RING = 4 };
-struct __align__(16) PeerSlot {   // 64 bytes: one rank's partial for one launch; valid when stamp == launch number
-    double fsum; u64 isum_lo; i64 isum_hi; i64 count; i64 mn_bits; i64 mx_bits; u64 flags; u64 stamp;
-};
-enum : u64 { SLOT_IS_FP = 1ull << 32, SLOT_IS_U64 = 1ull << 33 };   // how to compare mn_bits / mx_bits
-struct PeerState {                // device memory, one per context
-    u64 seq;                      // launches posted so far (the same on every rank)
-    DeviceResult* pending;        // record of the newest launch, still holding the local partial only
-    u64 has_pending;
-};
-struct PeerTable {                // passed by value as a kernel parameter; world <= 1 means "no exchange"
-    int world, rank;
-    u32 spin_limit, pad;
-    PeerState* state;
-    PeerSlot* area[PEER_MAX];     // area[r]: base of rank r's exchange area = PeerSlot[PEER_RING][PEER_MAX], peer-mapped
-};
-__device__ __forceinline__ void st_release_sys(u64* p, u64 v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ u64 ld_acquire_sys(const u64* p) {
-    u64 v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-// Thread r < world stores `mine` into peer r's area, slot of launch `seq`.
-static __device__ __noinline__ void peer_post(const PeerTable& pt, u64 seq, const PeerSlot& mine) {
-    if ((int)threadIdx.x < pt.world) {
-        PeerSlot* dst = pt.area[threadIdx.x] + (seq % PEER_RING) * PEER_MAX + pt.rank;
-        volatile PeerSlot* vd = dst;
-        vd->fsum = mine.fsum; vd->isum_lo = mine.isum_lo; vd->isum_hi = mine.isum_hi; vd->count = mine.count;
-        vd->mn_bits = mine.mn_bits; vd->mx_bits = mine.mx_bits; vd->flags = mine.flags;
-        __threadfence_system();
-        st_release_sys(&dst->stamp, seq);
-    }
-}
-// Whole block: wait (bounded) for every rank's partial of launch `seq` in this GPU's own area, fold them in rank order
-// and write the global record to `out`. `slots` and `failed` are shared memory.
-static __device__ __noinline__ void peer_complete(const PeerTable& pt, u64 seq, DeviceResult* out, PeerSlot* slots, int* failed) {
-    if (threadIdx.x == 0) *failed = 0;
-    __syncthreads();
-    if ((int)threadIdx.x < pt.world) {
-        const int r = threadIdx.x;
-        const PeerSlot* src = pt.area[pt.rank] + (seq % PEER_RING) * PEER_MAX + r;
-        u32 polls = 0; bool ok = true;
-        while (ld_acquire_sys(&src->stamp) != seq) {
-            if (++polls > pt.spin_limit) { ok = false; break; }
-            if (polls > 64) __nanosleep(polls > 65536 ? 1000 : 100);
-        }
-        if (ok) {
-            const volatile PeerSlot* vs = src;
-            slots[r].fsum = vs->fsum; slots[r].isum_lo = vs->isum_lo; slots[r].isum_hi = vs->isum_hi; slots[r].count = vs->count;
-            slots[r].mn_bits = vs->mn_bits; slots[r].mx_bits = vs->mx_bits; slots[r].flags = vs->flags;
-        } else {
-            atomicExch(failed, 1);
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        if (*failed) {                                    // a peer never showed up: say so, keep the local partial
-            out->flags = out->flags | (u64)FLAG_TIMEOUT;
-        } else {
-            PeerSlot g = slots[0];
-            const bool fp = (g.flags & SLOT_IS_FP) != 0, u64cmp = (g.flags & SLOT_IS_U64) != 0;
-            for (int r = 1; r < pt.world; ++r) {          // rank order: the same arithmetic on every GPU
-                const PeerSlot& o = slots[r];
-                g.fsum += o.fsum;
-                const u64 lo = g.isum_lo + o.isum_lo;
-                g.isum_hi += o.isum_hi + (lo < o.isum_lo ? 1 : 0);
-                g.isum_lo = lo;
-                g.count += o.count;
-                if (fp) {
-                    if (__longlong_as_double(o.mn_bits) < __longlong_as_double(g.mn_bits)) g.mn_bits = o.mn_bits;
-                    if (__longlong_as_double(o.mx_bits) > __longlong_as_double(g.mx_bits)) g.mx_bits = o.mx_bits;
-                } else if (u64cmp) {
-                    if ((u64)o.mn_bits < (u64)g.mn_bits) g.mn_bits = o.mn_bits;
-                    if ((u64)o.mx_bits > (u64)g.mx_bits) g.mx_bits = o.mx_bits;
-                } else {
-                    if (o.mn_bits < g.mn_bits) g.mn_bits = o.mn_bits;
-                    if (o.mx_bits > g.mx_bits) g.mx_bits = o.mx_bits;
-                }
-                g.flags |= o.flags;
-            }
-            out->fsum = g.fsum; out->count_f = (double)g.count; out->isum_lo = (i64)g.isum_lo; out->isum_hi = g.isum_hi;
-            out->count = g.count;
-            if (fp) { out->fmin = __longlong_as_double(g.mn_bits); out->fmax = __longlong_as_double(g.mx_bits); out->imin = 0; out->imax = 0; }
-            else { out->fmin = 0; out->fmax = 0; out->imin = g.mn_bits; out->imax = g.mx_bits; }
-            out->flags = g.flags & 0xffffffffull;
-        }
-    }
-    __syncthreads();
-}
-// One block: complete the newest launch's record (used after the last query of a batch, and by the blocking API).
-__device__ __forceinline__ void peer_flush_body(const PeerTable& pt) {
-    __shared__ PeerSlot s_slots[PEER_MAX];
-    __shared__ int s_failed;
-    __shared__ u64 s_seq;
-    __shared__ DeviceResult* s_out;
-    if (threadIdx.x == 0) {
-        s_out = pt.state->has_pending ? pt.state->pending : nullptr;
-        s_seq = pt.state->seq;
-        pt.state->has_pending = 0;
-    }
-    __syncthreads();
-    if (s_out) peer_complete(pt, s_seq, s_out, s_slots, &s_failed);
-}
-
 // ------------------------------------------------------------------ reduce: chain + Sum/Min/Max/Count in one read
 // Persistent grid. Each block leaves its partial in slot blockIdx.x; the block that takes the last
 // ticket combines the slots in index order. Nothing depends on which block finishes first.
 template <class C, int RED, int BLOCK, int UNROLL, bool VEC>
 __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
                                             i64 n, Partial* __restrict__ partials, unsigned int* __restrict__ ticket,
-                                            DeviceResult* __restrict__ res, const PeerTable& peers) {
+                                            DeviceResult* __restrict__ res) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     constexpr int E = pack_elems<C, VEC>::value;
     __shared__ Partial s_part[BLOCK / 32];
     __shared__ bool s_last;
-    __shared__ PeerSlot s_peer[PEER_MAX];
-    __shared__ PeerSlot s_mine;
-    __shared__ int s_peer_failed;
-    __shared__ u64 s_seq;
-    __shared__ DeviceResult* s_prev;
 
     Acc<O, RED> acc; acc.init();
     // Whole tiles of BLOCK*UNROLL packs are dealt round-robin, the same number to every block, so that at any moment all
@@ -570,24 +451,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         if constexpr (is_fp<O>::value) { res->fmin = __longlong_as_double(p.mn_bits); res->fmax = __longlong_as_double(p.mx_bits); res->imin = 0; res->imax = 0; }
         else { res->fmin = 0; res->fmax = 0; res->imin = p.mn_bits; res->imax = p.mx_bits; }
         res->flags = p.flags;
-        if (peers.world > 1) {
-            // Post this launch's partial; take over the completion of the previous launch's record.
-            PeerState* st = peers.state;
-            const u64 seq = st->seq + 1;
-            st->seq = seq;
-            s_seq = seq;
-            s_prev = st->has_pending ? st->pending : nullptr;
-            st->pending = res; st->has_pending = 1;
-            s_mine.fsum = p.fsum; s_mine.isum_lo = p.isum_lo; s_mine.isum_hi = res->isum_hi; s_mine.count = p.count;
-            s_mine.mn_bits = p.mn_bits; s_mine.mx_bits = p.mx_bits;
-            s_mine.flags = (u64)p.flags | (is_fp<O>::value ? SLOT_IS_FP : 0ull) | (same_t<O, u64>::value ? SLOT_IS_U64 : 0ull);
-        }
         *ticket = 0;   // ready for the next launch on this stream
-    }
-    if (peers.world > 1) {
-        __syncthreads();
-        peer_post(peers, s_seq, s_mine);
-        if (s_prev) peer_complete(peers, s_seq - 1, s_prev, s_peer, &s_peer_failed);
     }
 }
 

@@ -740,12 +740,12 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                  "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
         } else {
             // Keep the register count where 6 (one input) or 4 (Zip) blocks share an SM: measured as fast as 8 blocks, and
-            // unlike a cap of 32 registers it leaves the once-per-launch tail (fold, exchange between GPUs) free of spills.
+            // unlike a cap of 32 registers it leaves the once-per-launch tail (the fold of the block partials) free of spills.
             const std::string rb = B + ", " + std::to_string(tuning.reduce_min_blocks > 0 ? tuning.reduce_min_blocks : (info.n_in == 2 ? 4 : 6));
             s += "extern \"C\" __global__ void __launch_bounds__(" + rb + ") dcb_reduce_" + variants[v] + suffix +
-                 "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res, const __grid_constant__ dcb::PeerTable peers) {\n"
+                 "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res) {\n"
                  "    dcb::reduce_body<" + C + ", " + std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">(" + cast_in() +
-                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res, peers);\n}\n";
+                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res);\n}\n";
         }
     }
     return s;

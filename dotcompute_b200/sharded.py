@@ -6,10 +6,12 @@ and has a generic data-parallel splitter that the LINQ path never calls
 (src/Core/DotCompute.Core/Execution/Types/CommunicationBackend.cs:12-19). Here the element range is cut into
 contiguous shards, each rank runs the fused kernel on its shard, and only the 128-byte record crosses NVLink:
 
-  Sum / Average / Count   the kernel leaves its fp64 (or int64) partial in a device tensor that is handed to
-                          all_reduce(SUM) on the same stream - no host round trip between kernel and collective
-  Min / Max               records are all-gathered and folded in rank order (NaN bookkeeping needs an OR, which
-                          NCCL has no reduction for)
+  reductions, by default  connect_peers(): a one-warp kernel on a side stream stores each GPU's partial into every
+                          peer's memory over NVLink, waits (bounded) for theirs and folds them in rank order; it runs
+                          beside the next query's reduce kernel, so the exchange is off the critical path
+  reductions, NCCL route  Sum / Average / Count: the record tensor goes straight into all_reduce(SUM) on the same
+                          stream; Min / Max: records are all-gathered and folded in rank order (NaN bookkeeping
+                          needs an OR, which NCCL has no reduction for)
   ToArray                 each rank compacts its shard; all_gather of the survivor counts gives every rank its
                           offset in the global result, which is the shards' outputs concatenated in rank order -
                           identical to the single-GPU stable order
@@ -164,11 +166,6 @@ def connect_peers(acc: CudaAccelerator, group=None) -> bool:
     return True
 
 
-def flush_peers(acc: CudaAccelerator, stream_ptr: int = 0) -> None:
-    """Enqueue the completion of the newest sharded reduction's record (a one-block kernel)."""
-    N.check(N.lib().dcb_peer_flush(acc.handle, C.c_void_p(stream_ptr)), acc.handle)
-
-
 def disconnect_peers(acc: CudaAccelerator) -> None:
     N.check(N.lib().dcb_peer_disconnect(acc.handle), acc.handle)
     acc._peers_connected = False
@@ -176,7 +173,9 @@ def disconnect_peers(acc: CudaAccelerator) -> None:
 
 class ShardedQuery:
     """One rank's part of a sharded query. `local` is this rank's shard (a device UnifiedBuffer), `ops` the
-    (kind, lambda) list without the terminal. Collectives run on torch's current stream."""
+    (kind, lambda) list without the terminal."""
+
+    RING = 8     # records in flight: a reduction may be enqueued before the exchange of the one RING steps earlier ended
 
     def __init__(self, accelerator: CudaAccelerator, local: UnifiedBuffer, ops=(), local_second: UnifiedBuffer | None = None,
                  group=None, force_jit: bool = False):
@@ -187,7 +186,15 @@ class ShardedQuery:
         self.group = group
         self.force_jit = force_jit
         self._pipes = {}
-        self._rec = None
+        self._ring = None
+        self._step = 0
+        self._side = None
+        self._kernel_done = None
+        self._exchange_done = None
+
+    @property
+    def fused(self) -> bool:
+        return bool(getattr(self.acc, "_peers_connected", False))
 
     def pipeline(self, terminal: int) -> CompiledPipeline:
         if terminal not in self._pipes:
@@ -196,34 +203,66 @@ class ShardedQuery:
                                                      self.ops + ((terminal, None),), self.force_jit)
         return self._pipes[terminal]
 
-    def record_tensor(self):
+    def _setup(self):
         import torch
-        if self._rec is None:
-            self._rec = torch.zeros(N.SLOT_NSLOTS, dtype=torch.int64, device=f"cuda:{self.acc.DeviceId}")
-        return self._rec
+        if self._ring is None:
+            dev = f"cuda:{self.acc.DeviceId}"
+            self._ring = [torch.zeros(N.SLOT_NSLOTS, dtype=torch.int64, device=dev) for _ in range(self.RING)]
+            self._kernel_done = [torch.cuda.Event() for _ in range(self.RING)]
+            self._exchange_done = [None] * self.RING
+            self._side = torch.cuda.Stream(device=dev)
 
-    def enqueue_reduce(self, terminal: int, stream_ptr: int):
-        """Kernel on `stream_ptr`, then the collective on torch's current stream (which must be that stream). No host
-        synchronisation: returns the device record tensor, combined across ranks once the stream reaches it."""
+    def record_tensor(self):
+        self._setup()
+        return self._ring[0]
+
+    def launch_local(self, terminal: int, stream, rec) -> None:
+        """Only the fused kernel over this rank's shard, on `stream` (a torch stream); its 128-byte record goes to `rec`."""
         pipe = self.pipeline(terminal)
-        rec = self.record_tensor()
         n = self.local.Length if self.second is None else min(self.local.Length, self.second.Length)
         in1 = C.c_void_p(self.second.GetDeviceMemory()) if self.second is not None else None
         N.check(N.lib().dcb_pipeline_run_async(pipe.handle, C.c_void_p(self.local.GetDeviceMemory()), in1, n, None, 0,
-                                               C.c_void_p(rec.data_ptr()), None, C.c_void_p(stream_ptr)), self.acc.handle)
-        if getattr(self.acc, "_peers_connected", False):
-            # The kernel's last block posted this GPU's partial to the peers. The record becomes the global result when the
-            # next reduction on this accelerator runs, or at flush_peers().
-            return rec
-        return combine_record(rec, terminal, pipe.info.out_type, self.group)
+                                               C.c_void_p(rec.data_ptr()), None, C.c_void_p(_stream_handle(stream))), self.acc.handle)
+
+    def exchange(self, terminal: int, stream, rec, slot: int):
+        """Enqueue the combination of `rec` across ranks. Fused: a one-warp kernel on the side stream, gated by an event on
+        `stream`; returns the event that marks the record complete. NCCL: collectives on `stream`; returns None."""
+        import torch
+        pipe = self.pipeline(terminal)
+        if not self.fused:
+            with torch.cuda.stream(stream):
+                combine_record(rec, terminal, pipe.info.out_type, self.group)
+            return None
+        self._kernel_done[slot].record(stream)
+        self._side.wait_event(self._kernel_done[slot])
+        N.check(N.lib().dcb_peer_exchange_async(self.acc.handle, C.c_void_p(rec.data_ptr()), pipe.info.out_type,
+                                                C.c_void_p(_stream_handle(self._side))), self.acc.handle)
+        done = self._exchange_done[slot] or torch.cuda.Event()
+        done.record(self._side)
+        self._exchange_done[slot] = done
+        return done
+
+    def enqueue_reduce(self, terminal: int, stream):
+        """Kernel on `stream`, then the exchange step. No host synchronisation. Returns (record tensor, event or None): the
+        record holds the global result once the event has completed (fused), or once `stream` reaches this point (NCCL)."""
+        self._setup()
+        slot = self._step % self.RING
+        self._step += 1
+        rec = self._ring[slot]
+        if self._exchange_done[slot] is not None:
+            stream.wait_event(self._exchange_done[slot])     # the record's previous use must be over before it is rewritten
+        self.launch_local(terminal, stream, rec)
+        return rec, self.exchange(terminal, stream, rec, slot)
 
     def reduce(self, terminal: int):
         """Run a reduction over all shards and return its scalar (same value on every rank)."""
         import torch
         stream = torch.cuda.current_stream()
-        rec = self.enqueue_reduce(terminal, _stream_handle(stream))
-        if getattr(self.acc, "_peers_connected", False):
-            flush_peers(self.acc, _stream_handle(stream))
+        rec, done = self.enqueue_reduce(terminal, stream)
+        if done is not None:
+            done.synchronize()
+        else:
+            stream.synchronize()
         pipe = self.pipeline(terminal)
         res = finalize_record(rec.cpu().numpy(), terminal, pipe.info.out_type)
         return pipe.scalar(res)

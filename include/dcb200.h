@@ -289,22 +289,22 @@ dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const vo
 
 /* ------------------------------------------------------------------ peer exchange */
 
-/* Fused combine for sharded reductions (one process per GPU). After dcb_peer_connect, every reduction pipeline run on
- * this context exchanges its partial with the other GPUs inside the reduce kernel itself: the kernel's last block stores
- * this GPU's partial into an exchange area in each peer's memory over NVLink and does not wait. The record of a launch is
- * completed (all ranks' partials folded in rank order, bit-identical on every GPU) by the NEXT reduction launched on the
- * context, or by dcb_peer_flush; dcb_pipeline_run (the blocking call) flushes by itself. So for a stream of queries neither
- * NVLink latency nor the skew between GPUs is on the critical path, and no separate collective is launched. All ranks must
- * run the same sequence of reductions. A peer that never arrives ends a (bounded) wait with DCB_RES_TIMEOUT in the record.
+/* Exchange of partials for sharded reductions (one process per GPU), without NCCL: dcb_peer_exchange_async enqueues a
+ * one-warp kernel that stores this GPU's partial (the record a reduction just wrote) into an exchange area in each peer's
+ * memory over NVLink, waits (bounded) for the peers' partials in its own area, folds all of them in rank order, so every GPU
+ * computes the bit-identical total, and rewrites the record with the global result. Enqueue it on a side stream behind the
+ * reduction (an event) and it runs beside the next query's reduce kernel, so neither NVLink latency nor the skew between GPUs
+ * is on the critical path of a stream of queries; dcb_pipeline_run (the blocking call) enqueues it on its own stream. All
+ * ranks must issue the same sequence of exchanges. A peer that never arrives ends the wait with DCB_RES_TIMEOUT in the record.
  * The reference has no multi-GPU LINQ path (device 0 only, src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:188);
  * its P2P manager only copies buffers (src/Backends/DotCompute.Backends.CUDA/P2P/CudaP2PManager.cs:137-242).
- *   dcb_peer_area_create  allocates this GPU's 2 KiB exchange area and writes its 64-byte CUDA IPC handle to handle_out
- *   dcb_peer_connect      handles = world handles, handle_stride bytes apart, gathered from all ranks (index = rank)
- *   dcb_peer_flush        enqueue the completion of the newest launch's record on `stream`
- *   dcb_peer_disconnect   back to single-GPU behaviour */
+ *   dcb_peer_area_create     allocates this GPU's 2 KiB exchange area and writes its 64-byte CUDA IPC handle to handle_out
+ *   dcb_peer_connect         handles = world handles, handle_stride bytes apart, gathered from all ranks (index = rank)
+ *   dcb_peer_exchange_async  d_record: the 128-byte device record of the reduction; out_type: DCB_T_* that reached its terminal
+ *   dcb_peer_disconnect      back to single-GPU behaviour */
 dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_t handle_cap);
 dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank, const void* handles, size_t handle_stride);
-dcb_status dcb_peer_flush(dcb_ctx* ctx, void* stream);
+dcb_status dcb_peer_exchange_async(dcb_ctx* ctx, void* d_record, int32_t out_type, void* stream);
 dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
 
 /* ------------------------------------------------------------- no device allocation */
