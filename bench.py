@@ -146,6 +146,8 @@ def parse_args():
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the result")
     ap.add_argument("--combine", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange of partial sums: inside the reduce kernel over NVLink peer stores (fused) or an NCCL all-reduce")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="enqueue the timed steps one by one instead of replaying them as one captured CUDA graph")
     ap.add_argument("--profile", action="store_true",
                     help="minimal run for a profiler: no clock spin, no e2e, no CPU baseline, no oracle check")
     ap.add_argument("--workload", default="c5-sum", choices=sorted(CONFIG_WORKLOADS) + ["c5-sum"],
@@ -373,31 +375,68 @@ def main() -> int:
                 q.enqueue_reduce(N.OP_SUM, stream)
             stream.synchronize()
         barrier()
-        # ---- timed region: K steps, device-resident; events around the whole region and around every kernel
+        # ---- timed region: K steps, device-resident
+        q._setup()
+
+        def run_steps(k_start=None, k_stop=None):
+            """K steps: the fused kernel over this rank's shard, then the exchange of the partial. Returns the last record."""
+            last, rec = None, None
+            for i in range(args.steps):
+                slot = q._step % q.RING
+                q._step += 1
+                rec = q._ring[slot]
+                if q._exchange_done[slot] is not None:
+                    stream.wait_event(q._exchange_done[slot])
+                if k_start is not None:
+                    k_start[i].record(stream)
+                q.launch_local(N.OP_SUM, stream, rec)           # the fused Where->Select->Sum kernel
+                if k_stop is not None:
+                    k_stop[i].record(stream)
+                last = q.exchange(N.OP_SUM, stream, rec, slot)   # side-stream NVLink exchange (fused) or NCCL all-reduce
+            if last is not None:
+                stream.wait_event(last)                          # the region ends when the last record is global
+            return rec
+
+        t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        graph = None
+        if not args.no_graph and (world == 1 or fused):
+            # The K steps are captured once as a CUDA graph (kernels, events and the side stream's exchange kernels) and
+            # the timed region replays it: no per-launch host work between kernels.
+            try:
+                q._step = 0
+                q._exchange_done = [None] * q.RING
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    rec = run_steps()
+                graph.replay()                                   # one untimed replay (graph upload)
+                barrier()
+            except Exception as exc:                             # capture refused: fall back to plain launches
+                print(f"bench.py: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+                graph = None
+                torch.cuda.synchronize()
+                q._exchange_done = [None] * q.RING
+        launches0 = acc.LaunchCount
+        if graph is not None:
+            with torch.cuda.stream(stream):
+                t_begin.record(stream)
+                graph.replay()
+                t_end.record(stream)
+            graph_launches = args.steps * (2 if fused else 1)
+        else:
+            t_begin.record(stream)
+            rec = run_steps()
+            t_end.record(stream)
+        barrier()
+        total_ms = t_begin.elapsed_time(t_end)
+        # Second pass of the same K steps, launched one by one with CUDA events around every kernel: the per-launch
+        # duration the roofline figure is computed from (events cannot be timed inside a replayed graph).
         k_start = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         k_stop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = acc.LaunchCount
-        q._setup()
-        t_begin.record(stream)
-        last = None
-        for i in range(args.steps):
-            slot = q._step % q.RING
-            q._step += 1
-            rec = q._ring[slot]
-            if q._exchange_done[slot] is not None:
-                stream.wait_event(q._exchange_done[slot])
-            k_start[i].record(stream)
-            q.launch_local(N.OP_SUM, stream, rec)          # the fused Where->Select->Sum kernel over this rank's shard
-            k_stop[i].record(stream)
-            last = q.exchange(N.OP_SUM, stream, rec, slot)  # side-stream NVLink exchange (fused) or NCCL all-reduce
-        if last is not None:
-            stream.wait_event(last)                         # the timed region ends when the last record is global
-        t_end.record(stream)
+        q._exchange_done = [None] * q.RING
+        rec = run_steps(k_start, k_stop)
         barrier()
-        launches = acc.LaunchCount - launches0
+        launches = graph_launches if graph is not None else (acc.LaunchCount - launches0) // 2
         clocks = sampler.stop() if sampler else None
-        total_ms = t_begin.elapsed_time(t_end)
         kernel_ms = [a.elapsed_time(b) for a, b in zip(k_start, k_stop)]
         rec_host = rec.cpu().numpy().copy()
 
@@ -470,9 +509,11 @@ def main() -> int:
                        "combine": ("none (1 GPU)" if world == 1 else
                                    "one-warp exchange kernel on a side stream: NVLink peer stores of the fp64 partials, fold in rank order, overlapped with the next step's kernel" if fused else
                                    "NCCL all-reduce of one fp64 partial per GPU"),
-                       "precompiled_kernel": bool(pipe.precompiled)},
+                       "precompiled_kernel": bool(pipe.precompiled),
+                       "launch": "the K steps are replayed as one CUDA graph" if graph is not None else "K plain launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_kind": peak_kind, "kernel": "dcb_reduce_vec (fused Where->Select->Sum)",
+                         "timing": "mean of per-launch CUDA-event durations over a second, un-graphed pass of the same K steps",
                          "kernel_ms": kernel_ms_mean, "frac_of_nominal_8TBs": achieved / 8000.0},
             "gpu_launches": int(launches),
             "clocks": clocks,
