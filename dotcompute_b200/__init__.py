@@ -7,6 +7,7 @@ sm_100a CUDA; there is no CPU or PyTorch path behind these names.
 from .errors import (ArgumentException, ArgumentNullException, CudaErrorClass, CudaException, DotComputeException,
                      InvalidOperationException, NotSupportedException, ObjectDisposedException, OverflowException)
 from .accelerator import BufferState, CudaAccelerator, CudaMemoryManager, PinnedArray, UnifiedBuffer
+from .orchestrator import ComputeOrchestrator, KernelParam, KernelRegistrationInfo, KernelRegistry, translate_kernel_method
 from .linq import (AsComputeQueryable, CompiledPipeline, ComputeLinqProvider, ComputeQueryable, ToComputeArray,
                    generate_source, translate_lambda)
 
@@ -16,4 +17,5 @@ __all__ = [
     "BufferState", "CudaAccelerator", "CudaMemoryManager", "PinnedArray", "UnifiedBuffer",
     "AsComputeQueryable", "CompiledPipeline", "ComputeLinqProvider", "ComputeQueryable", "ToComputeArray",
     "generate_source", "translate_lambda",
+    "ComputeOrchestrator", "KernelParam", "KernelRegistrationInfo", "KernelRegistry", "translate_kernel_method",
 ]

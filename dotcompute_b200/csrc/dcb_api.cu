@@ -615,6 +615,32 @@ extern "C" dcb_status dcb_translate_lambda(const char* lambda, const int32_t* pa
     return DCB_OK;
 }
 
+extern "C" dcb_status dcb_translate_kernel_method(const char* csharp_method, char* cuda_out, size_t cuda_cap, size_t* cuda_needed,
+                                                  char* meta_json, size_t meta_cap, char* err, size_t err_cap) {
+    if (err && err_cap) err[0] = '\0';
+    if (!csharp_method) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "csharp_method is null");
+    dcbt::KernelMethod km;
+    std::string e;
+    if (!dcbt::translate_kernel_method(csharp_method, &km, &e)) {
+        if (err && err_cap) snprintf(err, err_cap, "%s", e.c_str());
+        return set_err(nullptr, DCB_ERR_NOT_SUPPORTED, "%s", e.c_str());
+    }
+    if (cuda_needed) *cuda_needed = km.cuda_source.size() + 1;
+    if (cuda_out && cuda_cap) snprintf(cuda_out, cuda_cap, "%s", km.cuda_source.c_str());
+    if (meta_json && meta_cap) {
+        std::string j = "{\"name\": \"" + km.name + "\", \"needs_length\": " + (km.needs_length ? "true" : "false") +
+                        ", \"dimensions\": " + std::to_string(km.dimensions) + ", \"params\": [";
+        for (size_t i = 0; i < km.params.size(); ++i) {
+            const auto& p = km.params[i];
+            j += std::string(i ? ", " : "") + "{\"name\": \"" + p.name + "\", \"is_buffer\": " + (p.is_buffer ? "true" : "false") +
+                 ", \"is_readonly\": " + (p.is_readonly ? "true" : "false") + ", \"element_type\": \"" + dcbt::csharp_name(p.elem_type) + "\"}";
+        }
+        j += "]}";
+        snprintf(meta_json, meta_cap, "%s", j.c_str());
+    }
+    return DCB_OK;
+}
+
 extern "C" dcb_status dcb_pipeline_generate_source(const dcb_pipeline_desc* desc, char* buf, size_t cap, size_t* needed,
                                                    char* err, size_t err_cap) {
     char e[512] = "";

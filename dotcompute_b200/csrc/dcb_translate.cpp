@@ -79,7 +79,7 @@ static bool lex(const std::string& s, std::vector<Tok>* out, std::string* err) {
             t.kind = Tok::IDENT; t.text = s.substr(i, j - i); i = j;
         } else {
             static const char* three[] = {">>>", nullptr};
-            static const char* two[] = {"=>", "==", "!=", "<=", ">=", "&&", "||", "<<", ">>", nullptr};
+            static const char* two[] = {"=>", "==", "!=", "<=", ">=", "&&", "||", "<<", ">>", "+=", "-=", "*=", "/=", "%=", "&=", "|=", "^=", "++", "--", nullptr};
             t.kind = Tok::PUNCT;
             bool done = false;
             for (int k = 0; three[k] && !done; ++k)
@@ -87,7 +87,7 @@ static bool lex(const std::string& s, std::vector<Tok>* out, std::string* err) {
             for (int k = 0; two[k] && !done; ++k)
                 if (s.compare(i, 2, two[k]) == 0) { t.text = two[k]; i += 2; done = true; }
             if (!done) {
-                if (strchr("+-*/%&|^~!<>?:(),.", c) == nullptr) { *err = std::string("unexpected character '") + c + "'"; return false; }
+                if (strchr("+-*/%&|^~!<>?:(),.;{}[]=", c) == nullptr) { *err = std::string("unexpected character '") + c + "'"; return false; }
                 t.text = std::string(1, c); ++i;
             }
         }
@@ -103,6 +103,8 @@ struct Node {
     int type = T_NONE;
     bool const_int = false;       // an int-typed constant expression (C# lets it narrow implicitly when it fits)
     long long cval = 0;
+    bool is_buffer = false;       // a Span<T> / T[] kernel parameter: `type` is its element type, only a[i] and a.Length are allowed
+    bool is_lvalue = false;       // may stand on the left of an assignment
 };
 
 static std::string conv(const Node& n, int to) {
@@ -199,7 +201,22 @@ class Parser {
         if (!ok) *err = err_.empty() ? "syntax error" : err_;
         return ok;
     }
+    // Parse one expression starting at pos_ and stop behind it (statement parsers look at the delimiter themselves).
+    bool parse_expr(Node* out, std::string* err) {
+        bool ok = ternary(out);
+        if (!ok) *err = err_.empty() ? "syntax error" : err_;
+        return ok;
+    }
+    bool binop(const std::string& op, const Node& a, const Node& b, Node* r, std::string* err) {
+        bool ok = apply_binary(op, a, b, r);
+        if (!ok) *err = err_.empty() ? "bad operands" : err_;
+        return ok;
+    }
     size_t pos_ = 0;
+    bool kernel_mode = false;        // accept KernelContext.* and buffer.Length
+    bool thread_id_is_global = false; // ThreadId.X means the global index (body never names BlockId / BlockDim / GridDim)
+    bool used_length = false;
+    int max_dim = 1;
 
   private:
     const std::vector<Tok>& t_;
@@ -453,7 +470,39 @@ class Parser {
         ++pos_;
         if (id == "true" || id == "false") { out->type = T_BOOL; out->code = id; return true; }
         auto it = params_.find(id);
+        if (it != params_.end() && it->second.is_buffer) {
+            const Node& buf = it->second;
+            if (accept("[")) {
+                Node idx;
+                if (!ternary(&idx) || !expect("]")) return false;
+                if (!is_integral(idx.type)) return fail("an index must be an integer");
+                out->type = buf.type; out->is_lvalue = true;
+                out->code = buf.code + "[" + idx.code + "]";
+                return true;
+            }
+            if (is_punct(".") && peek(1).kind == Tok::IDENT && peek(1).text == "Length") {
+                pos_ += 2; used_length = true;
+                out->type = T_I32; out->code = "((int)__length)";
+                return true;
+            }
+            return fail("buffer '" + id + "' can only be indexed or asked for its Length");
+        }
         if (it != params_.end() && !is_punct(".")) { *out = it->second; return true; }
+        if (kernel_mode && (id == "KernelContext" || id == "Kernel") && is_punct(".") && peek(1).kind == Tok::IDENT &&
+            is_punct(".", 2) && peek(3).kind == Tok::IDENT) {
+            const std::string what = peek(1).text, axis = peek(3).text;
+            const char* intr = what == "ThreadId" ? "threadIdx" : what == "BlockId" ? "blockIdx" : what == "BlockDim" ? "blockDim" : what == "GridDim" ? "gridDim" : nullptr;
+            if (intr && (axis == "X" || axis == "Y" || axis == "Z")) {
+                pos_ += 4;
+                const std::string a = axis == "X" ? "x" : axis == "Y" ? "y" : "z";
+                if (axis == "Y") max_dim = std::max(max_dim, 2);
+                if (axis == "Z") max_dim = std::max(max_dim, 3);
+                out->type = T_I32;
+                if (what == "ThreadId" && thread_id_is_global) out->code = "((int)(blockIdx." + a + " * blockDim." + a + " + threadIdx." + a + "))";
+                else out->code = std::string("((int)") + intr + "." + a + ")";
+                return true;
+            }
+        }
         if (id == "System" && is_punct(".")) { ++pos_; if (peek().kind != Tok::IDENT) return fail("bad qualified name"); id = peek().text; ++pos_; }
         if (is_punct(".") && peek(1).kind == Tok::IDENT) {
             std::string member = peek(1).text;
@@ -616,6 +665,240 @@ bool translate_lambda(const std::string& lambda, const std::vector<std::string>&
     Node r;
     if (!p.parse(&r, err)) return false;
     *code = r.code; *result_type = r.type;
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------- [Kernel] methods
+namespace {
+
+struct MethodTranslator {
+    const std::vector<Tok>& t;
+    std::map<std::string, Node> syms;
+    Parser ex;
+    std::string err;
+    std::string body;
+
+    MethodTranslator(const std::vector<Tok>& toks) : t(toks), ex(toks, syms) { ex.kernel_mode = true; }
+
+    const Tok& peek(size_t k = 0) const { return t[std::min(ex.pos_ + k, t.size() - 1)]; }
+    bool is_p(const char* p, size_t k = 0) const { return peek(k).kind == Tok::PUNCT && peek(k).text == p; }
+    bool is_id(const char* p, size_t k = 0) const { return peek(k).kind == Tok::IDENT && peek(k).text == p; }
+    bool accept(const char* p) { if (is_p(p)) { ++ex.pos_; return true; } return false; }
+    bool fail(const std::string& m) { if (err.empty()) err = m; return false; }
+    bool expect(const char* p) { return accept(p) ? true : fail(std::string("expected '") + p + "' near '" + peek().text + "'"); }
+    bool expr(Node* n) { std::string e; if (!ex.parse_expr(n, &e)) return fail(e); return true; }
+
+    static int scalar_type(const std::string& s) {
+        static const std::map<std::string, int> m = {{"sbyte", T_I8}, {"byte", T_U8}, {"short", T_I16}, {"ushort", T_U16}, {"int", T_I32},
+            {"uint", T_U32}, {"long", T_I64}, {"ulong", T_U64}, {"float", T_F32}, {"double", T_F64}, {"bool", T_BOOL}};
+        auto it = m.find(s);
+        return it == m.end() ? T_NONE : it->second;
+    }
+
+    bool assign_to(const Node& lhs, const std::string& op, const Node& rhs, std::string* out) {
+        if (!lhs.is_lvalue) return fail("the left side of an assignment must be a variable or a buffer element");
+        if (op == "=") {
+            if (lhs.type == T_BOOL || rhs.type == T_BOOL) {
+                if (lhs.type != rhs.type) return fail("cannot convert between bool and a number");
+                *out = lhs.code + " = " + rhs.code; return true;
+            }
+            if (rhs.type != lhs.type && !implicit_ok(rhs.type, lhs.type) && !(rhs.const_int && const_fits(rhs.cval, lhs.type)))
+                return fail(std::string("cannot implicitly convert ") + csharp_name(rhs.type) + " to " + csharp_name(lhs.type));
+            *out = lhs.code + " = " + conv(rhs, lhs.type);
+            return true;
+        }
+        Node r; std::string e;
+        if (!ex.binop(op.substr(0, op.size() - 1), lhs, rhs, &r, &e)) return fail(e);
+        *out = lhs.code + " = " + conv(r, lhs.type);   // a compound assignment casts back to the left type, as in C#
+        return true;
+    }
+
+    // expression statement without the trailing ';' (also used for the init / increment parts of a for loop)
+    bool simple(std::string* out) {
+        if (is_p("++") || is_p("--")) {
+            const std::string op = peek().text; ++ex.pos_;
+            Node v; if (!expr(&v)) return false;
+            Node one; one.type = T_I32; one.code = "1"; one.const_int = true; one.cval = 1;
+            return assign_to(v, op == "++" ? "+=" : "-=", one, out);
+        }
+        Node lhs; if (!expr(&lhs)) return false;
+        if (is_p("++") || is_p("--")) {
+            const std::string op = peek().text; ++ex.pos_;
+            Node one; one.type = T_I32; one.code = "1"; one.const_int = true; one.cval = 1;
+            return assign_to(lhs, op == "++" ? "+=" : "-=", one, out);
+        }
+        static const char* ops[] = {"=", "+=", "-=", "*=", "/=", "%=", "&=", "|=", "^=", nullptr};
+        for (int i = 0; ops[i]; ++i) {
+            if (is_p(ops[i])) {
+                ++ex.pos_;
+                Node rhs; if (!expr(&rhs)) return false;
+                return assign_to(lhs, ops[i], rhs, out);
+            }
+        }
+        return fail("only assignments, ++ and -- can be used as statements");
+    }
+
+    bool declaration(std::string* out) {
+        const std::string tname = peek().text; ++ex.pos_;
+        int ty = tname == "var" ? T_NONE : scalar_type(tname);
+        std::string s;
+        while (true) {
+            if (peek().kind != Tok::IDENT) return fail("expected a variable name");
+            const std::string name = peek().text; ++ex.pos_;
+            if (syms.count(name)) return fail("'" + name + "' is already defined");
+            Node v; v.code = name; v.is_lvalue = true;
+            if (accept("=")) {
+                Node init; if (!expr(&init)) return false;
+                v.type = ty == T_NONE ? init.type : ty;
+                std::string a;
+                if (!assign_to(v, "=", init, &a)) return false;
+                s += std::string(cuda_name(v.type)) + " " + a + ";";
+            } else {
+                if (ty == T_NONE) return fail("a 'var' declaration needs an initialiser");
+                v.type = ty;
+                s += std::string(cuda_name(ty)) + " " + name + ";";
+            }
+            syms[name] = v;
+            if (!accept(",")) break;
+            s += " ";
+        }
+        *out = s;
+        return true;
+    }
+
+    bool statement(int depth) {
+        const std::string ind((size_t)depth * 4, ' ');
+        if (accept("{")) {
+            const std::map<std::string, Node> outer = syms;    // names declared inside the block end with it
+            body += ind + "{\n";
+            while (!is_p("}")) { if (peek().kind == Tok::END) return fail("missing '}'"); if (!statement(depth + 1)) return false; }
+            ++ex.pos_;
+            body += ind + "}\n";
+            syms = outer;
+            return true;
+        }
+        if (is_id("if")) {
+            ++ex.pos_;
+            Node c; if (!expect("(") || !expr(&c) || !expect(")")) return false;
+            if (c.type != T_BOOL) return fail("the condition of 'if' must be bool");
+            body += ind + "if (" + c.code + ")\n";
+            if (!statement(is_p("{") ? depth : depth + 1)) return false;
+            if (is_id("else")) {
+                ++ex.pos_;
+                body += ind + "else\n";
+                if (!statement(is_p("{") || is_id("if") ? depth : depth + 1)) return false;
+            }
+            return true;
+        }
+        if (is_id("while")) {
+            ++ex.pos_;
+            Node c; if (!expect("(") || !expr(&c) || !expect(")")) return false;
+            if (c.type != T_BOOL) return fail("the condition of 'while' must be bool");
+            body += ind + "while (" + c.code + ")\n";
+            return statement(is_p("{") ? depth : depth + 1);
+        }
+        if (is_id("for")) {
+            ++ex.pos_;
+            if (!expect("(")) return false;
+            const std::map<std::string, Node> outer = syms;    // the loop variable ends with the loop
+            struct Restore { std::map<std::string, Node>& s; const std::map<std::string, Node>& o; ~Restore() { s = o; } } restore{syms, outer};
+            std::string init, cond, inc;
+            if (!is_p(";")) {
+                if (peek().kind == Tok::IDENT && (peek().text == "var" || scalar_type(peek().text) != T_NONE) && peek(1).kind == Tok::IDENT) {
+                    if (!declaration(&init)) return false;
+                    init.pop_back();   // drop the ';' the declaration printed
+                } else if (!simple(&init)) return false;
+            }
+            if (!expect(";")) return false;
+            if (!is_p(";")) { Node c; if (!expr(&c)) return false; if (c.type != T_BOOL) return fail("the condition of 'for' must be bool"); cond = c.code; }
+            if (!expect(";")) return false;
+            if (!is_p(")")) { if (!simple(&inc)) return false; }
+            if (!expect(")")) return false;
+            body += ind + "for (" + init + "; " + cond + "; " + inc + ")\n";
+            return statement(is_p("{") ? depth : depth + 1);
+        }
+        if (is_id("return")) {
+            ++ex.pos_;
+            if (!expect(";")) return fail("a kernel returns nothing");
+            body += ind + "return;\n";
+            return true;
+        }
+        if (peek().kind == Tok::IDENT && (peek().text == "var" || scalar_type(peek().text) != T_NONE) && peek(1).kind == Tok::IDENT) {
+            std::string d; if (!declaration(&d) || !expect(";")) return false;
+            body += ind + d + "\n";
+            return true;
+        }
+        std::string st; if (!simple(&st) || !expect(";")) return false;
+        body += ind + st + ";\n";
+        return true;
+    }
+};
+
+}  // namespace
+
+bool translate_kernel_method(const std::string& csharp, KernelMethod* out, std::string* err) {
+    std::vector<Tok> toks;
+    if (!lex(csharp, &toks, err)) return false;
+    MethodTranslator m(toks);
+    size_t& pos = m.ex.pos_;
+    // [Kernel(...)] attributes, then modifiers, then `void Name(`
+    while (m.is_p("[")) {
+        int depth = 0;
+        do { if (m.is_p("[")) ++depth; if (m.is_p("]")) --depth; if (m.peek().kind == Tok::END) { *err = "unterminated attribute"; return false; } ++pos; } while (depth > 0);
+    }
+    while (m.is_id("public") || m.is_id("private") || m.is_id("internal") || m.is_id("static") || m.is_id("unsafe") || m.is_id("protected")) ++pos;
+    if (!m.is_id("void")) { *err = "a [Kernel] method must be 'static void'"; return false; }
+    ++pos;
+    if (m.peek().kind != Tok::IDENT) { *err = "expected the method name"; return false; }
+    out->name = m.peek().text; ++pos;
+    if (!m.expect("(")) { *err = m.err; return false; }
+    std::string sig;
+    while (!m.is_p(")")) {
+        if (m.is_id("in") || m.is_id("ref") || m.is_id("out") || m.is_id("this")) ++pos;
+        if (m.peek().kind != Tok::IDENT) { *err = "bad parameter list"; return false; }
+        std::string tname = m.peek().text; ++pos;
+        KernelParam kp;
+        int elem = T_NONE;
+        const bool generic = tname == "ReadOnlySpan" || tname == "Span" || tname == "ReadOnlyMemory" || tname == "Memory" ||
+                             tname == "IUnifiedMemoryBuffer" || tname == "UnifiedBuffer";
+        if (generic) {
+            if (!m.expect("<") || m.peek().kind != Tok::IDENT) { *err = "bad generic parameter type"; return false; }
+            elem = MethodTranslator::scalar_type(m.peek().text); ++pos;
+            if (!m.expect(">")) { *err = m.err; return false; }
+            kp.is_buffer = true;
+            kp.is_readonly = tname == "ReadOnlySpan" || tname == "ReadOnlyMemory";
+        } else {
+            elem = MethodTranslator::scalar_type(tname);
+            if (m.is_p("[") && m.is_p("]", 1)) { pos += 2; kp.is_buffer = true; kp.is_readonly = false; }
+        }
+        if (elem == T_NONE) { *err = "parameter type '" + tname + "' is not supported in a CUDA kernel"; return false; }
+        if (m.peek().kind != Tok::IDENT) { *err = "expected a parameter name"; return false; }
+        kp.name = m.peek().text; ++pos;
+        kp.elem_type = elem;
+        Node n; n.code = kp.name; n.type = elem; n.is_buffer = kp.is_buffer; n.is_lvalue = !kp.is_buffer;
+        m.syms[kp.name] = n;
+        if (!sig.empty()) sig += ", ";
+        if (kp.is_buffer) sig += std::string(kp.is_readonly ? "const " : "") + cuda_name(elem) + "* " + kp.name;
+        else sig += std::string(cuda_name(elem)) + " " + kp.name;
+        out->params.push_back(kp);
+        if (!m.accept(",")) break;
+    }
+    if (!m.expect(")")) { *err = m.err; return false; }
+    // In DotCompute's CPU invoker ThreadId is the global work-item index (BlockId reads 0). A body that never names BlockId,
+    // BlockDim or GridDim therefore means the global index by ThreadId; spelled with block arithmetic it is taken literally.
+    bool names_blocks = false;
+    for (const Tok& tk : toks) if (tk.kind == Tok::IDENT && (tk.text == "BlockId" || tk.text == "BlockDim" || tk.text == "GridDim")) names_blocks = true;
+    m.ex.thread_id_is_global = !names_blocks;
+    if (!m.is_p("{")) { *err = "expected the method body"; return false; }
+    ++pos;
+    while (!m.is_p("}")) {
+        if (m.peek().kind == Tok::END) { *err = "missing '}' at the end of the method"; return false; }
+        if (!m.statement(1)) { *err = m.err; return false; }
+    }
+    out->needs_length = m.ex.used_length;
+    out->dimensions = m.ex.max_dim;
+    if (out->needs_length) sig += std::string(sig.empty() ? "" : ", ") + "const unsigned int __length";
+    out->cuda_source = "extern \"C\" __global__ void " + out->name + "(" + sig + ") {\n" + m.body + "}\n";
     return true;
 }
 

@@ -28,6 +28,19 @@ bool is_numeric(int type);
 bool translate_lambda(const std::string& lambda, const std::vector<std::string>& args, const std::vector<int>& arg_types,
                       std::string* code, int* result_type, std::string* err);
 
+// A [Kernel] method (C# source text of one static void method) translated to CUDA C. Takes the place of
+// KernelExecutionMetadataEmitter.GenerateCuda / DetectDimensions
+// (src/Runtime/DotCompute.Generators/Kernel/Generation/KernelExecutionMetadataEmitter.cs:31-105, 275-436).
+struct KernelParam { std::string name; bool is_buffer = false; bool is_readonly = false; int elem_type = T_NONE; };
+struct KernelMethod {
+    std::string name;            // also the CUDA entry point
+    std::string cuda_source;     // extern "C" __global__ void name(...) { ... }
+    bool needs_length = false;   // the body read a buffer's .Length: a trailing `const unsigned int __length` was added
+    int dimensions = 1;          // 1, 2 or 3 (highest KernelContext axis used)
+    std::vector<KernelParam> params;
+};
+bool translate_kernel_method(const std::string& csharp, KernelMethod* out, std::string* err);
+
 struct OpSpec { int kind; std::string lambda; };   // kind = DCB_OP_*
 
 struct ChainInfo {

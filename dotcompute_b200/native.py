@@ -81,6 +81,7 @@ PROTOTYPES = {
     "dcb_unpin_host": (_i32, [_vp, _vp]),
     "dcb_memory_stats": (_i32, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "dcb_translate_lambda": (_i32, [C.c_char_p, C.POINTER(_i32), _i32, C.c_char_p, _sz, C.POINTER(_i32), C.c_char_p, _sz]),
+    "dcb_translate_kernel_method": (_i32, [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz), C.c_char_p, _sz, C.c_char_p, _sz]),
     "dcb_pipeline_compile": (_i32, [_vp, C.POINTER(PipelineDesc), _pp]),
     "dcb_pipeline_destroy": (_i32, [_vp]),
     "dcb_pipeline_info_get": (_i32, [_vp, C.POINTER(PipelineInfo)]),

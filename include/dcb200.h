@@ -237,6 +237,18 @@ dcb_status dcb_translate_lambda(const char* lambda, const int32_t* param_types, 
                                 char* out_code, size_t out_cap, int32_t* result_type,
                                 char* err, size_t err_cap);
 
+/* Translate one [Kernel] method (C# source of a `static void` method over Span<T> / ReadOnlySpan<T> / T[] buffers and scalars)
+ * to CUDA C. Replaces KernelExecutionMetadataEmitter.GenerateCuda / DetectDimensions
+ * (src/Runtime/DotCompute.Generators/Kernel/Generation/KernelExecutionMetadataEmitter.cs:31-105, 275-436). Statements: local
+ * declarations, assignments (also compound, ++, --), blocks, if / else, for, while, bare return; expressions as in lambdas plus
+ * buffer[i], buffer.Length (becomes a trailing `const unsigned int __length` parameter, as in the reference) and
+ * KernelContext.{ThreadId,BlockId,BlockDim,GridDim}.{X,Y,Z}. A body that names only ThreadId gets the global index for it, which is
+ * what the reference's CPU invoker gives it (KernelExecutionMetadataEmitter.cs:117-170). meta_json receives
+ * {"name", "needs_length", "dimensions", "params": [{"name", "is_buffer", "is_readonly", "element_type"}]}, the fields of the
+ * reference's generated registry entry (KernelRegistrationEmitter.cs:56-192). Needs no GPU. */
+dcb_status dcb_translate_kernel_method(const char* csharp_method, char* cuda_out, size_t cuda_cap, size_t* cuda_needed,
+                                       char* meta_json, size_t meta_cap, char* err, size_t err_cap);
+
 /* Build the fused kernels of a query. Replaces CompilationPipeline.CompileToGpuKernelAsync ->
  * CudaRuntimeKernelCompiler.CompileFromGraphAsync -> CudaKernelGenerator.GenerateCudaKernel -> NVRTC
  * (src/Extensions/DotCompute.Linq/CodeGeneration/CompilationPipeline.cs:914-965,
