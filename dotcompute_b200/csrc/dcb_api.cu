@@ -435,6 +435,8 @@ extern "C" dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls) {
     if (st) return st;
     NEED(ctx, max_polls > 0, "max_polls must be positive");
     ctx->spin_limit = max_polls;
+    ctx->peer_spin_limit = max_polls;
+    ctx->peers.spin_limit = max_polls;
     return DCB_OK;
 }
 
@@ -846,9 +848,13 @@ extern "C" dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, co
     const uint64_t fl = d->flags;
     if (fl & dcb::FLAG_SAW_NAN) r->flags |= DCB_RES_SAW_NAN;
     const bool fp = out_type == DCB_T_F32 || out_type == DCB_T_F64;
+    if (fl & dcb::FLAG_TIMEOUT) {
+        r->flags |= DCB_RES_TIMEOUT;
+        return set_err(ctx, DCB_ERR_TIMEOUT, terminal == DCB_OP_TOARRAY ? "a look-back wait in the compaction kernel ran out"
+                                                                        : "a peer's partial did not arrive in time");
+    }
     switch (terminal) {
         case DCB_OP_TOARRAY:
-            if (fl & dcb::FLAG_TIMEOUT) { r->flags |= DCB_RES_TIMEOUT; return set_err(ctx, DCB_ERR_TIMEOUT, "a look-back wait in the compaction kernel ran out"); }
             if (fl & dcb::FLAG_TRUNCATED) { r->flags |= DCB_RES_TRUNCATED; return set_err(ctx, DCB_ERR_OUTPUT_TOO_SMALL, "%lld elements survive, the output holds fewer", (long long)d->count); }
             return DCB_OK;
         case DCB_OP_COUNT:
@@ -1080,10 +1086,19 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
 }
 
 // ===================================================================================== peer exchange
+static dcb_status ensure_peer_area(dcb_ctx* ctx);
 extern "C" dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_t handle_cap) {
     dcb_status st = use(ctx);
     if (st) return st;
     NEED(ctx, handle_out != nullptr && handle_cap >= sizeof(cudaIpcMemHandle_t), "handle buffer must hold 64 bytes");
+    if ((st = ensure_peer_area(ctx))) return st;
+    cudaIpcMemHandle_t h;
+    CU(ctx, cudaIpcGetMemHandle(&h, ctx->peer_area));
+    memcpy(handle_out, &h, sizeof h);
+    return DCB_OK;
+}
+
+static dcb_status ensure_peer_area(dcb_ctx* ctx) {
     if (!ctx->peer_area) {
         const size_t bytes = sizeof(dcb::PeerSlot) * dcb::PEER_RING * dcb::PEER_MAX;
         CU(ctx, cudaMalloc(&ctx->peer_area, bytes));
@@ -1092,9 +1107,34 @@ extern "C" dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_
         CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
         CU(ctx, cudaDeviceSynchronize());
     }
-    cudaIpcMemHandle_t h;
-    CU(ctx, cudaIpcGetMemHandle(&h, ctx->peer_area));
-    memcpy(handle_out, &h, sizeof h);
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_peer_area_ptr(dcb_ctx* ctx, void** out_area, size_t* out_bytes) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_area != nullptr, "out_area is null");
+    if ((st = ensure_peer_area(ctx))) return st;
+    *out_area = ctx->peer_area;
+    if (out_bytes) *out_bytes = sizeof(dcb::PeerSlot) * dcb::PEER_RING * dcb::PEER_MAX;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_peer_connect_local(dcb_ctx* ctx, int32_t world, int32_t rank, void* const* areas) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, world >= 1 && world <= dcb::PEER_MAX, "world must be between 1 and 8");
+    NEED(ctx, rank >= 0 && rank < world, "rank outside the world");
+    NEED(ctx, areas != nullptr, "areas is null");
+    if ((st = ensure_peer_area(ctx))) return st;
+    dcb::PeerTable t = {};
+    t.world = world; t.rank = rank; t.spin_limit = ctx->peer_spin_limit; t.state = (dcb::PeerState*)ctx->peer_state;
+    CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
+    for (int r = 0; r < world; ++r) {
+        NEED(ctx, areas[r] != nullptr, "an area pointer is null");
+        t.area[r] = (dcb::PeerSlot*)(r == rank ? ctx->peer_area : areas[r]);
+    }
+    ctx->peers = t;
     return DCB_OK;
 }
 

@@ -487,62 +487,22 @@ template <class C, int BLOCK, bool VEC> struct compact_rows {
     static constexpr int value = compact_rows_for(BLOCK, pack_elems<C, VEC>::value, (int)sizeof(typename C::out_t));
 };
 
-// Tile = BLOCK threads; each warp owns ROWS rows of 32 packs, a contiguous run of ROWS*32*E elements. Element order
-// inside a warp's run is row, then lane, then position in the pack; ranks follow it, so the output keeps source order.
-//
-// One tile per block, tile id = blockIdx.x. The look-back waits on tiles with smaller ids, i.e. on blocks the hardware
-// dispatched earlier (a 1-D grid is dispatched in index order; NVIDIA's own single-pass scan relies on the same). Should
-// that ever not hold, the bounded polls below end the launch with FLAG_TIMEOUT instead of hanging the GPU.
-template <class C, int BLOCK, int ROWS, bool VEC>
-__device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
-                                             i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
-                                             u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
-                                             const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
-                                             unsigned int* __restrict__ abort_flag) {
+// Loads, chain, ranks and staging of one warp's run of a tile; returns the number of survivors the warp staged.
+// FULL = the whole tile lies inside the array, so no element needs a bound check.
+template <class C, int BLOCK, int ROWS, bool VEC, bool FULL>
+__device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                       i64 n, i64 warp_base, int lane, typename C::out_t* __restrict__ stage) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     constexpr int E = pack_elems<C, VEC>::value;
-    constexpr int WARPS = BLOCK / 32;
-    constexpr int WARP_ELEMS = ROWS * 32 * E;
-    constexpr int TILE = WARPS * WARP_ELEMS;
     // Per-row survivor counts of a lane are packed FIELD bits apiece into 32-bit words, so one shuffle scan ranks
     // several rows at once. A row total is at most 32*E, which fits 8 bits up to E = 4 (128 = 0x80), else 16.
     constexpr int FIELD = (32 * E <= 128) ? 8 : 16;
     constexpr int PER_WORD = 32 / FIELD;
     constexpr int WORDS = (ROWS + PER_WORD - 1) / PER_WORD;
     constexpr u32 FMASK = (FIELD == 8) ? 0xffu : 0xffffu;
-
-    __shared__ O s_stage[TILE];           // warp w stages its survivors, compacted, at [w*WARP_ELEMS, ...)
-    __shared__ int s_warp_tot[WARPS];
-    __shared__ i64 s_prefix;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const i64 tile = blockIdx.x;
-    const i64 tile_base = tile * TILE;
-    const i64 warp_base = tile_base + (i64)warp * WARP_ELEMS;
-    const bool full = tile_base + TILE <= n;
-
-    // 0. Pull a tile far ahead of this one into L2. A tile's look-back cannot finish before every earlier tile has
-    //    counted its survivors, so one slow HBM access holds up all tiles behind it; with the input already in L2 the
-    //    loads of all tiles take about the same, short time (measured: 8 % faster at 8 MB ahead, no gain beyond).
-#ifndef DCB_COMPACT_AHEAD_BYTES
-#define DCB_COMPACT_AHEAD_BYTES (8 << 20)
-#endif
-    if (DCB_COMPACT_AHEAD_BYTES > 0) {
-        const i64 ahead = tile + (i64)(DCB_COMPACT_AHEAD_BYTES) / (i64)(TILE * sizeof(A)) + 1;
-        if ((ahead + 1) * TILE <= n) {
-            const char* p0 = reinterpret_cast<const char*>(in0 + ahead * TILE);
-            for (int l = threadIdx.x; l < (int)(TILE * sizeof(A) / 128); l += BLOCK)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + (i64)l * 128));
-            if constexpr (C::n_in == 2) {
-                const char* p1 = reinterpret_cast<const char*>(in1 + ahead * TILE);
-                for (int l = threadIdx.x; l < (int)(TILE * sizeof(B) / 128); l += BLOCK)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + (i64)l * 128));
-            }
-        }
-    }
     // 1. loads: all rows of the thread are in flight before the first is used
     Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
-    if (full) {
+    if constexpr (FULL) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             const i64 idx = warp_base + ((i64)r * 32 + lane) * E;
@@ -580,7 +540,7 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
             bool keep;
             if constexpr (C::n_in == 2) keep = C::apply(a[r].e[k], b[r].e[k], val[r][k]);
             else keep = C::apply(a[r].e[k], B(), val[r][k]);
-            if (!full) keep = keep && (warp_base + ((i64)r * 32 + lane) * E + k < n);
+            if constexpr (!FULL) keep = keep && (warp_base + ((i64)r * 32 + lane) * E + k < n);
             bits |= (keep ? 1u : 0u) << k;
         }
         keepbits[r] = bits;
@@ -609,9 +569,7 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
         row_start += (int)((tot_word >> sh) & FMASK);
     }
     const int warp_run = row_start;
-    if (lane == 0) s_warp_tot[warp] = warp_run;
     // 4. stage the survivors, compacted, in the warp's run
-    O* stage = s_stage + warp * WARP_ELEMS;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
         int pos = rank[r];
@@ -620,6 +578,61 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
             if ((keepbits[r] >> k) & 1u) { stage[pos] = val[r][k]; ++pos; }
         }
     }
+    return warp_run;
+}
+
+// Tile = BLOCK threads; each warp owns ROWS rows of 32 packs, a contiguous run of ROWS*32*E elements. Element order
+// inside a warp's run is row, then lane, then position in the pack; ranks follow it, so the output keeps source order.
+//
+// One tile per block, tile id = blockIdx.x. The look-back waits on tiles with smaller ids, i.e. on blocks the hardware
+// dispatched earlier (a 1-D grid is dispatched in index order; NVIDIA's own single-pass scan relies on the same). Should
+// that ever not hold, the bounded polls below end the launch with FLAG_TIMEOUT instead of hanging the GPU.
+template <class C, int BLOCK, int ROWS, bool VEC>
+__device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                             i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
+                                             u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
+                                             const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
+                                             unsigned int* __restrict__ abort_flag) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    constexpr int E = pack_elems<C, VEC>::value;
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int WARP_ELEMS = ROWS * 32 * E;
+    constexpr int TILE = WARPS * WARP_ELEMS;
+
+    __shared__ O s_stage[TILE];           // warp w stages its survivors, compacted, at [w*WARP_ELEMS, ...)
+    __shared__ int s_warp_tot[WARPS];
+    __shared__ i64 s_prefix;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const i64 tile = blockIdx.x;
+    const i64 tile_base = tile * TILE;
+    const i64 warp_base = tile_base + (i64)warp * WARP_ELEMS;
+    const bool full = tile_base + TILE <= n;
+
+    // 0. Pull a tile far ahead of this one into L2. A tile's look-back cannot finish before every earlier tile has
+    //    counted its survivors, so one slow HBM access holds up all tiles behind it; with the input already in L2 the
+    //    loads of all tiles take about the same, short time (measured: 8 % faster at 8 MB ahead, no gain beyond).
+#ifndef DCB_COMPACT_AHEAD_BYTES
+#define DCB_COMPACT_AHEAD_BYTES (8 << 20)
+#endif
+    if (DCB_COMPACT_AHEAD_BYTES > 0) {
+        const i64 ahead = tile + (i64)(DCB_COMPACT_AHEAD_BYTES) / (i64)(TILE * sizeof(A)) + 1;
+        if ((ahead + 1) * TILE <= n) {
+            const char* p0 = reinterpret_cast<const char*>(in0 + ahead * TILE);
+            for (int l = threadIdx.x; l < (int)(TILE * sizeof(A) / 128); l += BLOCK)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + (i64)l * 128));
+            if constexpr (C::n_in == 2) {
+                const char* p1 = reinterpret_cast<const char*>(in1 + ahead * TILE);
+                for (int l = threadIdx.x; l < (int)(TILE * sizeof(B) / 128); l += BLOCK)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + (i64)l * 128));
+            }
+        }
+    }
+    // 1-4. loads, chain, ranks, staging (specialised on whether the tile needs bound checks)
+    O* stage = s_stage + warp * WARP_ELEMS;
+    const int warp_run = full ? compact_count_and_stage<C, BLOCK, ROWS, VEC, true>(in0, in1, n, warp_base, lane, stage)
+                              : compact_count_and_stage<C, BLOCK, ROWS, VEC, false>(in0, in1, n, warp_base, lane, stage);
+    if (lane == 0) s_warp_tot[warp] = warp_run;
     __syncthreads();                                       // warp totals and staged runs are visible
     int warp_off = 0, tile_total = 0;
 #pragma unroll

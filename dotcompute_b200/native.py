@@ -94,6 +94,8 @@ PROTOTYPES = {
     "dcb_pipeline_run_host": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, C.POINTER(Result)]),
     "dcb_peer_area_create": (_i32, [_vp, _vp, _sz]),
     "dcb_peer_connect": (_i32, [_vp, _i32, _i32, _vp, _sz]),
+    "dcb_peer_area_ptr": (_i32, [_vp, _pp, C.POINTER(_sz)]),
+    "dcb_peer_connect_local": (_i32, [_vp, _i32, _i32, _pp]),
     "dcb_peer_exchange_async": (_i32, [_vp, _vp, _i32, _vp]),
     "dcb_peer_disconnect": (_i32, [_vp]),
     "dcb_compact_noalloc": (_i32, [_i32, C.POINTER(PipelineDesc), _vp, _vp, _i64, _vp, _i64, _vp, _vp]),

@@ -190,8 +190,8 @@ dcb_status dcb_device_info(dcb_ctx* ctx, char* name, size_t name_cap, int32_t* s
 /* Use `stream` (a cudaStream_t) as the context's stream from now on; NULL restores its own. */
 dcb_status dcb_set_stream(dcb_ctx* ctx, void* stream);
 dcb_status dcb_stream_sync(dcb_ctx* ctx, void* stream);
-/* Upper bound on polls of one look-back wait inside the compaction kernel before it gives up
- * and reports DCB_ERR_TIMEOUT (default 1<<22). */
+/* Upper bound on polls of one device-side wait (a look-back wait inside the compaction kernel, a wait for a peer's
+ * partial in the exchange kernel) before it gives up and reports DCB_ERR_TIMEOUT (defaults 1<<22 and 1<<20). */
 dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls);
 
 /* ------------------------------------------------------------------------- memory */
@@ -312,10 +312,14 @@ dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const vo
  * its P2P manager only copies buffers (src/Backends/DotCompute.Backends.CUDA/P2P/CudaP2PManager.cs:137-242).
  *   dcb_peer_area_create     allocates this GPU's 2 KiB exchange area and writes its 64-byte CUDA IPC handle to handle_out
  *   dcb_peer_connect         handles = world handles, handle_stride bytes apart, gathered from all ranks (index = rank)
+ *   dcb_peer_area_ptr / dcb_peer_connect_local   the same for a host that drives several GPUs from ONE process (as the
+ *                            reference does): exchange plain device pointers of the areas (peer access enabled by the caller)
  *   dcb_peer_exchange_async  d_record: the 128-byte device record of the reduction; out_type: DCB_T_* that reached its terminal
  *   dcb_peer_disconnect      back to single-GPU behaviour */
 dcb_status dcb_peer_area_create(dcb_ctx* ctx, void* handle_out, size_t handle_cap);
 dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank, const void* handles, size_t handle_stride);
+dcb_status dcb_peer_area_ptr(dcb_ctx* ctx, void** out_area, size_t* out_bytes);
+dcb_status dcb_peer_connect_local(dcb_ctx* ctx, int32_t world, int32_t rank, void* const* areas);
 dcb_status dcb_peer_exchange_async(dcb_ctx* ctx, void* d_record, int32_t out_type, void* stream);
 dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
 

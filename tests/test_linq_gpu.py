@@ -326,3 +326,30 @@ def test_peer_exchange_world_of_one_is_transparent(built_library):
         N.check(N.lib().dcb_peer_disconnect(acc2.handle), acc2.handle)
     finally:
         acc2.Dispose()
+
+
+def test_exchange_wait_runs_out_and_reports_timeout(built_library):
+    """Failure detection without a GPU fault: a world of two where the second rank never posts its partial (its area is a
+    scratch buffer nobody writes). The exchange kernel's bounded wait runs out, the record says so, the blocking call
+    returns DCB_ERR_TIMEOUT (a transient-class CudaException), and the context keeps working afterwards."""
+    import ctypes as C
+    from dotcompute_b200 import CudaAccelerator, CudaErrorClass, CudaException, native as N
+    acc2 = CudaAccelerator(0)
+    try:
+        acc2.SetSpinLimit(2000)                                   # about a millisecond of polling
+        area, nbytes = C.c_void_p(), C.c_size_t()
+        N.check(N.lib().dcb_peer_area_ptr(acc2.handle, C.byref(area), C.byref(nbytes)), acc2.handle)
+        silent_peer = acc2.Memory.AllocateAsync(nbytes.value, np.uint8)
+        silent_peer.FillAsync(0)
+        areas = (C.c_void_p * 2)(area.value, silent_peer.GetDeviceMemory())
+        N.check(N.lib().dcb_peer_connect_local(acc2.handle, 2, 0, areas), acc2.handle)
+        x = rng(4).random(100_000, dtype=F)
+        with pytest.raises(CudaException) as e:
+            AsComputeQueryable(acc2.Memory.AllocateAndCopyAsync(x)).Where("x => x > 0.5f").Select("x => x * x + 3f").Sum()
+        assert e.value.status == 102 and e.value.Classification == CudaErrorClass.Transient and e.value.IsRetryable
+        N.check(N.lib().dcb_peer_disconnect(acc2.handle), acc2.handle)
+        want = Enumerable(x).Where(lambda v: v > F(0.5)).Select(lambda v: v * v + F(3)).Sum()
+        assert AsComputeQueryable(x, acc2).Where("x => x > 0.5f").Select("x => x * x + 3f").Sum() == want   # still usable
+        silent_peer.Dispose()
+    finally:
+        acc2.Dispose()
