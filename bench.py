@@ -35,6 +35,10 @@ THRESHOLD, THRESHOLD_TXT, ADDEND = 0.5, "0.5f", 3.0
 WHERE, SELECT = f"x => x > {THRESHOLD_TXT}", "x => x * x + 3f"
 SEED = 31
 BYTES_PER_ELEM = 4   # algorithmic: one float read per element, nothing written
+# DRAM bytes moved per algorithmic byte by the fused reduce kernel, from the ncu capture summarised in
+# profiles/reduce_where_select_sum_f32_2p28.md (dram__bytes_read.sum + dram__bytes_write.sum = 1.073766 GB + 3.3 MB for
+# 1.073742 GB of input); every element is read once, so traffic scales with the element count.
+TRAFFIC_RATIO = (1.073766e9 + 3.334e6) / 1.073741824e9
 
 
 def _rng(seed):
@@ -512,7 +516,9 @@ def main() -> int:
                        "precompiled_kernel": bool(pipe.precompiled),
                        "launch": "the K steps are replayed as one CUDA graph" if graph is not None else "K plain launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "dcb_reduce_vec (fused Where->Select->Sum)",
+                         "traffic": n_local * BYTES_PER_ELEM * TRAFFIC_RATIO,
+                         "traffic_source": "ncu capture at 2^28 elements scaled by the element count (bytes per launch)",
+                         "peak_kind": peak_kind, "kernel": "dcb_reduce_vec (fused Where->Select->Sum)",
                          "timing": "mean of per-launch CUDA-event durations over a second, un-graphed pass of the same K steps",
                          "kernel_ms": kernel_ms_mean, "frac_of_nominal_8TBs": achieved / 8000.0},
             "gpu_launches": int(launches),

@@ -65,6 +65,9 @@ struct dcb_ctx {
     size_t stage_in_cap[2] = {0, 0};
     void* stage_out = nullptr;
     size_t stage_out_cap = 0;
+    void* host_recs = nullptr;             // pinned: per-chunk records of the host path (grow-only)
+    void* dev_recs = nullptr;
+    size_t recs_cap = 0;                   // in records
     bool alive = true;
     // exchange of partials between GPUs (see PeerTable in dcb_kernels.cuh)
     dcb::PeerTable peers = {};
@@ -388,6 +391,8 @@ extern "C" dcb_status dcb_shutdown(dcb_ctx* ctx) {
     if (ctx->peer_state) cudaFree(ctx->peer_state);
     for (int i = 0; i < 2; ++i) if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
     if (ctx->stage_out) cudaFree(ctx->stage_out);
+    if (ctx->dev_recs) cudaFree(ctx->dev_recs);
+    if (ctx->host_recs) cudaFreeHost(ctx->host_recs);
     cudaStreamDestroy(ctx->own_stream);
     cudaStreamDestroy(ctx->copy_stream);
     cudaStreamDestroy(ctx->out_stream);
@@ -1002,11 +1007,19 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     if ((st = grow(ctx, &ctx->stage_in[0], &ctx->stage_in_cap[0], std::max<size_t>((size_t)n * sz0, 256)))) return st;
     if (I.n_in == 2 && (st = grow(ctx, &ctx->stage_in[1], &ctx->stage_in_cap[1], std::max<size_t>((size_t)n * sz1, 256)))) return st;
     if (to_array && (st = grow(ctx, &ctx->stage_out, &ctx->stage_out_cap, std::max<size_t>((size_t)n * szo, 256)))) return st;
-    // Per-chunk records live at the tail of a scratch allocation.
-    dcb::DeviceResult* d_recs = nullptr;
-    CU(ctx, cudaMallocAsync((void**)&d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, ctx->stream));
-    dcb::DeviceResult* h_recs = nullptr;
-    CU(ctx, cudaHostAlloc((void**)&h_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaHostAllocDefault));
+    // Per-chunk records: device array + pinned host mirror, kept on the context and grown when a larger input comes.
+    if ((size_t)n_chunks > ctx->recs_cap) {
+        CU(ctx, cudaDeviceSynchronize());
+        if (ctx->dev_recs) cudaFree(ctx->dev_recs);
+        if (ctx->host_recs) cudaFreeHost(ctx->host_recs);
+        ctx->dev_recs = ctx->host_recs = nullptr; ctx->recs_cap = 0;
+        const size_t cap = std::max<size_t>((size_t)n_chunks, 256);
+        CU(ctx, cudaMalloc(&ctx->dev_recs, sizeof(dcb::DeviceResult) * cap));
+        CU(ctx, cudaHostAlloc(&ctx->host_recs, sizeof(dcb::DeviceResult) * cap, cudaHostAllocDefault));
+        ctx->recs_cap = cap;
+    }
+    dcb::DeviceResult* d_recs = (dcb::DeviceResult*)ctx->dev_recs;
+    dcb::DeviceResult* h_recs = (dcb::DeviceResult*)ctx->host_recs;
 
     cudaStream_t cs = ctx->copy_stream, ks = ctx->stream, os = ctx->out_stream;
     std::vector<cudaEvent_t> copied((size_t)n_chunks), computed((size_t)n_chunks);
@@ -1016,8 +1029,6 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     }
     auto cleanup = [&]() {
         for (int c = 0; c < n_chunks; ++c) { cudaEventDestroy(copied[c]); cudaEventDestroy(computed[c]); }
-        cudaFreeAsync(d_recs, ctx->stream);
-        cudaFreeHost(h_recs);
     };
     cudaEvent_t t0 = p->ev0, t1 = p->ev1;
     uint32_t launches = 0;

@@ -928,7 +928,9 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
         } else if (op.kind == OP_WHERE) {
             if (!translate_lambda(op.lambda, {cur_var}, {cur}, &code, &rt, &e)) { *err = "Where: " + e; *status = ST_NOT_SUPPORTED; return false; }
             if (rt != T_BOOL) { *err = "Where: predicate must return bool"; *status = ST_NOT_SUPPORTED; return false; }
-            body += "        if (!" + code + ") return false;\n";
+            // Branch-free: lambdas are pure, so everything after a failed predicate may still be evaluated; the element
+            // is dropped by the flag. (An early return costs a divergent branch per element inside the unrolled kernels.)
+            body += "        keep = keep & " + code + ";\n";
             info->has_filter = true;
             key += "|W:" + code;
             continue;
@@ -969,8 +971,9 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
     s += std::string("    static constexpr int n_in = ") + (info->n_in == 2 ? "2" : "1") + ";\n";
     s += std::string("    static constexpr bool has_filter = ") + (info->has_filter ? "true" : "false") + ";\n";
     s += "    static __device__ __forceinline__ bool apply(const in0_t& p0, const in1_t& p1, out_t& out) {\n";
+    if (info->has_filter) s += "        bool keep = true;\n";
     s += body;
-    s += "        out = " + cur_var + ";\n        return true;\n    }\n};\n";
+    s += "        out = " + cur_var + std::string(";\n        return ") + (info->has_filter ? "keep" : "true") + ";\n    }\n};\n";
     info->chain_src = s;
     info->key = key;
     *status = 0;

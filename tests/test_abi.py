@@ -104,7 +104,7 @@ def test_untranslatable_lambdas_are_not_supported(lam, types):
 
 def test_generated_source_shape():
     src = generate_source(np.float32, [(N.OP_WHERE, "x => x > 0.5f"), (N.OP_SELECT, "x => x * x + 3f"), (N.OP_SUM, None)])
-    assert "struct dcb_chain" in src and "if (!(p0 > 0.5f)) return false;" in src
+    assert "struct dcb_chain" in src and "keep = keep & (p0 > 0.5f);" in src
     assert "dcb::reduce_body<dcb_chain, 1, 256, 4, true>" in src and 'extern "C" __global__' in src
     assert "atomicAdd" not in src                       # no float atomics: reductions are deterministic
     src = generate_source(np.int64, [(N.OP_WHERE, "k => (k & 0xF) == 3"), (N.OP_TOARRAY, None)])
