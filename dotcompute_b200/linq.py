@@ -124,7 +124,7 @@ def _split_lambda(text: str):
 class ComputeQueryable:
     """IQueryable<T> bound to the compute provider. Operators only record themselves; a terminal runs the query."""
 
-    def __init__(self, source, accelerator: CudaAccelerator | None = None, ops=(), second=None, force_jit=False):
+    def __init__(self, source, accelerator: CudaAccelerator | None = None, ops=(), second=None, force_jit=False, take=None):
         if source is None:
             raise errors.ArgumentNullException("source")
         self._source = source
@@ -132,6 +132,7 @@ class ComputeQueryable:
         self._ops = tuple(ops)
         self._acc = accelerator
         self._force_jit = force_jit
+        self._take = take            # Take(k) after Select/Where: only the first k results are materialised
 
     # ------------------------------------------------------------------ plumbing
     @property
@@ -154,6 +155,8 @@ class ComputeQueryable:
         return int(np.asarray(src).size)
 
     def _with(self, kind, lam, second=None):
+        if self._take is not None:
+            raise errors.NotSupportedException("operators after Take are not fused; materialise with ToArray first")
         return ComputeQueryable(self._source, self._acc, self._ops + ((kind, lam),), second if second is not None else self._second,
                                 self._force_jit)
 
@@ -178,6 +181,8 @@ class ComputeQueryable:
 
     def _run(self, terminal: int):
         """Run the query; returns (pipeline, Result, output array or None)."""
+        if self._take is not None and terminal != N.OP_TOARRAY:
+            raise errors.NotSupportedException("a reduction after Take is not fused; materialise with ToArray first")
         pipe = self._compile(terminal)
         acc = self.Accelerator
         n = self._length()
@@ -187,14 +192,18 @@ class ComputeQueryable:
             raise errors.ArgumentException("both Zip inputs must live on the same side (host arrays or device buffers)")
         to_array = terminal == N.OP_TOARRAY
         out = None
+        cap = n if self._take is None or not to_array else min(n, self._take)   # Take(k): the kernel stops writing at k
         if on_device:
             in0 = C.c_void_p(self._source.GetDeviceMemory())
             in1 = C.c_void_p(self._second.GetDeviceMemory()) if self._second is not None else None
             if to_array:
-                dbuf = acc.Memory.AllocateAsync(max(n, 1), pipe.out_dtype)
+                dbuf = acc.Memory.AllocateAsync(max(cap, 1), pipe.out_dtype)
                 try:
-                    N.check(N.lib().dcb_pipeline_run(pipe.handle, in0, in1, n, C.c_void_p(dbuf.GetDeviceMemory()), n, C.byref(res), None), acc.handle)
-                    out = dbuf.CopyToAsync(count=int(res.count)) if res.count else np.empty(0, pipe.out_dtype)
+                    st = N.lib().dcb_pipeline_run(pipe.handle, in0, in1, n if pipe.has_filter else cap, C.c_void_p(dbuf.GetDeviceMemory()), cap, C.byref(res), None)
+                    if not (st == 202 and self._take is not None):      # more survivors than Take asked for is not an error
+                        N.check(st, acc.handle)
+                    got = min(int(res.count), cap)
+                    out = dbuf.CopyToAsync(count=got) if got else np.empty(0, pipe.out_dtype)
                 finally:
                     dbuf.Dispose()
             else:
@@ -205,10 +214,13 @@ class ComputeQueryable:
             if self._second is not None:
                 a1, p1 = self._host_ptr(self._second, n)
             if to_array:
-                out = np.empty(n, dtype=pipe.out_dtype)
-                N.check(N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n, out.ctypes.data_as(C.c_void_p), n, C.byref(res)), acc.handle)
-                out = out[: int(res.count)]
-                if out.base is not None and res.count < n:
+                out = np.empty(cap, dtype=pipe.out_dtype)
+                st = N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n if pipe.has_filter else cap, out.ctypes.data_as(C.c_void_p), cap, C.byref(res))
+                if not (st == 202 and self._take is not None):
+                    N.check(st, acc.handle)
+                got = min(int(res.count), cap)
+                out = out[:got]
+                if out.base is not None and got < cap:
                     out = out.copy()
             else:
                 N.check(N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n, None, 0, C.byref(res)), acc.handle)
@@ -243,6 +255,13 @@ class ComputeQueryable:
     ComputeSelect = Select
     ComputeWhere = Where
 
+    def Cast(self, type_name: str) -> "ComputeQueryable":
+        """Cast<T>(): element-wise conversion to the C# type named (`"long"`, `"float"`, ...), a Select in the visitor's
+        vocabulary (src/Extensions/DotCompute.Linq/Compilation/ExpressionTreeVisitor.cs:234-272)."""
+        if type_name is None:
+            raise errors.ArgumentNullException("type_name")
+        return self.Select(f"x => ({type_name})x")
+
     def Skip(self, count: int) -> "ComputeQueryable":
         if self._ops:
             raise errors.NotSupportedException("Skip after Select/Where is not fused; materialise with ToArray first")
@@ -254,8 +273,9 @@ class ComputeQueryable:
         n = self._length()
         k = min(max(int(count), 0), n)
         if self._ops:
-            # Take after a filter needs the first k survivors: run, then cut (the kernel keeps order).
-            return _Materialized(self.ToArray()[:k])
+            # The first k results in source order: the compaction kernel keeps order and simply stops writing at k.
+            return ComputeQueryable(self._source, self._acc, self._ops, self._second, self._force_jit,
+                                    take=k if self._take is None else min(k, self._take))
         return ComputeQueryable(_slice(self._source, 0, k), self._acc, (), None, self._force_jit)
 
     # ------------------------------------------------------------------ terminals
