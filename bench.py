@@ -45,7 +45,7 @@ def _rng(seed):
     return np.random.Generator(np.random.PCG64(seed))
 
 
-# The other BASELINE configurations, measured kernel-only on one GPU (device-resident inputs). Each entry:
+# The other benchmark configurations of the reference's hot path, measured kernel-only on one GPU (device-resident inputs). Each entry:
 # default log2(n), input generator(s), operators, terminal, algorithmic bytes per element as a function of selectivity.
 CONFIG_WORKLOADS = {
     "c1-map": dict(log2n=20, gen=lambda n: [_rng(42).random(n, dtype=np.float32)], ops=[("S", "x => x * 2f + 1f")], term="ToArray",
@@ -155,7 +155,7 @@ def parse_args():
     ap.add_argument("--profile", action="store_true",
                     help="minimal run for a profiler: no clock spin, no e2e, no CPU baseline, no oracle check")
     ap.add_argument("--workload", default="c5-sum", choices=sorted(CONFIG_WORKLOADS) + ["c5-sum"],
-                    help="c5-sum (default, the headline) or one of the other BASELINE configurations, 1 GPU, kernel-only")
+                    help="c5-sum (default, the headline) or one of the other benchmark configurations, 1 GPU, kernel-only")
     args = ap.parse_args()
     if args.profile:
         args.no_e2e = args.no_cpu_baseline = args.no_check = True
@@ -245,7 +245,7 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def cpu_baseline(n_total: int, budget_s: float = 12.0) -> dict:
+def cpu_baseline(n_total: int, time_limit_s: float = 12.0) -> dict:
     """Times the restated CPU SIMD backend on this host: fused Where->Select->Sum over a bounded sample of the same
     seeded workload, all hardware threads; plus the one-thread scalar loop the shipped provider runs today."""
     import oracle
@@ -258,7 +258,7 @@ def cpu_baseline(n_total: int, budget_s: float = 12.0) -> dict:
         simd.where_select_sum(x, THRESHOLD, ADDEND)
         reps += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s * 0.6 or reps >= 200:
+        if dt > time_limit_s * 0.6 or reps >= 200:
             break
     simd_eps = n * reps / dt
     t0 = time.perf_counter()

@@ -1,5 +1,6 @@
-"""The BASELINE configurations at their full sizes, and the host path over several staging chunks. Every case is compared
-with the sequential CPU oracle directly (it finishes these sizes in about a second each); sizes follow BASELINE.json."""
+"""The benchmark configurations at their full sizes (2^20 map, 2^24 reductions, 2^26 fused filter-map, 2^28 Zip dot product and
+int64 filter), and the host path over several staging chunks. Every case is compared with the sequential CPU oracle directly
+(it finishes these sizes in about a second each)."""
 import numpy as np
 import pytest
 
