@@ -341,7 +341,20 @@ def main() -> int:
     N.check(N.lib().dcb_h2d_async(acc.handle, dev.handle, 0, C.c_void_p(pinned.ptr), n_local * 4, None), acc.handle)
     acc.Synchronize()
 
-    fused = world > 1 and args.combine == "fused" and connect_peers(acc)
+    fused = False
+    if world > 1 and args.combine == "fused":
+        # Every rank must take the same route: agree on whether the peer set-up (CUDA IPC) worked everywhere.
+        try:
+            ok = connect_peers(acc)
+        except Exception as exc:
+            print(f"bench.py[{rank}]: peer exchange set-up failed ({exc}); using the NCCL all-reduce", file=sys.stderr)
+            ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        fused = bool(int(flag[0]))
+        if ok and not fused:
+            from dotcompute_b200.sharded import disconnect_peers
+            disconnect_peers(acc)
     ops = ((N.OP_WHERE, WHERE), (N.OP_SELECT, SELECT))
     q = ShardedQuery(acc, dev, ops)
     pipe = q.pipeline(N.OP_SUM)
@@ -405,20 +418,26 @@ def main() -> int:
         graph = None
         if not args.no_graph and (world == 1 or fused):
             # The K steps are captured once as a CUDA graph (kernels, events and the side stream's exchange kernels) and
-            # the timed region replays it: no per-launch host work between kernels.
+            # the timed region replays it: no per-launch host work between kernels. All ranks replay, or none does.
+            ok = True
             try:
                 q._step = 0
                 q._exchange_done = [None] * q.RING
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=stream):
                     rec = run_steps()
-                graph.replay()                                   # one untimed replay (graph upload)
-                barrier()
             except Exception as exc:                             # capture refused: fall back to plain launches
-                print(f"bench.py: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+                print(f"bench.py[{rank}]: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+                ok = False
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+            if world > 1:
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag[0]):
+                graph.replay()                                   # one untimed replay (graph upload)
+            else:
                 graph = None
-                torch.cuda.synchronize()
                 q._exchange_done = [None] * q.RING
+            barrier()
         launches0 = acc.LaunchCount
         if graph is not None:
             with torch.cuda.stream(stream):

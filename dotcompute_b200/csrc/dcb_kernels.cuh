@@ -716,8 +716,27 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
     const i64 base = prefix + warp_off;
     if (base + warp_run <= out_cap) {                      // the usual case: no per-element bound check
         O* __restrict__ dst = out + base;
+        constexpr int VO = (sizeof(O) == 4 || sizeof(O) == 8) ? 16 / (int)sizeof(O) : 1;
+        if constexpr (VEC && VO > 1) {
+            // `out` is 16-byte aligned in the vector kernels: a few single elements up to the next 16-byte boundary, then
+            // 16-byte stores (one instruction moves VO elements), then the last few.
+            int head = (int)((VO - (base & (VO - 1))) & (VO - 1));
+            if (head > warp_run) head = warp_run;
+            if (lane < head) dst[lane] = stage[lane];
+            const int nvec = (warp_run - head) / VO;
+#pragma unroll 2
+            for (int v = lane; v < nvec; v += 32) {
+                Pack<O, VO> q;
+#pragma unroll
+                for (int k = 0; k < VO; ++k) q.e[k] = stage[head + v * VO + k];
+                q.store(dst + head + v * VO);
+            }
+            const int done = head + nvec * VO;
+            if (lane < warp_run - done) dst[done + lane] = stage[done + lane];
+        } else {
 #pragma unroll 4
-        for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
+            for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
+        }
     } else {
         for (int i = lane; i < warp_run; i += 32) {
             const i64 pos = base + i;
