@@ -150,6 +150,7 @@ def parse_args():
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the result")
     ap.add_argument("--combine", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange of partial sums: inside the reduce kernel over NVLink peer stores (fused) or an NCCL all-reduce")
+    ap.add_argument("--no-numa", action="store_true", help="do not bind the process to the GPU's NUMA node")
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue the timed steps one by one instead of replaying them as one captured CUDA graph")
     ap.add_argument("--profile", action="store_true",
@@ -234,6 +235,31 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm),
                 "window": "0.7 s of the same steps run untimed immediately before, plus the timed region (50 ms sampling)"}
+
+
+def bind_to_gpu_numa_node(device_index: int) -> str:
+    """Restrict this process to the CPUs of the NUMA node the GPU hangs off, before the pinned host shard is allocated and
+    filled, so that its pages are local to the GPU's PCIe root (first-touch placement). Returns a note for the JSON line."""
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(device_index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "numa node unknown"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return f"gpu on numa node {node}, none of its cpus allowed here"
+        os.sched_setaffinity(0, allowed)
+        return f"bound to numa node {node} ({len(allowed)} cpus)"
+    except Exception as exc:   # no sysfs, no permission: leave the placement to the OS
+        return f"not bound ({type(exc).__name__})"
 
 
 def measured_peak_gbs():
@@ -333,6 +359,7 @@ def main() -> int:
     start, stop = shard_bounds(n_total, world, rank, 4)
     n_local = stop - start
     acc = CudaAccelerator(local_rank)
+    numa_note = "not requested" if args.no_numa else bind_to_gpu_numa_node(local_rank)
 
     # ---- data: pinned host shard (the e2e source), copied once to HBM (the resident source)
     pinned = acc.Memory.AllocatePinned(n_local, np.float32)
@@ -517,7 +544,7 @@ def main() -> int:
         e2e_ms = float(te[0]) / e2e_steps
         n_chunks = -(-n_local * 4 // (32 << 20))
         e2e = {"value": n_total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": n_total * 4,
-               "d2h_bytes_per_step": 128 * n_chunks * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "wall_ms_per_step": wall_ms / e2e_steps,
+               "d2h_bytes_per_step": 128 * n_chunks * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "wall_ms_per_step": wall_ms / e2e_steps, "host_placement": numa_note,
                "note": "pinned host shard -> 32 MiB chunked H2D overlapped with per-chunk kernels -> records D2H; PCIe-bound"}
 
     if rank == 0:

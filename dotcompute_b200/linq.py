@@ -328,6 +328,35 @@ class ComputeQueryable:
     def Any(self, predicate: str | None = None) -> bool:
         return self.Count(predicate) > 0
 
+    def First(self, predicate: str | None = None):
+        """First element (that satisfies `predicate`); InvalidOperationException if there is none, as in System.Linq."""
+        q = self.Where(predicate) if predicate is not None else self
+        got = q.Take(1).ToArray()
+        if got.size == 0:
+            raise errors.InvalidOperationException("Sequence contains no " + ("matching element" if predicate else "elements"))
+        return got[0]
+
+    def FirstOrDefault(self, predicate: str | None = None):
+        q = self.Where(predicate) if predicate is not None else self
+        got = q.Take(1).ToArray()
+        return got[0] if got.size else got.dtype.type(0)
+
+    def ElementAt(self, index: int):
+        if index < 0:
+            raise errors.ArgumentException("index must not be negative")
+        got = self.Take(index + 1).ToArray()
+        if got.size <= index:
+            raise errors.ArgumentException("index is past the end of the sequence")
+        return got[index]
+
+    def Contains(self, value) -> bool:
+        """Contains(value): an equality Where plus Count. The literal is printed in the element type's C# spelling."""
+        dt = self._dtype_of(self._source) if not self._ops else None
+        if dt is None:
+            dt = self._compile(N.OP_TOARRAY).out_dtype
+        lit = _literal(value, dt)
+        return self.Count(f"x => x == {lit}") > 0
+
     def All(self, predicate: str) -> bool:
         if predicate is None:
             raise errors.ArgumentNullException("predicate")
@@ -348,6 +377,22 @@ class _Materialized:
 
     def __iter__(self):
         return iter(self._arr)
+
+
+def _literal(value, dtype) -> str:
+    """C# literal of `value` in the type of `dtype` (for queries built from values, such as Contains)."""
+    dt = np.dtype(dtype)
+    if dt == np.float32:
+        return repr(float(np.float32(value))) + "f" if np.isfinite(value) else ("float.NaN" if np.isnan(value) else ("float.PositiveInfinity" if value > 0 else "float.NegativeInfinity"))
+    if dt == np.float64:
+        return repr(float(value)) + "d" if np.isfinite(value) else ("double.NaN" if np.isnan(value) else ("double.PositiveInfinity" if value > 0 else "double.NegativeInfinity"))
+    if dt == np.bool_:
+        return "true" if value else "false"
+    v = int(value)
+    suffix = {np.dtype(np.uint32): "u", np.dtype(np.int64): "L", np.dtype(np.uint64): "UL"}.get(dt, "")
+    if v < 0:
+        return f"(-{-v}{suffix})" if v != -2**63 else "long.MinValue"
+    return f"{v}{suffix}"
 
 
 def _slice(src, offset, length):

@@ -353,3 +353,20 @@ def test_exchange_wait_runs_out_and_reports_timeout(built_library):
         silent_peer.Dispose()
     finally:
         acc2.Dispose()
+
+
+def test_first_contains_elementat_cast(acc):
+    x = np.arange(1, 100_001, dtype=np.int32)
+    q = AsComputeQueryable(x, acc)
+    assert q.First("x => x % 7 == 0") == 7 and q.First() == 1
+    assert q.FirstOrDefault("x => x > 1000000") == 0
+    with pytest.raises(InvalidOperationException):
+        q.First("x => x < 0")
+    assert q.Where("x => x % 2 == 0").ElementAt(10) == 22
+    assert q.Contains(99_999) and not q.Contains(-5)
+    f = np.array([0.1, 0.25, 2.5], dtype=F)
+    assert AsComputeQueryable(f, acc).Contains(0.25) and not AsComputeQueryable(f, acc).Contains(0.3)
+    assert AsComputeQueryable(f, acc).Select("x => x * 2f").Contains(5.0)
+    assert AsComputeQueryable(x, acc).Cast("long").Select("x => x * 1000000L").Max() == 100_000 * 1_000_000
+    with pytest.raises(NotSupportedException):
+        q.Where("x => x > 5").Take(3).Sum()
