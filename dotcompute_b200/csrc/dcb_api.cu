@@ -41,7 +41,8 @@ thread_local char tl_error[1024] = "";
 
 struct Scratch {
     dcb::Partial* partials = nullptr;
-    unsigned int* words = nullptr;      // 512 bytes: [0] reduce ticket, [64] compaction abort flag (separate 128-byte lines)
+    unsigned int* words = nullptr;      // 512 bytes: [0] reduce ticket, [32] [33] tile-id and finished-block counters of the
+                                        // pipelined compaction, [64] compaction abort flag (separate 128-byte lines)
     unsigned long long* desc = nullptr; // look-back descriptors
     size_t desc_cap = 0;
     unsigned int epoch = 0;
@@ -90,6 +91,8 @@ struct dcb_pipeline {
     cudaLibrary_t lib = nullptr;
     const void* k_vec = nullptr;
     const void* k_scalar = nullptr;
+    const void* k_pipe = nullptr;        // pipelined compaction kernel (null: the query has none)
+    int pipe_rows = 0, pipe_nbuf = 0, occ_pipe = 1;   // its rows per warp, buffers per input, resident blocks per SM
     bool precompiled = false;
     int unroll = 4;
     int occ_vec = 1, occ_scalar = 1;     // resident blocks per SM
@@ -188,8 +191,9 @@ dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
         size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
         cap = std::max(cap, sc.desc_cap * 2);
         if (sc.desc) { CU(ctx, cudaStreamSynchronize(s)); CU(ctx, cudaFree(sc.desc)); sc.desc = nullptr; }
-        CU(ctx, cudaMalloc(&sc.desc, cap * sizeof(unsigned long long)));
-        CU(ctx, cudaMemset(sc.desc, 0, cap * sizeof(unsigned long long)));
+        // two spare descriptors: the pipelined kernel fetches them in aligned pairs
+        CU(ctx, cudaMalloc(&sc.desc, (cap + 2) * sizeof(unsigned long long)));
+        CU(ctx, cudaMemset(sc.desc, 0, (cap + 2) * sizeof(unsigned long long)));
         sc.desc_cap = cap;
         sc.epoch = 0;
     }
@@ -204,6 +208,12 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     tuning.compact_rows = env_int("DCB200_COMPACT_ROWS", 0);
     tuning.compact_min_blocks = env_int("DCB200_COMPACT_MINBLOCKS", tuning.compact_min_blocks);
     p->compact_block = tuning.compact_block;
+    tuning.pipe_rows = env_int("DCB200_PIPE_ROWS", 0);
+    tuning.pipe_min_blocks = env_int("DCB200_PIPE_MINBLOCKS", tuning.pipe_min_blocks);
+    tuning.pipe_lag = env_int("DCB200_PIPE_LAG", tuning.pipe_lag);
+    tuning.pipe_nbuf = env_int("DCB200_PIPE_NBUF", tuning.pipe_nbuf);
+    p->pipe_nbuf = tuning.pipe_nbuf;
+    p->pipe_rows = dcbt::pipe_rows_for(p->info) > 0 ? (tuning.pipe_rows > 0 ? tuning.pipe_rows : dcbt::pipe_rows_for(p->info)) : 0;
     p->unroll = tuning.unroll;
     p->jit_rows = tuning.compact_rows;
     p->source = dcbt::build_program(p->info, "", kKernelsHeaderText, tuning, true);
@@ -244,6 +254,11 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     CU(ctx, cudaLibraryGetKernel(&ks, p->lib, (std::string(stem) + "scalar").c_str()));
     p->k_vec = (const void*)kv;
     p->k_scalar = (const void*)ks;
+    if (p->pipe_rows > 0) {
+        cudaKernel_t kp = nullptr;
+        CU(ctx, cudaLibraryGetKernel(&kp, p->lib, "dcb_compact_pipe"));
+        p->k_pipe = (const void*)kp;
+    }
     return DCB_OK;
 }
 
@@ -257,8 +272,15 @@ dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
     else { (void)cudaGetLastError(); p->occ_vec = 4; }
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_scalar, blk, 0) == cudaSuccess && occ > 0) p->occ_scalar = occ;
     else { (void)cudaGetLastError(); p->occ_scalar = 4; }
+    if (p->k_pipe) {
+        // More than 48 KB of dynamic shared memory has to be asked for once per kernel.
+        const int dyn = (int)dcbt::pipe_smem_bytes(p->info, p->pipe_rows, p->pipe_nbuf);
+        if (cudaFuncSetAttribute(p->k_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_pipe, dcbt::pipe_block_threads(), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_pipe = occ;
+        else { (void)cudaGetLastError(); p->k_pipe = nullptr; }   // this device cannot run it: the one-tile-per-block kernel stays
+    }
     const int cap = env_int("DCB200_BLOCKS_PER_SM", 0);
-    if (cap > 0) { p->occ_vec = std::min(p->occ_vec, cap); p->occ_scalar = std::min(p->occ_scalar, cap); }
+    if (cap > 0) { p->occ_vec = std::min(p->occ_vec, cap); p->occ_scalar = std::min(p->occ_scalar, cap); p->occ_pipe = std::min(p->occ_pipe, cap); }
     CU(ctx, cudaMalloc(&p->d_result, DCB_DEVICE_RESULT_BYTES));
     CU(ctx, cudaMemset(p->d_result, 0, DCB_DEVICE_RESULT_BYTES));
     CU(ctx, cudaHostAlloc(&p->h_record, DCB_DEVICE_RESULT_BYTES, cudaHostAllocDefault));
@@ -702,6 +724,9 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->k_scalar = b->k_scalar;
         p->unroll = b->unroll;
         p->compact_block = b->compact_block;
+        p->k_pipe = b->k_pipe;
+        p->pipe_rows = b->pipe_rows;
+        p->pipe_nbuf = b->pipe_nbuf;
         p->source.clear();
     } else if ((st = load_jit(ctx, p)) != DCB_OK) {
         free_pipeline(p);
@@ -794,8 +819,10 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         return launch(ctx, fn, grid, args, s);
     }
     if (to_array) {
+        // The pipelined kernel moves whole tiles with 16-byte bulk copies: both inputs 16-byte aligned, vector output.
+        const bool pipe = vec && p->k_pipe && env_int("DCB200_COMPACT_PIPE", 1) != 0 && (I.n_in == 1 || aligned_to(in1, 16));
         const int rows = vec ? p->rows_vec : p->rows_scalar;
-        const int64_t tile = (int64_t)(p->compact_block / 32) * rows * 32 * E;
+        const int64_t tile = pipe ? (int64_t)dcbt::pipe_tile_elems(I, p->pipe_rows) : (int64_t)(p->compact_block / 32) * rows * 32 * E;
         long long num_tiles = (n + tile - 1) / tile;
         if (num_tiles == 0) {
             // Nothing to scan: the record is the previous one (or zero).
@@ -819,6 +846,16 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc,
                         (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag};
         if (launches) *launches += 1;
+        if (pipe) {
+            // Persistent blocks, as many as fit the GPU at once (fewer for a small input); tile ids come from counters[0].
+            unsigned int* counters = sc.words + 32;
+            void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&epoch, (void*)&spin,
+                             (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters};
+            const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * p->occ_pipe);
+            CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads()), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
+            ctx->launches += 1;
+            return DCB_OK;
+        }
         return launch(ctx, fn, (unsigned)num_tiles, args, s, p->compact_block);   // one tile per block, ids in dispatch order
     }
     // reductions

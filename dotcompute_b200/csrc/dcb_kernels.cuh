@@ -8,6 +8,7 @@
 //   map_body      Select/Zip only, ToArray       : out[i] = f(in[i])
 //   reduce_body   any chain, Sum/Min/Max/Avg/Count: one read of the input, nothing written but a record
 //   compact_body  chain with a Where, ToArray     : stable stream compaction, single pass
+//   compact_pipe_body  the same, persistent blocks whose input arrives by asynchronous bulk copies
 //
 // All three are HBM-bound streaming kernels: 128-bit loads with a streaming cache hint, several
 // independent loads in flight per thread, no tensor cores. This file is compiled both by nvcc
@@ -111,6 +112,16 @@ struct Pack {
             h = __ldcs(reinterpret_cast<const unsigned short*>(p));
         } else if constexpr (BYTES == 1) {
             b = __ldcs(reinterpret_cast<const unsigned char*>(p));
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) e[i] = p[i];
+        }
+    }
+    // Plain load, for a pack that lies in shared memory (the cache hints above exist for global memory only).
+    __device__ __forceinline__ void load_shared(const T* p) {
+        if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) q[i] = reinterpret_cast<const uint4*>(p)[i];
         } else {
 #pragma unroll
             for (int i = 0; i < E; ++i) e[i] = p[i];
@@ -487,45 +498,19 @@ template <class C, int BLOCK, bool VEC> struct compact_rows {
     static constexpr int value = compact_rows_for(BLOCK, pack_elems<C, VEC>::value, (int)sizeof(typename C::out_t));
 };
 
-// Loads, chain, ranks and staging of one warp's run of a tile; returns the number of survivors the warp staged.
+// Chain, ranks and staging of one warp's run of a tile, whose packs the lanes hold in registers (row r of lane l is
+// pack r*32+l of the run); returns the number of survivors the warp staged, compacted and in source order, at `stage`.
 // FULL = the whole tile lies inside the array, so no element needs a bound check.
-template <class C, int BLOCK, int ROWS, bool VEC, bool FULL>
-__device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
-                                                       i64 n, i64 warp_base, int lane, typename C::out_t* __restrict__ stage) {
+template <class C, int ROWS, int E, bool FULL>
+__device__ __forceinline__ int compact_rank_and_stage(const Pack<typename C::in0_t, E> (&a)[ROWS], const Pack<typename C::in1_t, E> (&b)[ROWS],
+                                                      i64 n, i64 warp_base, int lane, typename C::out_t* stage) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
-    constexpr int E = pack_elems<C, VEC>::value;
     // Per-row survivor counts of a lane are packed FIELD bits apiece into 32-bit words, so one shuffle scan ranks
     // several rows at once. A row total is at most 32*E, which fits 8 bits up to E = 4 (128 = 0x80), else 16.
     constexpr int FIELD = (32 * E <= 128) ? 8 : 16;
     constexpr int PER_WORD = 32 / FIELD;
     constexpr int WORDS = (ROWS + PER_WORD - 1) / PER_WORD;
     constexpr u32 FMASK = (FIELD == 8) ? 0xffu : 0xffffu;
-    // 1. loads: all rows of the thread are in flight before the first is used
-    Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
-    if constexpr (FULL) {
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const i64 idx = warp_base + ((i64)r * 32 + lane) * E;
-            a[r].load(in0 + idx);
-            if constexpr (C::n_in == 2) b[r].load(in1 + idx);
-        }
-    } else {
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const i64 idx = warp_base + ((i64)r * 32 + lane) * E;
-#pragma unroll
-            for (int k = 0; k < E; ++k) {
-                if (idx + k < n) {
-                    a[r].e[k] = in0[idx + k];
-                    if constexpr (C::n_in == 2) b[r].e[k] = in1[idx + k];
-                } else {
-                    a[r].e[k] = A();
-                    if constexpr (C::n_in == 2) b[r].e[k] = B();
-                }
-            }
-        }
-    }
-
     // 2. chain, per-lane survivor bits and counts
     O val[ROWS][E];
     u32 keepbits[ROWS];
@@ -579,6 +564,127 @@ __device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* 
         }
     }
     return warp_run;
+}
+
+// Loads of one warp's run from global memory, then compact_rank_and_stage.
+template <class C, int BLOCK, int ROWS, bool VEC, bool FULL>
+__device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                       i64 n, i64 warp_base, int lane, typename C::out_t* __restrict__ stage) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B;
+    constexpr int E = pack_elems<C, VEC>::value;
+    // all rows of the thread are in flight before the first is used
+    Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
+    if constexpr (FULL) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const i64 idx = warp_base + ((i64)r * 32 + lane) * E;
+            a[r].load(in0 + idx);
+            if constexpr (C::n_in == 2) b[r].load(in1 + idx);
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const i64 idx = warp_base + ((i64)r * 32 + lane) * E;
+#pragma unroll
+            for (int k = 0; k < E; ++k) {
+                if (idx + k < n) {
+                    a[r].e[k] = in0[idx + k];
+                    if constexpr (C::n_in == 2) b[r].e[k] = in1[idx + k];
+                } else {
+                    a[r].e[k] = A();
+                    if constexpr (C::n_in == 2) b[r].e[k] = B();
+                }
+            }
+        }
+    }
+
+    return compact_rank_and_stage<C, ROWS, E, FULL>(a, b, n, warp_base, lane, stage);
+}
+
+
+// Decoupled look-back of tile `tile` (> 0), run by one whole warp after the tile's own descriptor was published:
+// returns, in every lane, the number of survivors of all earlier tiles, or sets `failed` when a bounded wait ran out.
+__device__ __forceinline__ i64 compact_lookback(const u64* __restrict__ desc, i64 tile, int lane, u32 epoch, u32 spin_limit,
+                                                const unsigned int* abort_flag, bool& failed_out) {
+    // One step inspects LOOK_WIN*32 predecessors, nearest first: sub-window j holds tiles look-32j-lane. All loads
+    // of a step are issued before the first is examined. The walk stops at the nearest tile whose inclusive
+    // prefix is known. Every poll loop is bounded.
+    constexpr int LOOK_WIN = 2;
+    i64 exclusive = 0;
+    i64 look = tile - 1;
+    bool failed = false, done = false;
+    while (!done && !failed) {
+
+        u64 d[LOOK_WIN];
+#pragma unroll
+        for (int j = 0; j < LOOK_WIN; ++j) {
+            const i64 idx = look - (i64)j * 32 - lane;
+            d[j] = idx >= 0 ? desc_load(desc + idx) : desc_make(epoch, ST_INCLUSIVE, 0);   // before tile 0: empty, inclusive
+        }
+#pragma unroll
+        for (int j = 0; j < LOOK_WIN; ++j) {
+            if (done || failed) break;
+            const i64 idx = look - (i64)j * 32 - lane;
+            u32 st = desc_status(d[j], epoch);
+            u32 polls = 0;
+            while (st == ST_INVALID) {
+                // the abort word is looked at every 16th poll only: every poller shares its L2 path
+                if (++polls > spin_limit || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
+                // Back off before asking again: a poll is an L2 round trip, and hundreds of warps share these lines.
+#ifndef DCB_POLL_SLEEP_NS
+#define DCB_POLL_SLEEP_NS 200
+#endif
+                __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
+
+                d[j] = desc_load(desc + idx);
+                st = desc_status(d[j], epoch);
+            }
+            if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
+            const unsigned int inc = __ballot_sync(0xffffffffu, st == ST_INCLUSIVE);
+            const int first = inc ? (__ffs(inc) - 1) : 32;
+            if (lane <= first) exclusive += (i64)(d[j] & DESC_VALUE_MASK);
+            if (inc) done = true;
+        }
+        look -= 32 * LOOK_WIN;
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) exclusive += __shfl_xor_sync(0xffffffffu, exclusive, m);
+    failed_out = failed;
+    return exclusive;
+}
+
+// A warp copies its staged run of `warp_run` survivors to out[base ...]; consecutive lanes write consecutive elements.
+template <typename O, bool VEC>
+__device__ __forceinline__ void compact_copy_out(O* __restrict__ out, i64 out_cap, i64 base, int warp_run, int lane, const O* stage) {
+    if (base + warp_run <= out_cap) {                      // the usual case: no per-element bound check
+        O* __restrict__ dst = out + base;
+        constexpr int VO = (sizeof(O) == 4 || sizeof(O) == 8) ? 16 / (int)sizeof(O) : 1;
+        if constexpr (VEC && VO > 1) {
+            // `out` is 16-byte aligned in the vector kernels: a few single elements up to the next 16-byte boundary, then
+            // 16-byte stores (one instruction moves VO elements), then the last few.
+            int head = (int)((VO - (base & (VO - 1))) & (VO - 1));
+            if (head > warp_run) head = warp_run;
+            if (lane < head) dst[lane] = stage[lane];
+            const int nvec = (warp_run - head) / VO;
+#pragma unroll 2
+            for (int v = lane; v < nvec; v += 32) {
+                Pack<O, VO> q;
+#pragma unroll
+                for (int k = 0; k < VO; ++k) q.e[k] = stage[head + v * VO + k];
+                q.store(dst + head + v * VO);
+            }
+            const int done = head + nvec * VO;
+            if (lane < warp_run - done) dst[done + lane] = stage[done + lane];
+        } else {
+#pragma unroll 4
+            for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
+        }
+    } else {
+        for (int i = lane; i < warp_run; i += 32) {
+            const i64 pos = base + i;
+            if (pos < out_cap) out[pos] = stage[i];
+        }
+    }
 }
 
 // Tile = BLOCK threads; each warp owns ROWS rows of 32 packs, a contiguous run of ROWS*32*E elements. Element order
@@ -651,49 +757,8 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
             }
         } else {
             if (lane == 0) desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tile_total));
-            // One step inspects LOOK_WIN*32 predecessors, nearest first: sub-window j holds tiles look-32j-lane. All loads
-            // of a step are issued before the first is examined. The walk stops at the nearest tile whose inclusive
-            // prefix is known. Every poll loop is bounded.
-            constexpr int LOOK_WIN = 2;
-            i64 exclusive = 0;
-            i64 look = tile - 1;
-            bool failed = false, done = false;
-            while (!done && !failed) {
-
-                u64 d[LOOK_WIN];
-#pragma unroll
-                for (int j = 0; j < LOOK_WIN; ++j) {
-                    const i64 idx = look - (i64)j * 32 - lane;
-                    d[j] = idx >= 0 ? desc_load(desc + idx) : desc_make(epoch, ST_INCLUSIVE, 0);   // before tile 0: empty, inclusive
-                }
-#pragma unroll
-                for (int j = 0; j < LOOK_WIN; ++j) {
-                    if (done || failed) break;
-                    const i64 idx = look - (i64)j * 32 - lane;
-                    u32 st = desc_status(d[j], epoch);
-                    u32 polls = 0;
-                    while (st == ST_INVALID) {
-                        // the abort word is looked at every 16th poll only: every poller shares its L2 path
-                        if (++polls > spin_limit || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
-                        // Back off before asking again: a poll is an L2 round trip, and hundreds of warps share these lines.
-#ifndef DCB_POLL_SLEEP_NS
-#define DCB_POLL_SLEEP_NS 200
-#endif
-                        __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
-
-                        d[j] = desc_load(desc + idx);
-                        st = desc_status(d[j], epoch);
-                    }
-                    if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
-                    const unsigned int inc = __ballot_sync(0xffffffffu, st == ST_INCLUSIVE);
-                    const int first = inc ? (__ffs(inc) - 1) : 32;
-                    if (lane <= first) exclusive += (i64)(d[j] & DESC_VALUE_MASK);
-                    if (inc) done = true;
-                }
-                look -= 32 * LOOK_WIN;
-            }
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) exclusive += __shfl_xor_sync(0xffffffffu, exclusive, m);
+            bool failed = false;
+            const i64 exclusive = compact_lookback(desc, tile, lane, epoch, spin_limit, abort_flag, failed);
             if (lane == 0) {
                 if (failed) {
                     // A wait ran out (or another tile's did). Tell the tiles still waiting, and leave a record that says
@@ -712,42 +777,286 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
     const i64 prefix = s_prefix;
     if (prefix < 0) return;                                // a bounded wait ran out: leave without writing
 
-    // 6. each warp copies its compacted run; consecutive lanes write consecutive elements
-    const i64 base = prefix + warp_off;
-    if (base + warp_run <= out_cap) {                      // the usual case: no per-element bound check
-        O* __restrict__ dst = out + base;
-        constexpr int VO = (sizeof(O) == 4 || sizeof(O) == 8) ? 16 / (int)sizeof(O) : 1;
-        if constexpr (VEC && VO > 1) {
-            // `out` is 16-byte aligned in the vector kernels: a few single elements up to the next 16-byte boundary, then
-            // 16-byte stores (one instruction moves VO elements), then the last few.
-            int head = (int)((VO - (base & (VO - 1))) & (VO - 1));
-            if (head > warp_run) head = warp_run;
-            if (lane < head) dst[lane] = stage[lane];
-            const int nvec = (warp_run - head) / VO;
-#pragma unroll 2
-            for (int v = lane; v < nvec; v += 32) {
-                Pack<O, VO> q;
-#pragma unroll
-                for (int k = 0; k < VO; ++k) q.e[k] = stage[head + v * VO + k];
-                q.store(dst + head + v * VO);
-            }
-            const int done = head + nvec * VO;
-            if (lane < warp_run - done) dst[done + lane] = stage[done + lane];
-        } else {
-#pragma unroll 4
-            for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
-        }
-    } else {
-        for (int i = lane; i < warp_run; i += 32) {
-            const i64 pos = base + i;
-            if (pos < out_cap) out[pos] = stage[i];
-        }
-    }
+    // 6. each warp copies its compacted run
+    compact_copy_out<O, VEC>(out, out_cap, prefix + warp_off, warp_run, lane, stage);
     if (tile == num_tiles - 1 && threadIdx.x == 0) {
         const i64 total = prefix + tile_total;
         res->count = total; res->count_f = (double)total;
         res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
         res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+    }
+}
+
+
+// ------------------------------------------------------------------ compact, pipelined: persistent blocks fed by bulk copies
+// Asynchronous bulk copies (the TMA unit, untiled form) and the shared-memory barriers they complete on.
+__device__ __forceinline__ u32 smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(u64* bar, u32 arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(u64* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
+    u32 ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ u64 global_timer_ns() {
+    u64 t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for phase `parity` of `bar`: false when the phase has not completed after `limit` tries or, since one
+// try may itself suspend the thread for a while, after `limit` microseconds (two seconds at most), whichever is first.
+__device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const u64 budget = (u64)limit * 1000ull < 2000000000ull ? (u64)limit * 1000ull : 2000000000ull;
+    const u64 t0 = global_timer_ns();
+    for (u32 tries = 0; tries < limit; ++tries) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > budget) break;
+    }
+    return false;
+}
+// Global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completing on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_global, u32 bytes, u64* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst_smem)), "l"(src_global), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// Orders this thread's earlier shared-memory accesses before later accesses made by bulk copies.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Sum of the survivor counts of tiles [lo, hi), run by one whole warp: the look-back of a persistent block. Such a block
+// knows the prefix after its own previous tile, so what it needs is the counts of the tiles drawn since, a known range,
+// read with all loads in flight at once rather than window by window. Returns the sum in every lane, or sets `failed`
+// when a bounded wait for a count that was not yet published ran out.
+__device__ __forceinline__ i64 compact_range_sum(const u64* __restrict__ desc, i64 lo, i64 hi, int lane, u32 epoch, u32 spin_limit,
+                                                 const unsigned int* abort_flag, bool& failed_out) {
+    constexpr int DEPTH = 8;                                  // descriptors per lane per step: 256 tiles per round trip
+    i64 sum = 0;
+    bool failed = false;
+    for (i64 base = lo; base < hi && !failed; base += 32 * DEPTH) {
+        u64 d[DEPTH];
+#pragma unroll
+        for (int u = 0; u < DEPTH; ++u) {
+            const i64 idx = base + (i64)u * 32 + lane;
+            d[u] = idx < hi ? desc_load(desc + idx) : desc_make(epoch, ST_AGGREGATE, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < DEPTH; ++u) {
+            const i64 idx = base + (i64)u * 32 + lane;
+            u32 polls = 0;
+            while (!failed && desc_status(d[u], epoch) == ST_INVALID) {
+                if (++polls > spin_limit || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
+                __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
+                d[u] = desc_load(desc + idx);
+            }
+            if (!failed) sum += (i64)(d[u] & DESC_VALUE_MASK);
+        }
+        failed = __any_sync(0xffffffffu, failed);
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    failed_out = failed;
+    return sum;
+}
+
+// Same result as compact_body, other schedule: a software pipeline over the tiles of a persistent block.
+//
+// About one block per SM slot stays resident and works through tiles whose ids it draws from a counter. In round k the
+// block (1) ranks tile k, whose input a bulk copy brought into shared memory while earlier rounds ran, and stages the
+// survivors in place, over the input it has just read (hence sizeof(out) <= sizeof(in0)); after the round's one block
+// barrier (2) one thread draws the id of tile k+PRE and starts its copies into the buffer tile k-LAG-1 left, (3) warp 0
+// publishes the count of tile k and works out the output offset of tile k-LAG+1, whose predecessors published their
+// counts a round or more ago, so it rarely has to wait, and (4) all warps write tile k-LAG, whose offset was worked out
+// a round earlier. The HBM reads never pause for a look-back. NBUF = LAG + 1 + PRE buffers per input.
+//
+// Offsets: the block knows the offset after its own previous tile; the offset of its next tile adds the counts of the
+// tiles drawn in between (compact_range_sum). Descriptors therefore carry counts only.
+//
+// Progress: a tile's offset waits only for counts of tiles with smaller ids; ids are drawn in increasing order by blocks
+// that are already running, and ranking a tile never waits for another block, so the smallest id whose count is missing
+// always belongs to a block that is about to rank it. No assumption about how many blocks are resident. All waits are
+// bounded all the same. LAG > PRE is required: a block starts with PRE + 1 neighbouring ids and ranks them over its
+// first PRE + 1 rounds; the offset of the next block's first tile needs all of them, and with LAG > PRE it is asked for
+// only after that many rounds (asked for earlier, every block would wait for the block before it, one after another).
+//
+// `counters[0]` hands out tile ids, `counters[1]` counts finished blocks; both must be zero at launch and the last block
+// to finish zeroes them again. That block also turns the record into FLAG_TIMEOUT if any block gave up.
+// Launch with BLOCK threads and NBUF * TILE * (sizeof(in0) [+ sizeof(in1)]) bytes of dynamic shared memory.
+template <class C, int BLOCK, int ROWS, int LAG, int NBUF>
+__device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                  i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
+                                                  u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
+                                                  const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
+                                                  unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
+    constexpr int PRE = NBUF - LAG - 1;
+    static_assert(PRE >= 1 && LAG > PRE && NBUF <= 16, "NBUF = LAG + 1 + PRE with LAG > PRE >= 1");
+    constexpr int E = 16 / (int)sizeof(A);
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int WARP_ELEMS = ROWS * 32 * E;
+    constexpr int TILE = WARPS * WARP_ELEMS;
+    constexpr u32 BYTES_A = (u32)(TILE * sizeof(A));
+    constexpr u32 BYTES_B = C::n_in == 2 ? (u32)(TILE * sizeof(B)) : 0u;
+    static_assert(BYTES_A % 16 == 0 && BYTES_B % 16 == 0, "bulk copies move multiples of 16 bytes");
+
+    extern __shared__ __align__(128) unsigned char s_dyn[];   // NBUF buffers of in0, then NBUF buffers of in1
+    __shared__ __align__(8) u64 s_bar[NBUF];                  // round r completes phase (r / NBUF) & 1 of s_bar[r % NBUF]
+    __shared__ i64 s_tile[NBUF];                              // tile id of the round held in each buffer (num_tiles = none)
+    __shared__ int s_tot[NBUF][WARPS];                        // survivors per warp of that tile
+    __shared__ i64 s_prefix[2];                               // output offset of the tile of round j at [j & 1]; -1 = gave up
+    __shared__ int s_dead;                                    // a copy did not arrive within the limit
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int FETCHER = BLOCK > 32 ? 32 : 0;              // lane 0 of warp 1: warp 0 is busy with the offsets
+    bool exhausted = false;                                   // used by the fetching thread only
+
+    // Draws the id of the tile this block handles in round r and starts the copies of its input. The round's barrier
+    // completes in every case, and s_tile is written before the arrival: whoever has waited for the barrier may read the
+    // id. A whole tile completes it with its bytes; the ragged last tile (read with plain loads) and "no tile left"
+    // complete it at once.
+    auto fetch = [&](i64 r) {
+        i64 t = num_tiles;
+        if (!exhausted) {
+            t = (i64)atomicAdd(counters, 1u);
+            if (t >= num_tiles) { t = num_tiles; exhausted = true; }
+        }
+        const int st = (int)(r % NBUF);
+        s_tile[st] = t;
+        if (t < num_tiles && (t + 1) * TILE <= n) {
+            mbar_expect_tx(&s_bar[st], BYTES_A + BYTES_B);
+            bulk_load(s_dyn + (size_t)st * BYTES_A, in0 + t * TILE, BYTES_A, &s_bar[st]);
+            if constexpr (C::n_in == 2)
+                bulk_load(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B, in1 + t * TILE, BYTES_B, &s_bar[st]);
+        } else {
+            mbar_arrive(&s_bar[st]);
+        }
+    };
+
+    if (threadIdx.x == FETCHER) {
+#pragma unroll
+        for (int st = 0; st < NBUF; ++st) mbar_init(&s_bar[st], 1u);
+        s_dead = 0;
+        fence_async_smem();                                   // the barriers exist before a copy can complete on them
+        for (i64 r = 0; r < PRE; ++r) fetch(r);
+    }
+    __syncthreads();
+
+    const i64 base_prev = prev ? prev->count : 0;
+    i64 last_tile = -1, run_incl = 0;                         // warp 0: the block's previous tile, survivors up to and including it
+    i64 nvalid = (i64)1 << 62;                                // rounds in which this block has a tile (known once an id ran past the end)
+    i64 k = 0;
+    i64 copies_upto = -1;                                     // when giving up: last round whose copies may still be in flight
+    bool gave_up = false;
+    for (;; ++k) {
+        const int st = (int)(k % NBUF);
+        const bool arrived = mbar_wait(&s_bar[st], (u32)((k / NBUF) & 1), spin_limit);   // the round's id, and its input if it has a whole tile
+        if (!arrived) s_dead = 1;                             // seen by all after the barrier below
+        const i64 tile = arrived ? s_tile[st] : num_tiles;
+        if (tile >= num_tiles && nvalid > k) nvalid = k;
+        const bool have_k = k < nvalid;
+        const i64 j0 = k - LAG;                               // the round whose tile is written now
+        if (!have_k && j0 >= nvalid) break;                   // nothing left to rank, nothing left to write
+
+        // (1) rank tile k and stage its survivors in place
+        if (have_k) {
+            const i64 tile_base = tile * TILE;
+            A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A);
+            O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
+            int warp_run;
+            if (tile_base + TILE <= n) {
+                Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    const int idx = warp * WARP_ELEMS + (r * 32 + lane) * E;
+                    a[r].load_shared(bufA + idx);
+                    if constexpr (C::n_in == 2)
+                        b[r].load_shared(reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + idx);
+                }
+                __syncwarp();                                 // every lane holds its packs before any lane overwrites the run
+                warp_run = compact_rank_and_stage<C, ROWS, E, true>(a, b, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
+            } else {
+                warp_run = compact_count_and_stage<C, BLOCK, ROWS, true, false>(in0, in1, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
+            }
+            if (lane == 0) s_tot[st][warp] = warp_run;
+        }
+        __syncthreads();   // counts of tile k visible; everyone is done writing tile k-LAG-1; s_prefix of tile k-LAG visible
+        if (s_dead) { gave_up = true; copies_upto = k + PRE - 1; break; }
+
+        // (2) refill the buffer tile k-LAG-1 left with the tile of round k+PRE
+        if (threadIdx.x == FETCHER) fetch(k + PRE);
+
+        if (warp == 0) {
+            // (3) publish the count of tile k, then the output offset of tile k-LAG+1, for the next round
+            if (have_k && lane == 0) {
+                int tot = 0;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) tot += s_tot[st][w];
+                desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tot));
+            }
+            const i64 j1 = k - LAG + 1;
+            if (j1 >= 0 && j1 < nvalid) {
+                const int s1 = (int)(j1 % NBUF);
+                const i64 t1 = s_tile[s1];
+                int tot1 = 0;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) tot1 += s_tot[s1][w];
+                bool failed = false;
+                const i64 between = compact_range_sum(desc, last_tile + 1, t1, lane, epoch, spin_limit, abort_flag, failed);
+                const i64 exclusive = run_incl + between;
+                run_incl = exclusive + tot1;
+                last_tile = t1;
+                if (lane == 0) {
+                    s_prefix[j1 & 1] = failed ? -1 : base_prev + exclusive;
+                    if (!failed && t1 == num_tiles - 1) {
+                        const i64 total = base_prev + exclusive + tot1;
+                        res->count = total; res->count_f = (double)total;
+                        res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+                        res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+                    }
+                }
+            }
+        }
+
+        // (4) write tile k-LAG, then hand its buffer back to the copy engine's view of shared memory
+        if (j0 >= 0 && j0 < nvalid) {
+            const int s0 = (int)(j0 % NBUF);
+            const i64 prefix = s_prefix[j0 & 1];
+            if (prefix < 0) { gave_up = true; copies_upto = k + PRE; break; }
+            int warp_off = 0;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) warp_off += (w < warp) ? s_tot[s0][w] : 0;
+            const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)s0 * BYTES_A) + warp * WARP_ELEMS);
+            compact_copy_out<O, true>(out, out_cap, prefix + warp_off, s_tot[s0][warp], lane, stage0);
+            fence_async_smem();
+        }
+    }
+
+    if (gave_up) {
+        // Tell the tiles still waiting. Copies this block started must land before its shared memory is given to another
+        // block: wait for the rounds that were started, again with a limit.
+        if (threadIdx.x == 0) atomicExch(abort_flag, epoch);
+        __syncthreads();
+        if (threadIdx.x == FETCHER)
+            for (i64 j = k + 1; j <= copies_upto; ++j) (void)mbar_wait(&s_bar[(int)(j % NBUF)], (u32)((j / NBUF) & 1), spin_limit);
+    }
+    // Sign off. The last block to do so resets the counters for the next launch and has the final say on the record.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int finished = atomicAdd(counters + 1, 1u);
+        if (finished == gridDim.x - 1) {
+            __threadfence();
+            if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT; }
+            counters[0] = 0; counters[1] = 0;
+        }
     }
 }
 

@@ -68,7 +68,20 @@ struct Tuning {
     int compact_block = 256;    // threads per block of the compaction kernels
     int compact_rows = 0;       // rows per warp in the compaction tile; 0 = automatic (dcb::compact_rows_for)
     int compact_min_blocks = 4; // second argument of __launch_bounds__ for the compaction kernels; 0 = none
+    int pipe_rows = 0;          // rows per warp in the pipelined compaction kernel; 0 = automatic (pipe_rows_for)
+    int pipe_lag = 2;           // rounds between ranking a tile and writing it
+    int pipe_nbuf = 4;          // shared-memory buffers per input: lag + 1 + tiles on their way in (fewer than lag)
+    int pipe_min_blocks = 3;    // second argument of __launch_bounds__ for the pipelined compaction kernel; 0 = none
 };
+
+// Rows per warp of the pipelined compaction kernel (dcb::compact_pipe_body, 256 threads, 16-byte packs of the
+// first input), or 0 when the query cannot use it: it stages survivors over the input it has read, so the output element
+// must not be larger than the first input's, and its two input buffers per block must fit shared memory.
+int pipe_rows_for(const ChainInfo& info);
+// Elements per tile, and dynamic shared memory per block of that kernel with `nbuf` buffers per input.
+long long pipe_tile_elems(const ChainInfo& info, int rows);
+long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf);
+int pipe_block_threads();   // threads per block that kernel is launched with
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
                           const Tuning& tuning, bool with_prelude);
 
