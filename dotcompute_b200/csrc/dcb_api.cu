@@ -92,7 +92,7 @@ struct dcb_pipeline {
     const void* k_vec = nullptr;
     const void* k_scalar = nullptr;
     const void* k_pipe = nullptr;        // pipelined compaction kernel (null: the query has none)
-    int pipe_rows = 0, pipe_nbuf = 0, occ_pipe = 1;   // its rows per warp, buffers per input, resident blocks per SM
+    int pipe_rows = 0, pipe_nbuf = 0, pipe_ctrl = 0, occ_pipe = 1;   // its rows per warp, buffers per input, extra warp, resident blocks per SM
     bool precompiled = false;
     int unroll = 4;
     int occ_vec = 1, occ_scalar = 1;     // resident blocks per SM
@@ -213,6 +213,8 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     tuning.pipe_lag = env_int("DCB200_PIPE_LAG", tuning.pipe_lag);
     tuning.pipe_nbuf = env_int("DCB200_PIPE_NBUF", tuning.pipe_nbuf);
     p->pipe_nbuf = tuning.pipe_nbuf;
+    tuning.pipe_ctrl = env_int("DCB200_PIPE_CTRL", tuning.pipe_ctrl);
+    p->pipe_ctrl = tuning.pipe_ctrl;
     p->pipe_rows = dcbt::pipe_rows_for(p->info) > 0 ? (tuning.pipe_rows > 0 ? tuning.pipe_rows : dcbt::pipe_rows_for(p->info)) : 0;
     p->unroll = tuning.unroll;
     p->jit_rows = tuning.compact_rows;
@@ -276,7 +278,7 @@ dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
         // More than 48 KB of dynamic shared memory has to be asked for once per kernel.
         const int dyn = (int)dcbt::pipe_smem_bytes(p->info, p->pipe_rows, p->pipe_nbuf);
         if (cudaFuncSetAttribute(p->k_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_pipe, dcbt::pipe_block_threads(), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_pipe = occ;
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_pipe, dcbt::pipe_block_threads(p->pipe_ctrl), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_pipe = occ;
         else { (void)cudaGetLastError(); p->k_pipe = nullptr; }   // this device cannot run it: the one-tile-per-block kernel stays
     }
     const int cap = env_int("DCB200_BLOCKS_PER_SM", 0);
@@ -727,6 +729,7 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->k_pipe = b->k_pipe;
         p->pipe_rows = b->pipe_rows;
         p->pipe_nbuf = b->pipe_nbuf;
+        p->pipe_ctrl = b->pipe_ctrl;
         p->source.clear();
     } else if ((st = load_jit(ctx, p)) != DCB_OK) {
         free_pipeline(p);
@@ -852,7 +855,7 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
             void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&epoch, (void*)&spin,
                              (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters};
             const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * p->occ_pipe);
-            CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads()), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
+            CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads(p->pipe_ctrl)), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
             ctx->launches += 1;
             return DCB_OK;
         }

@@ -12,6 +12,7 @@ struct dcb_builtin_entry {
     const void* k_pipe;     // pipelined compaction kernel, or null when the query has none
     int pipe_rows;          // rows per warp it was built with
     int pipe_nbuf;          // shared-memory buffers per input it was built with
+    int pipe_ctrl;          // 1 = built with the extra offsets warp
 };
 
 const dcb_builtin_entry* dcb_builtin_find(const char* key);

@@ -837,7 +837,10 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // when a bounded wait for a count that was not yet published ran out.
 __device__ __forceinline__ i64 compact_range_sum(const u64* __restrict__ desc, i64 lo, i64 hi, int lane, u32 epoch, u32 spin_limit,
                                                  const unsigned int* abort_flag, bool& failed_out) {
-    constexpr int DEPTH = 8;                                  // descriptors per lane per step: 256 tiles per round trip
+#ifndef DCB_RANGE_DEPTH
+#define DCB_RANGE_DEPTH 8
+#endif
+    constexpr int DEPTH = DCB_RANGE_DEPTH;                    // descriptors per lane per step: 256 tiles per round trip
     i64 sum = 0;
     bool failed = false;
     for (i64 base = lo; base < hi && !failed; base += 32 * DEPTH) {
@@ -888,8 +891,8 @@ __device__ __forceinline__ i64 compact_range_sum(const u64* __restrict__ desc, i
 //
 // `counters[0]` hands out tile ids, `counters[1]` counts finished blocks; both must be zero at launch and the last block
 // to finish zeroes them again. That block also turns the record into FLAG_TIMEOUT if any block gave up.
-// Launch with BLOCK threads and NBUF * TILE * (sizeof(in0) [+ sizeof(in1)]) bytes of dynamic shared memory.
-template <class C, int BLOCK, int ROWS, int LAG, int NBUF>
+// Launch with BLOCK + 32 * CTRL threads and NBUF * TILE * (sizeof(in0) [+ sizeof(in1)]) bytes of dynamic shared memory.
+template <class C, int BLOCK, int ROWS, int LAG, int NBUF, int CTRL>
 __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
                                                   i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
                                                   u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
@@ -914,8 +917,12 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
     __shared__ i64 s_prefix[2];                               // output offset of the tile of round j at [j & 1]; -1 = gave up
     __shared__ int s_dead;                                    // a copy did not arrive within the limit
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int FETCHER = BLOCK > 32 ? 32 : 0;              // lane 0 of warp 1: warp 0 is busy with the offsets
+    // CTRL = 1 adds a warp in front that only publishes counts and works out offsets (BLOCK + 32 threads in all); with
+    // CTRL = 0 the first ranking warp does that on top of its share of the tile. `warp` counts ranking warps; -1 = the extra warp.
+    const int warp = (int)(threadIdx.x >> 5) - CTRL, lane = threadIdx.x & 31;
+    const bool offsets_warp = CTRL ? warp < 0 : warp == 0;
+    const bool ranks = warp >= 0;
+    constexpr int FETCHER = (CTRL + (WARPS > 1 ? 1 : 0)) * 32;   // lane 0 of the second ranking warp: it does not work on offsets
     bool exhausted = false;                                   // used by the fetching thread only
 
     // Draws the id of the tile this block handles in round r and starts the copies of its input. The round's barrier
@@ -966,7 +973,7 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
         if (!have_k && j0 >= nvalid) break;                   // nothing left to rank, nothing left to write
 
         // (1) rank tile k and stage its survivors in place
-        if (have_k) {
+        if (have_k && ranks) {
             const i64 tile_base = tile * TILE;
             A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A);
             O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
@@ -993,7 +1000,7 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
         // (2) refill the buffer tile k-LAG-1 left with the tile of round k+PRE
         if (threadIdx.x == FETCHER) fetch(k + PRE);
 
-        if (warp == 0) {
+        if (offsets_warp) {
             // (3) publish the count of tile k, then the output offset of tile k-LAG+1, for the next round
             if (have_k && lane == 0) {
                 int tot = 0;
@@ -1030,6 +1037,7 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
             const int s0 = (int)(j0 % NBUF);
             const i64 prefix = s_prefix[j0 & 1];
             if (prefix < 0) { gave_up = true; copies_upto = k + PRE; break; }
+            if (!ranks) continue;                             // the extra warp has no run to write
             int warp_off = 0;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) warp_off += (w < warp) ? s_tot[s0][w] : 0;

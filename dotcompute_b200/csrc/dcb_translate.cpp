@@ -999,7 +999,7 @@ int pipe_rows_for(const ChainInfo& info) {
     const int rows = 16384 / (kPipeBlock * e * pipe_bytes_per_elem(info));
     return rows < 1 ? 0 : (rows > 8 ? 8 : rows);
 }
-int pipe_block_threads() { return kPipeBlock; }
+int pipe_block_threads(int ctrl) { return kPipeBlock + (ctrl ? 32 : 0); }
 long long pipe_tile_elems(const ChainInfo& info, int rows) { return (long long)(kPipeBlock / 32) * rows * 32 * (16 / type_size(info.in0)); }
 long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf) { return (long long)nbuf * pipe_tile_elems(info, rows) * pipe_bytes_per_elem(info); }
 
@@ -1044,14 +1044,14 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
             const int prow = tuning.pipe_rows > 0 ? tuning.pipe_rows : pipe_rows_for(info);
             if (v == 0 && pipe_rows_for(info) > 0) {
                 const std::string PB = std::to_string(kPipeBlock);
-                const std::string PT = std::to_string(pipe_block_threads());
+                const std::string PT = std::to_string(pipe_block_threads(tuning.pipe_ctrl));
                 const std::string pbounds = tuning.pipe_min_blocks > 0 ? PT + ", " + std::to_string(tuning.pipe_min_blocks) : PT;
                 s += "extern \"C\" __global__ void __launch_bounds__(" + pbounds + ") dcb_compact_pipe" + suffix +
                      "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
                      "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag, "
                      "unsigned int* counters) {\n"
                      "    dcb::compact_pipe_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) + ", " +
-                     std::to_string(tuning.pipe_nbuf) + ">(" + cast_in() + ", n, (" + C +
+                     std::to_string(tuning.pipe_nbuf) + ", " + std::to_string(tuning.pipe_ctrl ? 1 : 0) + ">(" + cast_in() + ", n, (" + C +
                      "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters);\n}\n";
             }
         } else {

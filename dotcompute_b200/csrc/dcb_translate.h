@@ -71,6 +71,7 @@ struct Tuning {
     int pipe_rows = 0;          // rows per warp in the pipelined compaction kernel; 0 = automatic (pipe_rows_for)
     int pipe_lag = 2;           // rounds between ranking a tile and writing it
     int pipe_nbuf = 4;          // shared-memory buffers per input: lag + 1 + tiles on their way in (fewer than lag)
+    int pipe_ctrl = 1;          // 1 = an extra warp for counts and offsets (288 threads per block instead of 256)
     int pipe_min_blocks = 3;    // second argument of __launch_bounds__ for the pipelined compaction kernel; 0 = none
 };
 
@@ -81,7 +82,7 @@ int pipe_rows_for(const ChainInfo& info);
 // Elements per tile, and dynamic shared memory per block of that kernel with `nbuf` buffers per input.
 long long pipe_tile_elems(const ChainInfo& info, int rows);
 long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf);
-int pipe_block_threads();   // threads per block that kernel is launched with
+int pipe_block_threads(int ctrl);   // threads per block that kernel is launched with
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
                           const Tuning& tuning, bool with_prelude);
 
