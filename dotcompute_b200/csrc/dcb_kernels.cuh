@@ -566,6 +566,42 @@ __device__ __forceinline__ int compact_rank_and_stage(const Pack<typename C::in0
     return warp_run;
 }
 
+// Chain, ranks and staging of one warp's run that lies in shared memory, element-wise: the run is taken as rows of 32
+// consecutive elements, lane l handling element 32*r + l of row r, so a row's survivors are ranked with one ballot and
+// land in consecutive words of `stage` (no shuffle scan, no bank conflicts). `stage` may be the start of the run itself
+// when sizeof(out) <= sizeof(in0): a row is written only after it, and every row before it, has been read. Returns the
+// number of survivors staged, in source order.
+template <class C, int NROWS>
+__device__ __forceinline__ int compact_rank_rows_and_stage(const typename C::in0_t* run0, const typename C::in1_t* run1, int lane,
+                                                           typename C::out_t* stage) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    // rows held in registers at a time: the largest of 16, 8, 4, 2, 1 that divides the run (the whole run if it is short)
+    constexpr int CHUNK = NROWS <= 16 ? NROWS : (NROWS % 16 == 0 ? 16 : (NROWS % 8 == 0 ? 8 : (NROWS % 4 == 0 ? 4 : (NROWS % 2 == 0 ? 2 : 1))));
+    static_assert(NROWS % CHUNK == 0, "whole chunks");
+    const u32 below = (1u << lane) - 1u;
+    int base = 0;
+#pragma unroll 1
+    for (int c = 0; c < NROWS; c += CHUNK) {
+        A a[CHUNK]; B b[CHUNK];
+#pragma unroll
+        for (int r = 0; r < CHUNK; ++r) {
+            a[r] = run0[(c + r) * 32 + lane];
+            if constexpr (C::n_in == 2) b[r] = run1[(c + r) * 32 + lane];
+        }
+        __syncwarp();                                         // every lane holds its elements before any lane overwrites the rows
+#pragma unroll
+        for (int r = 0; r < CHUNK; ++r) {
+            O v; bool keep;
+            if constexpr (C::n_in == 2) keep = C::apply(a[r], b[r], v); else keep = C::apply(a[r], B(), v);
+            const u32 m = __ballot_sync(0xffffffffu, keep);
+            if (keep) stage[base + __popc(m & below)] = v;
+            base += __popc(m);
+        }
+        __syncwarp();
+    }
+    return base;
+}
+
 // Loads of one warp's run from global memory, then compact_rank_and_stage.
 template <class C, int BLOCK, int ROWS, bool VEC, bool FULL>
 __device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
@@ -979,6 +1015,7 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
             O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
             int warp_run;
             if (tile_base + TILE <= n) {
+#ifdef DCB_PIPE_PACK_RANKS
                 Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) {
@@ -989,6 +1026,11 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
                 }
                 __syncwarp();                                 // every lane holds its packs before any lane overwrites the run
                 warp_run = compact_rank_and_stage<C, ROWS, E, true>(a, b, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
+#else
+                warp_run = compact_rank_rows_and_stage<C, ROWS * E>(
+                    bufA + warp * WARP_ELEMS,
+                    reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + warp * WARP_ELEMS, lane, stage);
+#endif
             } else {
                 warp_run = compact_count_and_stage<C, BLOCK, ROWS, true, false>(in0, in1, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
             }
