@@ -78,10 +78,11 @@ static bool lex(const std::string& s, std::vector<Tok>* out, std::string* err) {
             while (j < n && (isalnum((unsigned char)s[j]) || s[j] == '_')) ++j;
             t.kind = Tok::IDENT; t.text = s.substr(i, j - i); i = j;
         } else {
-            static const char* three[] = {">>>", nullptr};
+            static const char* three[] = {">>>", "<<=", ">>=", nullptr};
             static const char* two[] = {"=>", "==", "!=", "<=", ">=", "&&", "||", "<<", ">>", "+=", "-=", "*=", "/=", "%=", "&=", "|=", "^=", "++", "--", nullptr};
             t.kind = Tok::PUNCT;
             bool done = false;
+            if (s.compare(i, 4, ">>>=") == 0) { t.text = ">>>="; i += 4; done = true; }
             for (int k = 0; three[k] && !done; ++k)
                 if (s.compare(i, 3, three[k]) == 0) { t.text = three[k]; i += 3; done = true; }
             for (int k = 0; two[k] && !done; ++k)
@@ -727,7 +728,7 @@ struct MethodTranslator {
             Node one; one.type = T_I32; one.code = "1"; one.const_int = true; one.cval = 1;
             return assign_to(lhs, op == "++" ? "+=" : "-=", one, out);
         }
-        static const char* ops[] = {"=", "+=", "-=", "*=", "/=", "%=", "&=", "|=", "^=", nullptr};
+        static const char* ops[] = {"=", "+=", "-=", "*=", "/=", "%=", "&=", "|=", "^=", "<<=", ">>=", ">>>=", nullptr};
         for (int i = 0; ops[i]; ++i) {
             if (is_p(ops[i])) {
                 ++ex.pos_;
