@@ -30,6 +30,8 @@ PY_LAMBDAS = {
     "x => true": lambda x: np.ones(np.shape(x), bool), "x => false": lambda x: np.zeros(np.shape(x), bool),
     "x => x < 6": lambda x: x < 6, "x => x < 100": lambda x: x < 100,
     "x => x + 42.0f": lambda x: x + F(42), "x => x * 2.0f + 1.0f": lambda x: x * F(2) + F(1),
+    "x => x * 3.5f": lambda x: x * F(3.5), "x => (x * 2.0f + 10.0f) / x": lambda x: (x * F(2) + F(10)) / x,
+    "x => x * 2.0f": lambda x: x * F(2),
 }
 
 
@@ -46,5 +48,12 @@ def check_expectation(fx, got):
         assert got.size == fx["expect_len"] and got[0] == fx["expect_first"] and got[-1] == fx["expect_last"], fx["name"]
     if "expect_from_linq" in fx:
         x = fixture_input(fx)
-        want = {"x + 42": x + F(42), "x * 2 + 1": x * F(2) + F(1)}[fx["expect_from_linq"]]
-        assert np.array_equal(np.asarray(got).view(np.uint32), want.view(np.uint32)), fx["name"]
+        want = {"x + 42": lambda: x + F(42), "x * 2 + 1": lambda: x * F(2) + F(1), "x * 3.5": lambda: x * F(3.5),
+                "(x * 2 + 10) / x": lambda: (x * F(2) + F(10)) / x, "x * 2": lambda: x * F(2)}[fx["expect_from_linq"]]()
+        got = np.asarray(got)
+        if "abs_tol" in fx:        # the reference asserts closeness only (BeApproximately)
+            assert got.shape == want.shape and np.all(np.abs(got.astype(np.float64) - want) <= fx["abs_tol"]), fx["name"]
+        elif "rel_tol" in fx:
+            assert got.shape == want.shape and np.all(np.abs(got.astype(np.float64) - want) <= np.abs(want.astype(np.float64)) * fx["rel_tol"]), fx["name"]
+        else:
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), fx["name"]

@@ -4,7 +4,8 @@ The reference is C#/.NET and cannot run in this image, so the values below were 
 `src` names the file and lines inside the DotCompute tree. Inputs given as ranges are expanded here. Expected outputs
 are the literals the reference asserts (never computed by this script), except `expect_from_linq`, where the
 reference test itself asserts equality with System.Linq over the same lambda: there the expected column is left out
-and the test compares oracle and GPU against IEEE float arithmetic done operation by operation.
+and the test compares oracle and GPU against IEEE float arithmetic done operation by operation. Where the reference
+asserts only closeness (`abs_tol` / `rel_tol`, its own numbers), the fixture carries that tolerance.
 
 Run: python tests/golden/make_fixtures.py
 """
@@ -70,6 +71,13 @@ FIX = [
      "ops": [], "terminal": "ToArray", "expect_len": 10000, "expect_first": 1, "expect_last": 10000},
     {"name": "add42_matches_linq", "src": f"{C}:490-504", "dtype": "float32", "input": {"range": [0, 9999]},
      "ops": [["Select", "x => x + 42.0f"]], "terminal": "ToArray", "expect_from_linq": "x + 42"},
+    {"name": "times3_5_approx", "src": f"{C}:505-522", "dtype": "float32", "input": {"range": [0, 9999]},
+     "ops": [["Select", "x => x * 3.5f"]], "terminal": "ToArray", "expect_from_linq": "x * 3.5", "abs_tol": 0.0001},
+    {"name": "complex_expression_approx", "src": f"{C}:524-541", "dtype": "float32", "input": {"range": [1, 10000]},
+     "ops": [["Select", "x => (x * 2.0f + 10.0f) / x"]], "terminal": "ToArray", "expect_from_linq": "(x * 2 + 10) / x", "abs_tol": 0.001},
+    {"name": "edge_values_times2", "src": f"{C}:563-581", "dtype": "float32",
+     "input": [0.0, -1.0, 1.0, 1.7014117331926443e38, -1.7014117331926443e38],
+     "ops": [["Select", "x => x * 2.0f"]], "terminal": "ToArray", "expect_from_linq": "x * 2", "rel_tol": 0.0001},
     {"name": "mul2add1_1000", "src": f"{C}:544-561", "dtype": "float32", "input": {"range": [0, 999]},
      "ops": [["Select", "x => x * 2.0f + 1.0f"]], "terminal": "ToArray", "expect_from_linq": "x * 2 + 1"},
     {"name": "mul2add1_10000", "src": f"{C}:544-561", "dtype": "float32", "input": {"range": [0, 9999]},
