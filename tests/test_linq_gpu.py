@@ -370,3 +370,23 @@ def test_first_contains_elementat_cast(acc):
     assert AsComputeQueryable(x, acc).Cast("long").Select("x => x * 1000000L").Max() == 100_000 * 1_000_000
     with pytest.raises(NotSupportedException):
         q.Where("x => x > 5").Take(3).Sum()
+
+
+def test_division_and_sqrt_are_correctly_rounded(acc):
+    """Division and square root are single IEEE operations in C#; the kernels are built without fast-math, so they
+    must round exactly as numpy does, denormal operands included (no flush to zero)."""
+    x = np.arange(1, 10001).astype(F)
+    got = AsComputeQueryable(x, acc).Select("x => (x * 2.0f + 10.0f) / x").ToArray()
+    assert np.array_equal(got.view(np.uint32), ((x * F(2) + F(10)) / x).view(np.uint32))
+    r = rng(3)
+    a = (r.standard_normal(1_000_003) * 1e3).astype(F)
+    a[a == 0] = 1
+    got = AsComputeQueryable(a, acc).Select("x => (x * 2.0f + 10.0f) / x").ToArray()
+    assert np.array_equal(got.view(np.uint32), ((a * F(2) + F(10)) / a).view(np.uint32))
+    d = r.standard_normal(1_000_003)
+    d[d == 0] = 1
+    got = AsComputeQueryable(d, acc).Select("x => 1.0 / x + Math.Sqrt(Math.Abs(x))").ToArray()
+    assert np.array_equal(got.view(np.uint64), (1.0 / d + np.sqrt(np.abs(d))).view(np.uint64))
+    t = (r.random(1_000_003, dtype=F) * 1e-38).astype(F) + F(1e-39)
+    got = AsComputeQueryable(t, acc).Select("x => x / 3f").ToArray()
+    assert np.array_equal(got.view(np.uint32), (t / F(3)).view(np.uint32))
