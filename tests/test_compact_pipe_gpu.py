@@ -86,3 +86,35 @@ def test_host_chunks_chain_offsets(acc, pipe):
     x = rng(13).integers(-2**62, 2**62, 9_000_000, dtype=np.int64)     # 72 MB: three chunks
     got = both(pipe, lambda: AsComputeQueryable(x, acc).Where("k => (k & 0xF) == 3"))
     assert np.array_equal(got, x[(x & 0xF) == 3])
+
+
+def test_three_compactions_at_once_on_one_gpu(built_library):
+    """Three contexts (three streams) compact at the same time from three host threads. Each launch asks for as many
+    persistent blocks as fit the GPU alone, so together they cannot all be resident: the kernels must make progress
+    without that assumption (a tile waits only for tiles of blocks that are already running), with no wait running out."""
+    import threading
+
+    from dotcompute_b200 import CudaAccelerator
+    accs = [CudaAccelerator(0) for _ in range(3)]
+    r = rng(17)
+    xs = [r.random(24_000_000, dtype=np.float32) for _ in accs]
+    bufs = [a.Memory.AllocateAndCopyAsync(x) for a, x in zip(accs, xs)]
+    wants = [x[x > 0.5] * x[x > 0.5] + np.float32(3) for x in xs]
+    ok = [True] * len(accs)
+    errors = []
+
+    def work(i):
+        try:
+            for _ in range(6):
+                got = AsComputeQueryable(bufs[i], accs[i]).Where("x => x > 0.5f").Select("x => x * x + 3f").ToArray()
+                ok[i] &= bool(np.array_equal(got, wants[i]))
+        except Exception as e:   # surfaced below: an exception in a thread must fail the test
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(accs))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert ok == [True, True, True]
