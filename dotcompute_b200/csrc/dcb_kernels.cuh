@@ -851,11 +851,11 @@ __device__ __forceinline__ u64 global_timer_ns() {
 // try may itself suspend the thread for a while, after `limit` microseconds (two seconds at most), whichever is first.
 __device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
     if (mbar_try_wait(bar, parity)) return true;
-    const u64 budget = (u64)limit * 1000ull < 2000000000ull ? (u64)limit * 1000ull : 2000000000ull;
+    const u64 max_ns = (u64)limit * 1000ull < 2000000000ull ? (u64)limit * 1000ull : 2000000000ull;
     const u64 t0 = global_timer_ns();
     for (u32 tries = 0; tries < limit; ++tries) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > budget) break;
+        if (global_timer_ns() - t0 > max_ns) break;
     }
     return false;
 }
