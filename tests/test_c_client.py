@@ -32,3 +32,21 @@ def test_c_client_runs_on_gpu(built_library, tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stderr
     assert "c_client ok" in out.stdout
+
+
+def test_pinvoke_stub_is_complete_and_current():
+    """include/Dcb200.PInvoke.cs (the LibraryImport class for the managed side) has one line per prototype of the header
+    and is what include/make_pinvoke.py generates from the header as it is now."""
+    import importlib.util
+    inc = os.path.join(ROOT, "include")
+    spec = importlib.util.spec_from_file_location("make_pinvoke", os.path.join(inc, "make_pinvoke.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with open(os.path.join(inc, "dcb200.h")) as f:
+        want = mod.generate(f.read())
+    with open(os.path.join(inc, "Dcb200.PInvoke.cs")) as f:
+        have = f.read()
+    assert have == want, "run python include/make_pinvoke.py"
+    from dotcompute_b200 import native
+    for name in native.declared_symbols():
+        assert f" {name}(" in have, name
