@@ -1110,5 +1110,206 @@ __device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __res
     }
 }
 
+// Experimental variant of compact_pipe_body (built only when a pipeline is compiled with the extra-warp setting 2): the
+// warp that works out offsets does not take part in the round's barrier. The ranking warps meet at a barrier of their
+// own, the first of them publishes the tile's count, and the offsets warp follows at its own pace, one tile after the
+// other, handing each offset over through a shared-memory barrier; a ranking warp waits for it only if the offset of the
+// tile it is about to write, ranked LAG rounds ago, is still missing. Same buffers, same id drawing, same bounded waits.
+// Launch with BLOCK + 32 threads.
+template <class C, int BLOCK, int ROWS, int LAG, int NBUF>
+__device__ __forceinline__ void compact_pipe_free_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                       i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
+                                                       u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
+                                                       const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
+                                                       unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
+    constexpr int PRE = NBUF - LAG - 1;
+    static_assert(PRE >= 1 && LAG > PRE && NBUF <= 16, "NBUF = LAG + 1 + PRE with LAG > PRE >= 1");
+    static_assert(BLOCK >= 64 && BLOCK % 32 == 0, "at least two ranking warps");
+    constexpr int E = 16 / (int)sizeof(A);
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int WARP_ELEMS = ROWS * 32 * E;
+    constexpr int TILE = WARPS * WARP_ELEMS;
+    constexpr u32 BYTES_A = (u32)(TILE * sizeof(A));
+    constexpr u32 BYTES_B = C::n_in == 2 ? (u32)(TILE * sizeof(B)) : 0u;
+    static_assert(BYTES_A % 16 == 0 && BYTES_B % 16 == 0, "bulk copies move multiples of 16 bytes");
+
+    extern __shared__ __align__(128) unsigned char s_dyn[];   // NBUF buffers of in0, then NBUF buffers of in1
+    // Round r uses slot r % NBUF and phase (r / NBUF) & 1 of: s_full (the copies have landed, the id is known),
+    // s_ranked (the counts of the tile are in s_tot), s_offset (s_prefix is valid).
+    __shared__ __align__(8) u64 s_full[NBUF], s_ranked[NBUF], s_offset[NBUF];
+    __shared__ i64 s_tile[NBUF];
+    __shared__ int s_tot[NBUF][WARPS];
+    __shared__ i64 s_prefix[NBUF];                            // -1 = the offsets warp gave up
+    __shared__ int s_dead;                                    // a wait ran out somewhere in this block
+
+    const int warp = (int)(threadIdx.x >> 5) - 1, lane = threadIdx.x & 31;   // ranking warps 0 .. WARPS-1; -1 = the offsets warp
+    const bool ranks = warp >= 0;
+    constexpr int PUBLISHER = 32;                             // lane 0 of the first ranking warp
+    constexpr int FETCHER = 64;                               // lane 0 of the second ranking warp
+    volatile int* dead = &s_dead;
+    bool exhausted = false;                                   // fetching thread only
+    i64 fetched_upto = -1;                                    // fetching thread only: last round it started
+
+    auto fetch = [&](i64 r) {
+        i64 t = num_tiles;
+        if (!exhausted) {
+            t = (i64)atomicAdd(counters, 1u);
+            if (t >= num_tiles) { t = num_tiles; exhausted = true; }
+        }
+        const int st = (int)(r % NBUF);
+        s_tile[st] = t;
+        fetched_upto = r;
+        if (t < num_tiles && (t + 1) * TILE <= n) {
+            mbar_expect_tx(&s_full[st], BYTES_A + BYTES_B);
+            bulk_load(s_dyn + (size_t)st * BYTES_A, in0 + t * TILE, BYTES_A, &s_full[st]);
+            if constexpr (C::n_in == 2)
+                bulk_load(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B, in1 + t * TILE, BYTES_B, &s_full[st]);
+        } else {
+            mbar_arrive(&s_full[st]);
+        }
+    };
+    // Bounded wait for round `r` of a barrier; ends early when another warp of the block has given up, and sleeps between
+    // tries so that a waiting warp does not take issue slots from the warps it waits for.
+    auto wait = [&](u64* bar, i64 r) -> bool {
+        const u32 parity = (u32)((r / NBUF) & 1);
+        if (mbar_try_wait(bar, parity)) return true;
+        const u64 max_ns = (u64)spin_limit * 1000ull < 2000000000ull ? (u64)spin_limit * 1000ull : 2000000000ull;
+        const u64 t0 = global_timer_ns();
+        for (u32 tries = 0; tries < spin_limit; ++tries) {
+            __nanosleep(tries < 8 ? 32 : 256);
+            if (mbar_try_wait(bar, parity)) return true;
+            if (*dead || global_timer_ns() - t0 > max_ns) break;
+        }
+        return false;
+    };
+
+    if (threadIdx.x == FETCHER) {
+#pragma unroll
+        for (int st = 0; st < NBUF; ++st) { mbar_init(&s_full[st], 1u); mbar_init(&s_ranked[st], 1u); mbar_init(&s_offset[st], 1u); }
+        s_dead = 0;
+        fence_async_smem();                                   // the barriers exist before a copy can complete on them
+        for (i64 r = 0; r < PRE; ++r) fetch(r);
+    }
+    __syncthreads();
+
+    if (!ranks) {
+        // ---------------------------------------------------------------- the offsets warp, at its own pace
+        const i64 base_prev = prev ? prev->count : 0;
+        i64 last_tile = -1, run_incl = 0;                     // the block's previous tile, survivors up to and including it
+        for (i64 j = 0;; ++j) {
+            const int s1 = (int)(j % NBUF);
+            if (!wait(&s_ranked[s1], j)) { if (lane == 0) { *dead = 1; atomicExch(abort_flag, epoch); } break; }
+            const i64 t1 = s_tile[s1];
+            if (t1 >= num_tiles) break;                       // the round after the block's last tile
+            int tot1 = 0;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) tot1 += s_tot[s1][w];
+            bool failed = false;
+            const i64 between = compact_range_sum(desc, last_tile + 1, t1, lane, epoch, spin_limit, abort_flag, failed);
+            const i64 exclusive = run_incl + between;
+            run_incl = exclusive + tot1;
+            last_tile = t1;
+            __syncwarp();
+            if (lane == 0) {
+                s_prefix[s1] = failed ? -1 : base_prev + exclusive;
+                if (!failed && t1 == num_tiles - 1) {
+                    const i64 total = base_prev + exclusive + tot1;
+                    res->count = total; res->count_f = (double)total;
+                    res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+                    res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+                }
+                if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
+                mbar_arrive(&s_offset[s1]);                   // the ranking warps read s_prefix after this
+            }
+            if (failed) break;
+        }
+    } else {
+        // ---------------------------------------------------------------- the ranking warps, one barrier of their own per round
+        i64 nvalid = (i64)1 << 62;                            // rounds in which this block has a tile
+        for (i64 k = 0;; ++k) {
+            const int st = (int)(k % NBUF);
+            const bool arrived = wait(&s_full[st], k);        // the round's id, and its input if it has a whole tile
+            if (!arrived) *dead = 1;                          // acted on by all after the barrier below
+            const i64 tile = arrived ? s_tile[st] : num_tiles;
+            if (tile >= num_tiles && nvalid > k) nvalid = k;
+            const bool have_k = k < nvalid;
+            const i64 j0 = k - LAG;                           // the round whose tile is written now
+
+            if (have_k) {                                     // rank tile k and stage its survivors in place
+                const i64 tile_base = tile * TILE;
+                A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A);
+                O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
+                int warp_run;
+                if (tile_base + TILE <= n)
+                    warp_run = compact_rank_rows_and_stage<C, ROWS * E>(
+                        bufA + warp * WARP_ELEMS,
+                        reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + warp * WARP_ELEMS, lane, stage);
+                else
+                    warp_run = compact_count_and_stage<C, BLOCK, ROWS, true, false>(in0, in1, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
+                if (lane == 0) s_tot[st][warp] = warp_run;
+            }
+            // The ranking warps only (the offsets warp is elsewhere): counts of tile k visible, everyone done writing tile
+            // k-LAG-1. Every decision to leave the loop is taken after this barrier, from values all threads agree on: the
+            // barrier itself ORs what each thread saw of s_dead, because the offsets warp may set it at any moment and
+            // two threads reading it one after the other could otherwise part ways, one of them waiting here for ever.
+            unsigned int any_dead;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(any_dead) : "r"((unsigned int)*dead), "n"(BLOCK) : "memory");
+            if (any_dead) break;
+            if (!have_k && j0 >= nvalid) break;               // nothing left to rank, nothing left to write
+
+            if (threadIdx.x == FETCHER) fetch(k + PRE);       // refill the buffer tile k-LAG-1 left
+            if (threadIdx.x == PUBLISHER && (have_k || k == nvalid)) {
+                if (have_k) {
+                    int tot = 0;
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) tot += s_tot[st][w];
+                    desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tot));
+                }
+                mbar_arrive(&s_ranked[st]);                   // also for the first round without a tile: it ends the offsets warp
+            }
+
+            if (j0 >= 0 && j0 < nvalid) {                     // write tile k-LAG, then hand its buffer back to the copy engine
+                const int s0 = (int)(j0 % NBUF);
+                const bool known = wait(&s_offset[s0], j0);
+                const i64 prefix = known ? s_prefix[s0] : -1;
+                if (prefix < 0) {
+                    *dead = 1;                                // acted on by all after the next barrier
+                } else {
+                    int warp_off = 0;
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) warp_off += (w < warp) ? s_tot[s0][w] : 0;
+                    const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)s0 * BYTES_A) + warp * WARP_ELEMS);
+                    compact_copy_out<O, true>(out, out_cap, prefix + warp_off, s_tot[s0][warp], lane, stage0);
+                    fence_async_smem();
+                }
+            }
+        }
+    }
+
+    __syncthreads();
+    if (s_dead) {
+        // Tell the tiles still waiting. Copies this block started must land before its shared memory is given to another
+        // block: wait for the rounds that may still be on their way, again with a limit each.
+        if (threadIdx.x == 0) atomicExch(abort_flag, epoch);
+        if (threadIdx.x == FETCHER)
+            for (i64 r = fetched_upto - NBUF + 1 > 0 ? fetched_upto - NBUF + 1 : 0; r <= fetched_upto; ++r)
+                (void)mbar_wait(&s_full[(int)(r % NBUF)], (u32)((r / NBUF) & 1), spin_limit);
+    }
+    // Sign off. The last block to do so resets the counters for the next launch and has the final say on the record.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int finished = atomicAdd(counters + 1, 1u);
+        if (finished == gridDim.x - 1) {
+            __threadfence();
+            if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT; }
+            counters[0] = 0; counters[1] = 0;
+        }
+    }
+}
+
 }  // namespace dcb
 #endif  // DCB_KERNELS_CUH

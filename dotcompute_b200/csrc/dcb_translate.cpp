@@ -1050,9 +1050,12 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                 s += "extern \"C\" __global__ void __launch_bounds__(" + pbounds + ") dcb_compact_pipe" + suffix +
                      "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
                      "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag, "
-                     "unsigned int* counters) {\n"
-                     "    dcb::compact_pipe_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) + ", " +
-                     std::to_string(tuning.pipe_nbuf) + ", " + std::to_string(tuning.pipe_ctrl ? 1 : 0) + ">(" + cast_in() + ", n, (" + C +
+                     "unsigned int* counters) {\n" +
+                     (tuning.pipe_ctrl == 2
+                          ? "    dcb::compact_pipe_free_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) +
+                                ", " + std::to_string(tuning.pipe_nbuf) + ">("
+                          : "    dcb::compact_pipe_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) + ", " +
+                                std::to_string(tuning.pipe_nbuf) + ", " + std::to_string(tuning.pipe_ctrl ? 1 : 0) + ">(") + cast_in() + ", n, (" + C +
                      "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters);\n}\n";
             }
         } else {

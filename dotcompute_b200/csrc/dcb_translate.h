@@ -71,7 +71,8 @@ struct Tuning {
     int pipe_rows = 0;          // rows per warp in the pipelined compaction kernel; 0 = automatic (pipe_rows_for)
     int pipe_lag = 2;           // rounds between ranking a tile and writing it
     int pipe_nbuf = 4;          // shared-memory buffers per input: lag + 1 + tiles on their way in (fewer than lag)
-    int pipe_ctrl = 1;          // 1 = an extra warp for counts and offsets (288 threads per block instead of 256)
+    int pipe_ctrl = 1;          // 1 = an extra warp for counts and offsets (288 threads per block instead of 256);
+                                // 2 = that warp outside the round's barrier (experimental, dcb::compact_pipe_free_body)
     int pipe_min_blocks = 3;    // second argument of __launch_bounds__ for the pipelined compaction kernel; 0 = none
 };
 
