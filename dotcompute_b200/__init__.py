@@ -6,7 +6,8 @@ sm_100a CUDA; there is no CPU or PyTorch path behind these names.
 """
 from .errors import (ArgumentException, ArgumentNullException, CudaErrorClass, CudaException, DotComputeException,
                      InvalidOperationException, NotSupportedException, ObjectDisposedException, OverflowException)
-from .accelerator import BufferState, CudaAccelerator, CudaMemoryManager, PinnedArray, UnifiedBuffer
+from .accelerator import (BufferState, CudaAccelerator, CudaMemoryManager, MapMode, MappedMemory, PinnedArray,
+                          UnifiedBuffer)
 from .orchestrator import ComputeOrchestrator, KernelParam, KernelRegistrationInfo, KernelRegistry, translate_kernel_method
 from .linq import (AsComputeQueryable, CompiledPipeline, ComputeLinqProvider, ComputeQueryable, ToComputeArray,
                    generate_source, translate_lambda)
@@ -14,7 +15,7 @@ from .linq import (AsComputeQueryable, CompiledPipeline, ComputeLinqProvider, Co
 __all__ = [
     "ArgumentException", "ArgumentNullException", "CudaErrorClass", "CudaException", "DotComputeException",
     "InvalidOperationException", "NotSupportedException", "ObjectDisposedException", "OverflowException",
-    "BufferState", "CudaAccelerator", "CudaMemoryManager", "PinnedArray", "UnifiedBuffer",
+    "BufferState", "CudaAccelerator", "CudaMemoryManager", "MapMode", "MappedMemory", "PinnedArray", "UnifiedBuffer",
     "AsComputeQueryable", "CompiledPipeline", "ComputeLinqProvider", "ComputeQueryable", "ToComputeArray",
     "generate_source", "translate_lambda",
     "ComputeOrchestrator", "KernelParam", "KernelRegistrationInfo", "KernelRegistry", "translate_kernel_method",

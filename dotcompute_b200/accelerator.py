@@ -45,6 +45,37 @@ class BufferState(enum.Enum):
     Disposed = 6
 
 
+class MapMode(enum.Enum):
+    """Access modes of IUnifiedMemoryBuffer<T>.Map (src/Core/DotCompute.Abstractions/Memory/MapMode.cs:9-30)."""
+    Read = 0
+    Write = 1
+    ReadWrite = 2
+
+
+class MappedMemory:
+    """What Map / MapRange return: a host view (`Span`, a numpy array) of a range of the buffer. Disposing it (or
+    leaving the `with` block) writes the view back to the device unless it was mapped for reading only."""
+
+    def __init__(self, buffer: "UnifiedBuffer", offset: int, length: int, mode: MapMode):
+        self._buffer, self._offset, self.Mode = buffer, offset, mode
+        self.Span = np.empty(length, dtype=buffer.dtype) if mode is MapMode.Write else buffer.CopyToAsync(None, offset, length)
+        self.Length = length
+        self._open = True
+
+    def Dispose(self) -> None:
+        if self._open:
+            self._open = False
+            if self.Mode is not MapMode.Read:
+                self._buffer.CopyFromAsync(self.Span, self._offset)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.Dispose()
+        return False
+
+
 class CudaAccelerator:
     """One GPU: context, stream, compiled-pipeline cache."""
 
@@ -143,6 +174,7 @@ class UnifiedBuffer:
         self._parent = parent       # keeps the owner of a slice alive
         self.State = BufferState.DeviceOnly
         self.IsDisposed = False
+        self._host = None           # host copy behind AsSpan / AsMemory; the device copy is the home of the data
 
     # -- properties of the interface
     @property
@@ -159,7 +191,15 @@ class UnifiedBuffer:
 
     @property
     def IsOnHost(self) -> bool:
-        return False
+        return self._host is not None and self.State in (BufferState.Synchronized, BufferState.HostDirty)
+
+    @property
+    def IsDirty(self) -> bool:
+        return self.State in (BufferState.HostDirty, BufferState.DeviceDirty)
+
+    @property
+    def ElementCount(self) -> int:
+        return self.Length
 
     @property
     def handle(self):
@@ -168,12 +208,69 @@ class UnifiedBuffer:
         return self._h
 
     def GetDeviceMemory(self) -> int:
+        self.EnsureOnDevice()
         return N.lib().dcb_devptr(self.handle) or 0
+
+    # -- host views. The device copy is the home; the host copy exists from the first AsSpan / EnsureOnHost on. Kernels
+    #    write the device copy without telling this object, so the host copy is trusted only while it is the newer one
+    #    (HostDirty): every other EnsureOnHost reads the device again.
+    def EnsureOnHost(self) -> None:
+        if self.State is not BufferState.HostDirty or self._host is None:
+            self._host = self.CopyToAsync(self._host if self._host is not None else None)
+            self.State = BufferState.Synchronized
+
+    EnsureOnHostAsync = EnsureOnHost
+
+    def AsReadOnlySpan(self) -> np.ndarray:
+        self.EnsureOnHost()
+        view = self._host.view()
+        view.flags.writeable = False
+        return view
+
+    AsReadOnlyMemory = AsReadOnlySpan
+
+    def AsSpan(self) -> np.ndarray:
+        """Writable host view. What is written becomes visible to the device at the next EnsureOnDevice / Synchronize /
+        GetDeviceMemory: the buffer counts as changed on the host from here on."""
+        self.EnsureOnHost()
+        self.State = BufferState.HostDirty
+        return self._host
+
+    AsMemory = AsSpan
+
+    def MarkHostDirty(self) -> None:
+        if self._host is None:
+            raise errors.InvalidOperationException("the buffer has no host copy to mark")
+        self.State = BufferState.HostDirty
+
+    def MarkDeviceDirty(self) -> None:
+        self.State = BufferState.DeviceDirty
+
+    def Synchronize(self) -> None:
+        if self.State is BufferState.HostDirty:
+            self.EnsureOnDevice()
+        elif self._host is not None:
+            self.EnsureOnHost()
+
+    SynchronizeAsync = Synchronize
+
+    def Map(self, mode: MapMode = MapMode.ReadWrite) -> MappedMemory:
+        return self.MapRange(0, self.Length, mode)
+
+    MapAsync = Map
+
+    def MapRange(self, offset: int, length: int, mode: MapMode = MapMode.ReadWrite) -> MappedMemory:
+        if offset < 0 or length < 0 or offset + length > self.Length:
+            raise errors.ArgumentException("range outside the buffer")
+        self.EnsureOnDevice()
+        return MappedMemory(self, offset, length, mode)
 
     # -- transfers
     def CopyFromAsync(self, source: np.ndarray, offset: int = 0) -> None:
         if source is None:
             raise errors.ArgumentNullException("source")
+        if self.State is BufferState.HostDirty and self._host is not None and source is not self._host:
+            self.EnsureOnDevice()     # changes made through AsSpan reach the device before this copy lands on top
         src = np.ascontiguousarray(source, dtype=self.dtype)
         if offset < 0 or offset + src.size > self.Length:
             raise errors.ArgumentException("source does not fit the buffer at this offset")
@@ -183,6 +280,10 @@ class UnifiedBuffer:
         self.State = BufferState.Synchronized
 
     def CopyToAsync(self, destination: np.ndarray | None = None, offset: int = 0, count: int | None = None) -> np.ndarray:
+        if isinstance(destination, UnifiedBuffer):
+            return self.CopyToBufferAsync(destination, offset, 0, count)
+        if self.State is BufferState.HostDirty and self._host is not None:
+            self.EnsureOnDevice()
         n = self.Length - offset if count is None else int(count)
         if offset < 0 or n < 0 or offset + n > self.Length:
             raise errors.ArgumentException("range outside the buffer")
@@ -224,6 +325,28 @@ class UnifiedBuffer:
 
     def EnsureOnDevice(self) -> None:
         _ = self.handle
+        if self.State is BufferState.HostDirty and self._host is not None:
+            host = self._host
+            self.CopyFromAsync(host)          # sets Synchronized
+
+    EnsureOnDeviceAsync = EnsureOnDevice
+
+    def CopyToBufferAsync(self, destination: "UnifiedBuffer", sourceOffset: int = 0, destinationOffset: int = 0,
+                          count: int | None = None) -> None:
+        """CopyToAsync(IUnifiedMemoryBuffer<T> destination[, sourceOffset, destinationOffset, count]): device to device."""
+        if destination is None:
+            raise errors.ArgumentNullException("destination")
+        n = self.Length - sourceOffset if count is None else int(count)
+        if destination.dtype != self.dtype:
+            raise errors.ArgumentException("destination has another element type")
+        if sourceOffset < 0 or destinationOffset < 0 or n < 0 or sourceOffset + n > self.Length or destinationOffset + n > destination.Length:
+            raise errors.ArgumentException("range outside a buffer")
+        self.EnsureOnDevice()
+        isz = self.dtype.itemsize
+        N.check(N.lib().dcb_d2d_async(self._acc.handle, destination.handle, destinationOffset * isz, self.handle,
+                                      sourceOffset * isz, n * isz, None), self._acc.handle)
+        self._acc.Synchronize()
+        destination.State = BufferState.DeviceDirty if destination._host is not None else BufferState.DeviceOnly
 
     def Dispose(self) -> None:
         if not self.IsDisposed:
