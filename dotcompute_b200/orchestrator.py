@@ -174,11 +174,17 @@ class ComputeOrchestrator:
         return (ceil(x, bx), ceil(y, by), ceil(z, bz)), (bx, by, bz)
 
     # ---- execution
-    def ExecuteAsync(self, kernelName: str, *args, accelerator: CudaAccelerator | None = None):
+    def ExecuteAsync(self, kernelName: str, *args, accelerator: CudaAccelerator | None = None, preferredBackend: str | None = None):
         """Run a registered kernel. Host arrays are copied to the device, writable ones copied back; returns the first
-        writable buffer argument (what ExecuteAsync<T> hands back for an array T)."""
+        writable buffer argument (what ExecuteAsync<T> hands back for an array T).
+
+        `preferredBackend` is the second overload of the reference (KernelExecutionService.cs:230-246): a wish, not a
+        demand. This engine has CUDA devices only, so "CUDA" / "GPU" select them and any other name falls back to the
+        optimal accelerator, as the reference does when no device of the wished type exists."""
         if self._disposed:
             raise errors.ObjectDisposedException("ComputeOrchestrator")
+        if preferredBackend is not None and not isinstance(preferredBackend, str):
+            raise errors.ArgumentException("preferredBackend must be a backend name")
         reg = self._resolve(kernelName)
         if not self.ValidateKernelArgsAsync(kernelName, *args):
             raise errors.ArgumentException(

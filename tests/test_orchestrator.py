@@ -120,3 +120,10 @@ def test_execute_async_on_gpu(acc):
     with pytest.raises(ArgumentException):
         orch.ExecuteAsync("Add", a, b)
     orch.Dispose()
+
+
+def test_preferred_backend_is_a_wish():
+    orch = ComputeOrchestrator.__new__(ComputeOrchestrator)     # no device needed for the argument check
+    orch._disposed = False
+    with pytest.raises(ArgumentException):
+        orch.ExecuteAsync("Add", preferredBackend=3)
