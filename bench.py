@@ -35,9 +35,9 @@ THRESHOLD, THRESHOLD_TXT, ADDEND = 0.5, "0.5f", 3.0
 WHERE, SELECT = f"x => x > {THRESHOLD_TXT}", "x => x * x + 3f"
 SEED = 31
 BYTES_PER_ELEM = 4   # algorithmic: one float read per element, nothing written
-# DRAM bytes moved per algorithmic byte by the fused reduce kernel, from the ncu capture summarised in
-# profiles/reduce_where_select_sum_f32_2p28.md (dram__bytes_read.sum + dram__bytes_write.sum = 1.073766 GB + 3.3 MB for
-# 1.073742 GB of input); every element is read once, so traffic scales with the element count.
+# DRAM bytes moved per algorithmic byte by the fused reduce kernel, from an ncu capture of it at 2^28 elements
+# (dram__bytes_read.sum + dram__bytes_write.sum = 1.073766 GB + 3.3 MB for 1.073742 GB of input); every element is read
+# once, so traffic scales with the element count.
 TRAFFIC_RATIO = (1.073766e9 + 3.334e6) / 1.073741824e9
 
 
@@ -76,22 +76,56 @@ CONFIG_WORKLOADS = {
 }
 
 
-def run_config(args) -> int:
-    """One of the secondary configurations: K launches of its fused kernel on device-resident input, one JSON line."""
-    import torch
-    from dotcompute_b200 import CudaAccelerator, native as N
-    from dotcompute_b200.linq import CompiledPipeline
-    from dotcompute_b200.accelerator import dcb_type
+CONFIG_ORDER = ["c1-map", "c2-sum-f32", "c2-min-f32", "c2-avg-f32", "c2-sum-i32", "c3-sum", "c3-toarray-50", "c3-toarray-01",
+                "c3-toarray-99", "headline-2p28", "c4-zipdot", "c4-i64-where"]
 
-    spec = CONFIG_WORKLOADS[args.workload]
-    log2n = args.log2n if args.log2n != 30 else spec["log2n"]
-    n = 1 << log2n
-    acc = CudaAccelerator(0)
+
+def _expected(spec_name, host, chk):
+    """What the oracle says the configuration's query returns: ('array', ndarray) or ('scalar', value, raw fp64 or None, sum|x| or None)."""
+    x = host[0]
+    if spec_name == "c1-map":
+        return ("array", chk.select_mul_add(x, 2.0, 1.0))
+    if spec_name == "c2-sum-f32":
+        v, raw = chk.sum_f32(x)
+        return ("scalar", v, raw, chk.sum_abs(x))
+    if spec_name == "c2-min-f32":
+        return ("scalar", chk.min_f32(x), None, None)
+    if spec_name == "c2-avg-f32":
+        _v, raw = chk.sum_f32(x)
+        return ("scalar", chk.average_f32(x), raw / x.size, chk.sum_abs(x) / x.size)
+    if spec_name == "c2-sum-i32":
+        return ("scalar", chk.sum_i32(x), None, None)
+    if spec_name.startswith("c3-toarray"):
+        thr = {"50": 0.5, "01": 0.99, "99": 0.01}[spec_name[-2:]]
+        return ("array", chk.where_gt_select_sq_add(x, thr, 3.0))
+    if spec_name in ("c3-sum", "headline-2p28"):
+        v, raw, _cnt = chk.where_gt_select_sq_add_sum(x, 0.5, 3.0)
+        return ("scalar", v, raw, raw)                      # every term is positive: sum|x| == sum
+    if spec_name == "c4-zipdot":
+        v, raw, sum_abs = chk.zip_mul_sum(x, host[1])
+        return ("scalar", v, raw, sum_abs)
+    if spec_name == "c4-i64-where":
+        return ("array", chk.where_mask_eq_i64(x, 0xF, 3))
+    raise KeyError(spec_name)
+
+
+def measure_config(acc, name, steps, warmup, log2n=None, check=True):
+    """K launches of one configuration's fused kernel on device-resident input (CUDA events on the launching stream, median),
+    then the result of the last launch against the oracle on the same seeded input. Returns a dict for the JSON line."""
+    import torch
+    from dotcompute_b200 import native as N
+    from dotcompute_b200.accelerator import dcb_type
+    from dotcompute_b200.linq import CompiledPipeline
+    from dotcompute_b200.sharded import finalize_record
+
+    spec = CONFIG_WORKLOADS[name]
+    n = 1 << (log2n or spec["log2n"])
     host = spec["gen"](n)
     bufs = [acc.Memory.AllocateAndCopyAsync(h) for h in host]
     kinds = {"S": N.OP_SELECT, "W": N.OP_WHERE, "Z": N.OP_ZIP}
     terms = {"ToArray": N.OP_TOARRAY, "Sum": N.OP_SUM, "Min": N.OP_MIN, "Max": N.OP_MAX, "Average": N.OP_AVERAGE, "Count": N.OP_COUNT}
-    ops = tuple((kinds[k], lam) for k, lam in spec["ops"]) + ((terms[spec["term"]], None),)
+    terminal = terms[spec["term"]]
+    ops = tuple((kinds[k], lam) for k, lam in spec["ops"]) + ((terminal, None),)
     pipe = CompiledPipeline(acc, dcb_type(host[0].dtype), dcb_type(host[1].dtype) if len(host) > 1 else 0, ops)
     out = acc.Memory.AllocateAsync(n, pipe.out_dtype) if spec["term"] == "ToArray" else None
     rec = acc.Memory.AllocateAsync(16, np.int64)
@@ -100,19 +134,19 @@ def run_config(args) -> int:
     outp = C.c_void_p(out.GetDeviceMemory()) if out else None
     stream = torch.cuda.Stream()
     sh = stream.cuda_stream
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if n * host[0].itemsize < (256 << 20) else None
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if n * host[0].itemsize * len(host) < (256 << 20) else None
 
     def step():
         N.check(N.lib().dcb_pipeline_run_async(pipe.handle, in0, in1, n, outp, n if out else 0, C.c_void_p(rec.GetDeviceMemory()), None,
                                                C.c_void_p(sh)), acc.handle)
 
     with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             step()
         stream.synchronize()
         l0 = acc.LaunchCount
         times = []
-        for _ in range(args.steps):
+        for _ in range(steps):
             if flush is not None:
                 flush.fill_(1)              # inputs smaller than L2 would otherwise be served from it
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -120,20 +154,52 @@ def run_config(args) -> int:
             stream.synchronize()
             times.append(a.elapsed_time(b))
         launches = acc.LaunchCount - l0
-    count = int(rec.ToArray()[N.SLOT_COUNT]) if spec["term"] in ("ToArray", "Count", "Average", "Min", "Max") else n
+    rec_host = rec.ToArray()
+    has_where = any(k == "W" for k, _ in spec["ops"])
+    count = int(rec_host[N.SLOT_COUNT]) if (has_where or spec["term"] in ("Count", "Average", "Min", "Max")) else n   # a plain map writes no record
     sel = count / n if spec["term"] == "ToArray" else 1.0
     ms = statistics.median(times)
     peak, kind = measured_peak_gbs()
     gbs = n * spec["bytes"](sel) / (ms * 1e-3) / 1e9
+    parity = None
+    if check:
+        import oracle
+        want = _expected(name, host, oracle.c_oracle())
+        if want[0] == "array":
+            got = out.CopyToAsync(count=count) if count else np.empty(0, pipe.out_dtype)
+            parity = bool(got.dtype == want[1].dtype and got.size == want[1].size and
+                          np.array_equal(got.view(np.uint8), want[1].view(np.uint8)))
+        else:
+            value = pipe.scalar(finalize_record(rec_host, terminal, pipe.info.out_type))
+            _k, exp, raw, sum_abs = want
+            parity = bool(value == exp)
+            if raw is not None:             # floating reductions: also the tolerance rule against the fp64 value
+                parity = parity and bool(abs(float(value) - raw) <= 1e-5 * sum_abs)
+    for b in bufs:
+        b.Dispose()
+    if out:
+        out.Dispose()
+    rec.Dispose()
+    return {"what": spec["what"], "n_elements": n, "ms": ms, "ms_best": min(times), "elements_per_s": n / (ms * 1e-3),
+            "bytes_per_element": spec["bytes"](sel), "selectivity": sel, "achieved_gbs": gbs, "frac": gbs / peak, "peak_kind": kind,
+            "parity": parity, "gpu_launches": int(launches), "precompiled_kernel": bool(pipe.precompiled),
+            "l2": "L2 flushed between launches (256 MiB write)" if flush is not None else "input larger than L2",
+            "dtype": str(host[0].dtype)}
+
+
+def run_config(args) -> int:
+    """One of the secondary configurations on its own: one JSON line in the shape of the headline's."""
+    from dotcompute_b200 import CudaAccelerator
+    acc = CudaAccelerator(0)
+    m = measure_config(acc, args.workload, args.steps, args.warmup, args.log2n if args.log2n != 30 else None, not args.no_check)
     print(json.dumps({
-        "metric": "kernel elements/s, device-resident (secondary configuration)", "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "ms_best": min(times), "higher_is_better": True,
-        "scaling": "n/a", "vs_baseline": None, "dtype": str(host[0].dtype), "data": "synthetic",
-        "config": {"workload": spec["what"], "n_elements": n, "selectivity": sel,
-                   "l2": "L2 flushed between launches (256 MiB write)" if flush is not None else "input larger than L2"},
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
-                     "peak_kind": kind, "bytes_per_element": spec["bytes"](sel)},
-        "gpu_launches": int(launches), "precompiled_kernel": bool(pipe.precompiled)}))
+        "metric": "kernel elements/s, device-resident (secondary configuration)", "value": m["elements_per_s"], "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m["ms"], "ms_best": m["ms_best"], "higher_is_better": True,
+        "scaling": "n/a", "vs_baseline": None, "dtype": m["dtype"], "data": "synthetic",
+        "config": {"workload": m["what"], "n_elements": m["n_elements"], "selectivity": m["selectivity"], "l2": m["l2"]},
+        "roofline": {"bound": "hbm", "achieved": m["achieved_gbs"], "peak": measured_peak_gbs()[0], "unit": "GB/s", "frac": m["frac"],
+                     "traffic": None, "peak_kind": m["peak_kind"], "bytes_per_element": m["bytes_per_element"]},
+        "parity": m["parity"], "gpu_launches": m["gpu_launches"], "precompiled_kernel": m["precompiled_kernel"]}))
     return 0
 
 
@@ -148,6 +214,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the result")
+    ap.add_argument("--no-extras", action="store_true", help="skip the ToArray half of config 5 and the other reductions")
+    ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration block of the 1-GPU run")
+    ap.add_argument("--config-steps", type=int, default=10, help="timed launches per secondary configuration")
     ap.add_argument("--combine", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange of partial sums: inside the reduce kernel over NVLink peer stores (fused) or an NCCL all-reduce")
     ap.add_argument("--no-numa", action="store_true", help="do not bind the process to the GPU's NUMA node")
@@ -159,7 +228,7 @@ def parse_args():
                     help="c5-sum (default, the headline) or one of the other benchmark configurations, 1 GPU, kernel-only")
     args = ap.parse_args()
     if args.profile:
-        args.no_e2e = args.no_cpu_baseline = args.no_check = True
+        args.no_e2e = args.no_cpu_baseline = args.no_check = args.no_extras = args.no_configs = True
     return args
 
 
@@ -298,13 +367,12 @@ def cpu_baseline(n_total: int, time_limit_s: float = 12.0) -> dict:
 
 def run_reference(args) -> int:
     """--impl reference: the reference's CPU implementation of the path (restated SIMD loops), all host threads, on the
-    same workload. Rank 0 alone works; other ranks leave."""
+    same workload: every step is one pass over all 2^log2n elements. Rank 0 alone works; other ranks leave."""
     if int(os.environ.get("RANK", "0")) != 0:
         return 0
     import oracle
     simd = oracle.cpu_simd()
-    n_total = 1 << args.log2n
-    n = min(n_total, 1 << 28)          # bounded sample: each step is one pass over 2^28 elements of the workload
+    n = 1 << args.log2n
     x = gen_shard(0, n)
     for _ in range(max(args.warmup, 1)):
         got = simd.where_select_sum(x, THRESHOLD, ADDEND)
@@ -313,20 +381,137 @@ def run_reference(args) -> int:
         got = simd.where_select_sum(x, THRESHOLD, ADDEND)
     dt = time.perf_counter() - t0
     eps = n * args.steps / dt
+    t0 = time.perf_counter()
+    m = min(n, 1 << 27)
+    simd.scalar_where_select_sum(x[:m], THRESHOLD, ADDEND)
+    scalar_eps = m / (time.perf_counter() - t0)
     want, raw, _cnt = oracle.c_oracle().where_gt_select_sq_add_sum(x, THRESHOLD, ADDEND)
-    sample = (f"each step = one pass over the first 2^{int(np.log2(n))} elements of the 2^{args.log2n} workload; {simd.variant}, "
-              f"{simd.threads} threads; C++ restatement of the reference's CPU SIMD backend (the C#/.NET original cannot run here)")
+    sample = (f"each step = one pass over all 2^{args.log2n} elements of the workload; {simd.variant}, {simd.threads} threads; "
+              f"C++ restatement of the reference's CPU SIMD backend (the C#/.NET original cannot run here)")
     line = {
         "impl": "reference", "metric": METRIC, "value": eps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"Where(x>0.5f).Select(x*x+3f).Sum(), 2^{args.log2n} float32 uniform[0,1) seed 31 (CPU: 2^{int(np.log2(n))} sample per step)"},
-        "cpu_baseline": {"value": eps, "unit": UNIT, "cores": simd.threads, "kind": "port", "sample": sample},
+        "config": {"workload": f"C5: Where(x>0.5f).Select(x*x+3f).Sum() over 2^{args.log2n} float32 uniform[0,1) seed 31, contiguous shards",
+                   "n_elements": n},
+        "cpu_baseline": {"value": eps, "unit": UNIT, "cores": simd.threads, "kind": "port", "sample": sample,
+                         "scalar_1thread": scalar_eps,
+                         "scalar_1thread_note": "the one-thread scalar loop is what the shipped provider really runs for this query (System.Linq fallback)"},
         "e2e": {"value": eps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "rel_err_vs_fp64": abs(float(got) - raw) / raw,   # fp32 lane accumulators, as in the reference's SIMD Sum
+        # fp32 lane accumulators, as in the reference's SIMD Sum: its own error, outside the 1e-5 rule the GPU path meets
+        "rel_err_vs_fp64": abs(float(got) - raw) / raw,
     }
     print(json.dumps(line))
     return 0
+
+
+def toarray_block(args, acc, q, pinned, stream, world, rank, device, fused, barrier):
+    """Config 5's other half: Where -> Select -> ToArray over the same shards. Each rank compacts its shard; the survivor
+    counts are exchanged by the one-warp peer-store kernel behind the compaction (no NCCL, no host round trip), which leaves
+    the rank's output offset and the global total in the record. Checked: the rank's output against the oracle on its own
+    shard, bit for bit; offset == sum of the lower ranks' counts; total == sum of all counts."""
+    import torch
+    import torch.distributed as dist
+    from dotcompute_b200 import native as N
+    import oracle
+
+    n_local = q.local.Length
+    pipe = q.pipeline(N.OP_TOARRAY)
+    out = acc.Memory.AllocateAsync(max(n_local, 1), np.float32)
+    rec = torch.zeros(N.SLOT_NSLOTS, dtype=torch.int64, device=device)
+    steps = max(3, min(args.steps, 10))
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            q.enqueue_compact(out, stream, rec)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(steps):
+            q.enqueue_compact(out, stream, rec)
+        t1.record(stream)
+        barrier()
+        ms = t0.elapsed_time(t1) / steps
+        # the compaction kernel alone (eventful pass, no exchange), for the roofline fraction of this kernel
+        ka, kb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kms = []
+        for _ in range(steps):
+            ka.record(stream)
+            N.check(N.lib().dcb_pipeline_run_async(pipe.handle, C.c_void_p(q.local.GetDeviceMemory()), None, n_local,
+                                                   C.c_void_p(out.GetDeviceMemory()), n_local, C.c_void_p(rec.data_ptr()), None,
+                                                   C.c_void_p(stream.cuda_stream)), acc.handle)
+            kb.record(stream)
+            stream.synchronize()
+            kms.append(ka.elapsed_time(kb))
+        if fused:                                            # leave the record exchanged, as after a full step
+            N.check(N.lib().dcb_peer_exchange_async(acc.handle, C.c_void_p(rec.data_ptr()), pipe.info.out_type,
+                                                    C.c_void_p(stream.cuda_stream)), acc.handle)
+        stream.synchronize()
+    host = rec.cpu().numpy()
+    if fused:
+        local_count, offset, total = int(host[N.SLOT_LOCAL_COUNT]), int(host[N.SLOT_OFFSET]), int(host[N.SLOT_COUNT])
+    else:
+        local_count = int(host[N.SLOT_COUNT])
+        offset = total = None
+    want = oracle.c_oracle().where_gt_select_sq_add(pinned.array, THRESHOLD, ADDEND)
+    got = out.CopyToAsync(count=local_count) if local_count else np.empty(0, np.float32)
+    data_ok = bool(got.size == want.size and np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+    counts = [want.size]
+    if world > 1:
+        allc = [torch.zeros(1, dtype=torch.int64, device=device) for _ in range(world)]
+        dist.all_gather(allc, torch.tensor([want.size], dtype=torch.int64, device=device))
+        counts = [int(c.item()) for c in allc]
+    if not fused:
+        offset, total = sum(counts[:rank]), sum(counts)      # the NCCL route: offsets from the all-gather of counts
+    offsets_ok = bool(offset == sum(counts[:rank]) and total == sum(counts))
+    t = torch.tensor([ms, statistics.median(kms), 0.0 if data_ok else 1.0, 0.0 if offsets_ok else 1.0], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out.Dispose()
+    ms, kms_med, bad_data, bad_off = (float(v) for v in t)
+    n_total = 1 << args.log2n
+    s_all = sum(counts) / n_total
+    peak, _kind = measured_peak_gbs()
+    gbs_gpu = n_local * (4.0 + 4.0 * local_count / max(n_local, 1)) / (kms_med * 1e-3) / 1e9
+    return {"workload": f"C5: Where(x>0.5f).Select(x*x+3f).ToArray() over 2^{args.log2n} float32, contiguous shards, output in rank order",
+            "ms_per_step": ms, "elements_per_s": n_total / (ms * 1e-3), "steps": steps, "selectivity": s_all,
+            "bytes_per_element": 4.0 + 4.0 * s_all, "kernel_ms": kms_med, "kernel_gbs_per_gpu": gbs_gpu, "frac": gbs_gpu / peak,
+            "parity": bad_data == 0.0, "offsets_ok": bad_off == 0.0, "total_survivors": int(sum(counts)),
+            "offset_rank0": 0, "exchange": ("one-warp peer-store kernel behind the compaction (offset and total in the record)" if fused
+                                            else ("none (1 GPU)" if world == 1 else "all-gather of counts (NCCL)"))}
+
+
+def reductions_parity_block(args, acc, dev, pinned, world, rank, device, ops):
+    """Min / Max / Average / Count of the mapped survivors (f32) and Sum over an int32 shard, through the same exchange as
+    the headline Sum; every result against the oracle's, combined over the ranks on the host."""
+    import torch
+    import torch.distributed as dist
+    from dotcompute_b200 import native as N
+    from dotcompute_b200.sharded import ShardedQuery
+    import oracle
+
+    chk = oracle.c_oracle()
+    want = chk.where_gt_select_sq_add(pinned.array, THRESHOLD, ADDEND)
+    w64 = want.astype(np.float64)
+    xi = (pinned.array * np.float32(2001.0)).astype(np.int32) - np.int32(1000)        # ints in [-1000, 1000]
+    local = [float(want.min()) if want.size else float("inf"), float(want.max()) if want.size else float("-inf"),
+             float(w64.sum()), float(np.abs(w64).sum()), float(want.size), float(xi.astype(np.int64).sum())]
+    allv = [local]
+    if world > 1:
+        allv = [None] * world
+        dist.all_gather_object(allv, local)
+    g_min, g_max = min(v[0] for v in allv), max(v[1] for v in allv)
+    g_sum, g_abs, g_cnt, g_isum = (sum(v[i] for v in allv) for i in (2, 3, 4, 5))
+    q = ShardedQuery(acc, dev, ops)
+    got_min, got_max, got_avg, got_cnt = q.Min(), q.Max(), q.Average(), q.Count()
+    di = acc.Memory.AllocateAndCopyAsync(xi)
+    got_isum = ShardedQuery(acc, di, ()).Sum()
+    di.Dispose()
+    detail = {"min": bool(float(got_min) == g_min), "max": bool(float(got_max) == g_max), "count": bool(int(got_cnt) == int(g_cnt)),
+              "average": bool(abs(float(got_avg) - g_sum / g_cnt) <= 1e-5 * g_abs / g_cnt), "sum_i32": bool(int(got_isum) == int(g_isum))}
+    ok = torch.tensor([1 if all(detail.values()) else 0], dtype=torch.int32, device=device)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return bool(int(ok[0])), detail
 
 
 def main() -> int:
@@ -547,6 +732,33 @@ def main() -> int:
                "d2h_bytes_per_step": 128 * n_chunks * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "wall_ms_per_step": wall_ms / e2e_steps, "host_placement": numa_note,
                "note": "pinned host shard -> 32 MiB chunked H2D overlapped with per-chunk kernels -> records D2H; PCIe-bound"}
 
+    # ---- config 5's ToArray half and the other reductions, through the same exchange; the NCCL all-reduce beside it
+    toarray = reductions_ok = reductions_detail = nccl_arm = None
+    if not args.profile and not args.no_extras:
+        toarray = toarray_block(args, acc, q, pinned, stream, world, rank, device, fused, barrier)
+        reductions_ok, reductions_detail = reductions_parity_block(args, acc, dev, pinned, world, rank, device, ops)
+        if world > 1 and fused:
+            from dotcompute_b200.sharded import combine_record
+            recn = torch.zeros(N.SLOT_NSLOTS, dtype=torch.int64, device=device)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    q.launch_local(N.OP_SUM, stream, recn)
+                    combine_record(recn, N.OP_SUM, pipe.info.out_type)
+                barrier()
+                n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                n0.record(stream)
+                for _ in range(args.steps):
+                    q.launch_local(N.OP_SUM, stream, recn)
+                    combine_record(recn, N.OP_SUM, pipe.info.out_type)     # ncclAllReduce of the fp64 partial on the same stream
+                n1.record(stream)
+                barrier()
+            tn = torch.tensor([n0.elapsed_time(n1) / args.steps], dtype=torch.float64, device=device)
+            dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+            got_n = np.float32(finalize_record(recn.cpu().numpy(), N.OP_SUM, pipe.info.out_type).f64)
+            nccl_arm = {"ms_per_step": float(tn[0]), "elements_per_s": n_total / (float(tn[0]) * 1e-3), "result": float(got_n),
+                        "same_result_as_peer_exchange": bool(got_n == got),
+                        "what": "the same K steps with an NCCL all-reduce of the fp64 partial after every kernel (plain launches)"}
+
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         achieved = n_local * BYTES_PER_ELEM / (kernel_ms_mean * 1e-3) / 1e9
@@ -574,8 +786,24 @@ def main() -> int:
         }
         if e2e:
             line["e2e"] = e2e
+        if toarray is not None:
+            line["toarray"] = toarray
+            line["reductions_parity"] = reductions_ok
+            line["reductions_parity_detail"] = reductions_detail
+        if nccl_arm is not None:
+            line["combine_nccl"] = nccl_arm
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(n_total)
+        if world == 1 and not args.profile and not args.no_configs:
+            # Every other benchmark configuration, kernel-only on this GPU, each checked against the oracle.
+            q = None
+            dev.Dispose()
+            cfgs = {}
+            for name in CONFIG_ORDER:
+                m = measure_config(acc, name, args.config_steps, 3)
+                cfgs[name] = {k: m[k] for k in ("what", "n_elements", "ms", "elements_per_s", "bytes_per_element", "selectivity",
+                                                 "achieved_gbs", "frac", "parity", "precompiled_kernel", "l2")}
+            line["configs"] = cfgs
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

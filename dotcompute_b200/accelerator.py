@@ -118,6 +118,16 @@ class CudaAccelerator:
     def Synchronize(self) -> None:
         N.check(N.lib().dcb_stream_sync(self.handle, None), self._h)
 
+    def SetOption(self, option: int, value: int) -> None:
+        """A per-context switch of the native library (native.OPT_*): which compaction kernel runs, the compiled-pipeline
+        cache bound, the host-driven time-out test switch."""
+        N.check(N.lib().dcb_set_option(self.handle, int(option), int(value)), self._h)
+
+    def GetOption(self, option: int) -> int:
+        v = C.c_int64()
+        N.check(N.lib().dcb_get_option(self.handle, int(option), C.byref(v)), self._h)
+        return int(v.value)
+
     def SetSpinLimit(self, max_polls: int) -> None:
         N.check(N.lib().dcb_set_spin_limit(self.handle, int(max_polls)), self._h)
 

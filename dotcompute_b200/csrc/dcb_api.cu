@@ -8,6 +8,7 @@
 #include <nvrtc.h>
 
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -16,6 +17,7 @@
 #include <limits>
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -39,14 +41,21 @@ constexpr size_t kHostChunkBytes = 32u << 20;
 
 thread_local char tl_error[1024] = "";
 
+// Device scratch of one pipeline on one stream. Launches on one stream run one after the other and may share it; launches
+// of the same pipeline on different streams may overlap on the GPU, so every stream gets a set of its own.
 struct Scratch {
     dcb::Partial* partials = nullptr;
     unsigned int* words = nullptr;      // 512 bytes: [0] reduce ticket, [32] [33] tile-id and finished-block counters of the
-                                        // pipelined compaction, [64] compaction abort flag (separate 128-byte lines)
+                                        // persistent compaction kernels, [64] compaction abort flag, [65] "withhold the first
+                                        // count" word of the time-out test (separate 128-byte lines)
     unsigned long long* desc = nullptr; // look-back descriptors
     size_t desc_cap = 0;
     unsigned int epoch = 0;
 };
+
+// Pipelines that exist, so that a handle used after dcb_shutdown or after its eviction is refused instead of followed.
+std::mutex g_live_mu;
+std::set<const void*> g_live_pipelines;
 
 }  // namespace
 
@@ -61,7 +70,16 @@ struct dcb_ctx {
     char err[1024] = "";
     std::mutex mu;
     std::map<std::string, dcb_pipeline*> cache;
-    int64_t bytes_in_use = 0, peak_bytes = 0, n_allocs = 0, launches = 0;
+    int64_t bytes_in_use = 0, peak_bytes = 0, n_allocs = 0;
+    std::atomic<int64_t> launches{0};
+    // Options (dcb_set_option); the initial values come from the environment once, at dcb_init.
+    int opt_compact_kernel = 0;            // DCB_OPT_COMPACT_KERNEL
+    int opt_force_scalar = 0;              // DCB_OPT_FORCE_SCALAR
+    int opt_blocks_per_sm = 0;             // DCB_OPT_BLOCKS_PER_SM (0 = what fits)
+    int opt_withhold_first_count = 0;      // DCB_OPT_WITHHOLD_FIRST_COUNT
+    int opt_cache_max = 100;               // DCB_OPT_CACHE_MAX_ENTRIES (the reference: new KernelCache(maxEntries: 100))
+    uint64_t cache_clock = 0;              // use counter behind the cache's least-recently-used order
+    std::mutex host_mu;                    // serialises dcb_pipeline_run_host: the staging buffers belong to the context
     void* stage_in[2] = {nullptr, nullptr};
     size_t stage_in_cap[2] = {0, 0};
     void* stage_out = nullptr;
@@ -99,7 +117,12 @@ struct dcb_pipeline {
     int rows_vec = 1, rows_scalar = 1;   // compaction rows per warp
     int jit_rows = 0;                    // rows forced by a tuning experiment (0 = automatic)
     int compact_block = 256;             // threads per block of the compaction kernels
-    Scratch sc;
+    const void* k_stream = nullptr;      // streamed compaction kernel (null: the query has none)
+    int stream_rows = 0, stream_warps = 0, stream_nbuf = 0, occ_stream = 1;
+    std::mutex mu;                       // guards `scratch` and every enqueue that uses it
+    std::map<cudaStream_t, Scratch> scratch;
+    std::mutex run_mu;                   // serialises the blocking calls, which share d_result / h_record / ev0 / ev1
+    uint64_t last_use = 0;
     dcb::DeviceResult* d_result = nullptr;
     void* h_record = nullptr;            // pinned, DCB_DEVICE_RESULT_BYTES * kMaxChunks
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -179,21 +202,23 @@ size_t pack_align(int elems, int type) { return (size_t)std::min(16, elems * dcb
 
 int compact_rows(int block, int elems, int out_type) { return dcb::compact_rows_for(block, elems, dcbt::type_size(out_type)); }
 
-dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s) {
+// The scratch set of pipeline `p` for stream `s` (p->mu held), with room for `num_tiles` descriptors. What must start at
+// zero is cleared ON `s`, so the clearing is ordered before the launch that follows on the same stream.
+dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s, Scratch** out) {
     dcb_ctx* ctx = p->ctx;
-    Scratch& sc = p->sc;
+    Scratch& sc = p->scratch[s];
+    *out = &sc;
     if (!sc.partials) {
         CU(ctx, cudaMalloc(&sc.partials, sizeof(dcb::Partial) * kMaxPartials));
         CU(ctx, cudaMalloc(&sc.words, 512));
-        CU(ctx, cudaMemset(sc.words, 0, 512));
+        CU(ctx, cudaMemsetAsync(sc.words, 0, 512, s));
     }
     if ((size_t)num_tiles > sc.desc_cap) {
         size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
         cap = std::max(cap, sc.desc_cap * 2);
-        if (sc.desc) { CU(ctx, cudaStreamSynchronize(s)); CU(ctx, cudaFree(sc.desc)); sc.desc = nullptr; }
-        // two spare descriptors: the pipelined kernel fetches them in aligned pairs
+        if (sc.desc) { CU(ctx, cudaStreamSynchronize(s)); CU(ctx, cudaFree(sc.desc)); sc.desc = nullptr; sc.desc_cap = 0; }
         CU(ctx, cudaMalloc(&sc.desc, (cap + 2) * sizeof(unsigned long long)));
-        CU(ctx, cudaMemset(sc.desc, 0, (cap + 2) * sizeof(unsigned long long)));
+        CU(ctx, cudaMemsetAsync(sc.desc, 0, (cap + 2) * sizeof(unsigned long long), s));
         sc.desc_cap = cap;
         sc.epoch = 0;
     }
@@ -215,6 +240,19 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     p->pipe_nbuf = tuning.pipe_nbuf;
     tuning.pipe_ctrl = env_int("DCB200_PIPE_CTRL", tuning.pipe_ctrl);
     p->pipe_ctrl = tuning.pipe_ctrl;
+    tuning.stream = env_int("DCB200_STREAM", tuning.stream);
+    tuning.stream_warps = env_int("DCB200_STREAM_WARPS", tuning.stream_warps);
+    tuning.stream_rows = env_int("DCB200_STREAM_ROWS", 0);
+    tuning.stream_lag = env_int("DCB200_STREAM_LAG", tuning.stream_lag);
+    tuning.stream_nbuf = env_int("DCB200_STREAM_NBUF", tuning.stream_nbuf);
+    tuning.stream_depth = env_int("DCB200_STREAM_DEPTH", tuning.stream_depth);
+    tuning.stream_ahead_mb = env_int("DCB200_STREAM_AHEAD_MB", tuning.stream_ahead_mb);
+    tuning.stream_min_blocks = env_int("DCB200_STREAM_MINBLOCKS", tuning.stream_min_blocks);
+    tuning.stream_draw_ahead = env_int("DCB200_STREAM_DRAW_AHEAD", tuning.stream_draw_ahead);
+    p->stream_warps = tuning.stream_warps;
+    p->stream_nbuf = tuning.stream_nbuf;
+    p->stream_rows = (tuning.stream && dcbt::stream_rows_for(p->info, tuning.stream_warps) > 0)
+                         ? (tuning.stream_rows > 0 ? tuning.stream_rows : dcbt::stream_rows_for(p->info, tuning.stream_warps)) : 0;
     p->pipe_rows = dcbt::pipe_rows_for(p->info) > 0 ? (tuning.pipe_rows > 0 ? tuning.pipe_rows : dcbt::pipe_rows_for(p->info)) : 0;
     p->unroll = tuning.unroll;
     p->jit_rows = tuning.compact_rows;
@@ -261,6 +299,11 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
         CU(ctx, cudaLibraryGetKernel(&kp, p->lib, "dcb_compact_pipe"));
         p->k_pipe = (const void*)kp;
     }
+    if (p->stream_rows > 0) {
+        cudaKernel_t kst = nullptr;
+        CU(ctx, cudaLibraryGetKernel(&kst, p->lib, "dcb_compact_stream"));
+        p->k_stream = (const void*)kst;
+    }
     return DCB_OK;
 }
 
@@ -281,21 +324,35 @@ dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_pipe, dcbt::pipe_block_threads(p->pipe_ctrl), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_pipe = occ;
         else { (void)cudaGetLastError(); p->k_pipe = nullptr; }   // this device cannot run it: the one-tile-per-block kernel stays
     }
-    const int cap = env_int("DCB200_BLOCKS_PER_SM", 0);
-    if (cap > 0) { p->occ_vec = std::min(p->occ_vec, cap); p->occ_scalar = std::min(p->occ_scalar, cap); p->occ_pipe = std::min(p->occ_pipe, cap); }
+    if (p->k_stream) {
+        const int dyn = (int)dcbt::stream_smem_bytes(p->info, p->stream_rows, p->stream_warps, p->stream_nbuf);
+        if (cudaFuncSetAttribute(p->k_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_stream, dcbt::stream_block_threads(p->stream_warps), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_stream = occ;
+        else { (void)cudaGetLastError(); p->k_stream = nullptr; }
+    }
     CU(ctx, cudaMalloc(&p->d_result, DCB_DEVICE_RESULT_BYTES));
-    CU(ctx, cudaMemset(p->d_result, 0, DCB_DEVICE_RESULT_BYTES));
+    CU(ctx, cudaMemsetAsync(p->d_result, 0, DCB_DEVICE_RESULT_BYTES, ctx->stream));
     CU(ctx, cudaHostAlloc(&p->h_record, DCB_DEVICE_RESULT_BYTES, cudaHostAllocDefault));
     CU(ctx, cudaEventCreate(&p->ev0));
     CU(ctx, cudaEventCreate(&p->ev1));
-    return ensure_scratch(p, 0, ctx->stream);
+    {
+        std::lock_guard<std::mutex> g(g_live_mu);
+        g_live_pipelines.insert(p);
+    }
+    return DCB_OK;
 }
 
 void free_pipeline(dcb_pipeline* p) {
     if (!p) return;
-    if (p->sc.partials) cudaFree(p->sc.partials);
-    if (p->sc.words) cudaFree(p->sc.words);
-    if (p->sc.desc) cudaFree(p->sc.desc);
+    {
+        std::lock_guard<std::mutex> g(g_live_mu);
+        g_live_pipelines.erase(p);
+    }
+    for (auto& kv : p->scratch) {
+        if (kv.second.partials) cudaFree(kv.second.partials);
+        if (kv.second.words) cudaFree(kv.second.words);
+        if (kv.second.desc) cudaFree(kv.second.desc);
+    }
     if (p->d_result) cudaFree(p->d_result);
     if (p->h_record) cudaFreeHost(p->h_record);
     if (p->ev0) cudaEventDestroy(p->ev0);
@@ -395,6 +452,11 @@ extern "C" dcb_status dcb_init(int32_t device, dcb_ctx** out_ctx) {
     ctx->cc_major = prop.major;
     ctx->cc_minor = prop.minor;
     ctx->spin_limit = (uint32_t)env_int("DCB200_SPIN_LIMIT", 1 << 22);
+    // The environment is read here, once; afterwards these are changed with dcb_set_option.
+    ctx->opt_compact_kernel = env_int("DCB200_COMPACT_KERNEL", 0);
+    ctx->opt_force_scalar = env_int("DCB200_FORCE_SCALAR", 0);
+    ctx->opt_blocks_per_sm = env_int("DCB200_BLOCKS_PER_SM", 0);
+    ctx->opt_cache_max = std::max(1, env_int("DCB200_CACHE_MAX_ENTRIES", 100));
     if (prop.major != 10) {
         delete ctx;
         return set_err(nullptr, DCB_ERR_NO_DEVICE, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
@@ -467,6 +529,42 @@ extern "C" dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls) {
     ctx->peer_spin_limit = max_polls;
     ctx->peers.spin_limit = max_polls;
     return DCB_OK;
+}
+
+extern "C" dcb_status dcb_set_option(dcb_ctx* ctx, int32_t option, int64_t value) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    switch (option) {
+        case DCB_OPT_COMPACT_KERNEL:
+            NEED(ctx, value >= 0 && value <= 2, "DCB_OPT_COMPACT_KERNEL takes 0 (automatic), 1 (one tile per block) or 2 (round-based)");
+            ctx->opt_compact_kernel = (int)value; return DCB_OK;
+        case DCB_OPT_FORCE_SCALAR: ctx->opt_force_scalar = value != 0; return DCB_OK;
+        case DCB_OPT_BLOCKS_PER_SM:
+            NEED(ctx, value >= 0 && value <= 32, "DCB_OPT_BLOCKS_PER_SM takes 0 (what fits) to 32");
+            ctx->opt_blocks_per_sm = (int)value; return DCB_OK;
+        case DCB_OPT_WITHHOLD_FIRST_COUNT: ctx->opt_withhold_first_count = value != 0; return DCB_OK;
+        case DCB_OPT_CACHE_MAX_ENTRIES:
+            NEED(ctx, value >= 1 && value <= (1 << 20), "DCB_OPT_CACHE_MAX_ENTRIES takes 1 to 2^20");
+            ctx->opt_cache_max = (int)value; return DCB_OK;
+        default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "unknown option %d", (int)option);
+    }
+}
+
+extern "C" dcb_status dcb_get_option(dcb_ctx* ctx, int32_t option, int64_t* out_value) {
+    dcb_status st = use(ctx);
+    if (st) return st;
+    NEED(ctx, out_value != nullptr, "out_value is null");
+    std::lock_guard<std::mutex> g(ctx->mu);
+    switch (option) {
+        case DCB_OPT_COMPACT_KERNEL: *out_value = ctx->opt_compact_kernel; return DCB_OK;
+        case DCB_OPT_FORCE_SCALAR: *out_value = ctx->opt_force_scalar; return DCB_OK;
+        case DCB_OPT_BLOCKS_PER_SM: *out_value = ctx->opt_blocks_per_sm; return DCB_OK;
+        case DCB_OPT_WITHHOLD_FIRST_COUNT: *out_value = ctx->opt_withhold_first_count; return DCB_OK;
+        case DCB_OPT_CACHE_MAX_ENTRIES: *out_value = ctx->opt_cache_max; return DCB_OK;
+        case DCB_OPT_CACHE_ENTRIES: *out_value = (int64_t)ctx->cache.size(); return DCB_OK;
+        default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "unknown option %d", (int)option);
+    }
 }
 
 // ============================================================================================ memory
@@ -713,8 +811,21 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
     auto it = ctx->cache.find(cache_key);
     if (it != ctx->cache.end()) {
         it->second->refs += 1;
+        it->second->last_use = ++ctx->cache_clock;
         *out_pipeline = it->second;
         return DCB_OK;
+    }
+    // Bounded cache, as the reference's KernelCache(maxEntries: 100): before a new entry goes in, the least recently
+    // used entries that nobody holds (every dcb_pipeline_compile matched by a dcb_pipeline_destroy) are dropped with
+    // their module and scratch. Entries still held stay, so the bound can be exceeded while handles are outstanding.
+    while ((int)ctx->cache.size() >= ctx->opt_cache_max) {
+        auto victim = ctx->cache.end();
+        for (auto c = ctx->cache.begin(); c != ctx->cache.end(); ++c)
+            if (c->second->refs == 0 && (victim == ctx->cache.end() || c->second->last_use < victim->second->last_use)) victim = c;
+        if (victim == ctx->cache.end()) break;
+        CU(ctx, cudaDeviceSynchronize());     // nothing of the victim's may still be running when its memory goes
+        free_pipeline(victim->second);
+        ctx->cache.erase(victim);
     }
     dcb_pipeline* p = new dcb_pipeline();
     p->ctx = ctx;
@@ -730,6 +841,10 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->pipe_rows = b->pipe_rows;
         p->pipe_nbuf = b->pipe_nbuf;
         p->pipe_ctrl = b->pipe_ctrl;
+        p->k_stream = b->k_stream;
+        p->stream_rows = b->stream_rows;
+        p->stream_warps = b->stream_warps;
+        p->stream_nbuf = b->stream_nbuf;
         p->source.clear();
     } else if ((st = load_jit(ctx, p)) != DCB_OK) {
         free_pipeline(p);
@@ -737,6 +852,7 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
     }
     if ((st = finish_pipeline(ctx, p)) != DCB_OK) { free_pipeline(p); return st; }
     p->compile_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    p->last_use = ++ctx->cache_clock;
     ctx->cache[cache_key] = p;
     *out_pipeline = p;
     return DCB_OK;
@@ -744,8 +860,13 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
 
 extern "C" dcb_status dcb_pipeline_destroy(dcb_pipeline* p) {
     if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
-    // Pipelines live in their context's cache until dcb_shutdown; destroy only drops the caller's reference.
-    std::lock_guard<std::mutex> g(p->ctx->mu);
+    // A pipeline stays in its context's cache; destroy only drops the caller's reference, after which the cache may
+    // evict it. A handle whose pipeline is already gone (its context was shut down) is refused, not followed.
+    {
+        std::lock_guard<std::mutex> live(g_live_mu);
+        if (!g_live_pipelines.count(p)) return set_err(nullptr, DCB_ERR_DISPOSED, "pipeline was already released with its context");
+    }
+    std::lock_guard<std::mutex> g(p->ctx->mu);   // the caller's reference keeps the cache from evicting it meanwhile
     if (p->refs > 0) p->refs -= 1;
     return DCB_OK;
 }
@@ -805,28 +926,40 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
     bool vec = aligned_to(in0, 16);
     if (I.n_in == 2) vec = vec && aligned_to(in1, pack_align(e_vec, I.in1));
     if (to_array) vec = vec && aligned_to(out, pack_align(e_vec, I.out_type)) ;
-    if (env_int("DCB200_FORCE_SCALAR", 0)) vec = false;
+    if (ctx->opt_force_scalar) vec = false;
     const void* fn = vec ? p->k_vec : p->k_scalar;
     const int E = vec ? e_vec : 1;
     long long nn = n;
+    const int occ_cap = ctx->opt_blocks_per_sm > 0 ? ctx->opt_blocks_per_sm : (1 << 20);
+    std::lock_guard<std::mutex> guard(p->mu);   // the scratch of (pipeline, stream) and the order of enqueues that use it
 
     if (to_array && !I.has_filter) {
         NEED(ctx, out_cap >= n, "output capacity below the element count");
         if (n == 0) return DCB_OK;
         const int unroll = vec ? p->unroll : p->unroll * 2;
         const int64_t tiles = (n / E + (int64_t)kBlock * unroll - 1) / ((int64_t)kBlock * unroll);
-        const int64_t max_grid = (int64_t)ctx->sm_count * (vec ? p->occ_vec : p->occ_scalar);
+        const int64_t max_grid = (int64_t)ctx->sm_count * std::min(occ_cap, vec ? p->occ_vec : p->occ_scalar);
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out};
         if (launches) *launches += 1;
         return launch(ctx, fn, grid, args, s);
     }
     if (to_array) {
-        // The pipelined kernel moves whole tiles with 16-byte bulk copies: both inputs 16-byte aligned, vector output.
-        const bool pipe = vec && p->k_pipe && env_int("DCB200_COMPACT_PIPE", 1) != 0 && (I.n_in == 1 || aligned_to(in1, 16));
+        // Which kernel. The streamed kernel takes any element-aligned pointers as long as both inputs sit at the same
+        // element offset from a 16-byte boundary (its bulk copies start at that boundary); the round-based pipelined kernel
+        // needs every pointer 16-byte aligned; the one-tile-per-block kernel takes anything (scalar variant if unaligned).
+        const size_t sz0 = (size_t)dcbt::type_size(I.in0), sz1 = I.n_in == 2 ? (size_t)dcbt::type_size(I.in1) : 1;
+        unsigned int head = (unsigned int)(((uintptr_t)in0 % 16) / sz0);
+        const bool stream_ok = p->k_stream && ctx->opt_compact_kernel == 0 && !ctx->opt_force_scalar && (uintptr_t)in0 % sz0 == 0 &&
+                               (I.n_in == 1 || ((uintptr_t)in1 - (uintptr_t)head * sz1) % 16 == 0);
+        const bool pipe = !stream_ok && vec && p->k_pipe && ctx->opt_compact_kernel != 1 && (I.n_in == 1 || aligned_to(in1, 16));
         const int rows = vec ? p->rows_vec : p->rows_scalar;
-        const int64_t tile = pipe ? (int64_t)dcbt::pipe_tile_elems(I, p->pipe_rows) : (int64_t)(p->compact_block / 32) * rows * 32 * E;
-        long long num_tiles = (n + tile - 1) / tile;
+        if (!stream_ok) head = 0;
+        const int64_t tile = stream_ok ? (int64_t)dcbt::stream_tile_elems(I, p->stream_rows, p->stream_warps)
+                           : pipe      ? (int64_t)dcbt::pipe_tile_elems(I, p->pipe_rows)
+                                       : (int64_t)(p->compact_block / 32) * rows * 32 * E;
+        long long num_tiles = (n + (int64_t)head + tile - 1) / tile;
+        if (n == 0) num_tiles = 0;
         if (num_tiles == 0) {
             // Nothing to scan: the record is the previous one (or zero).
             if (d_prev) CU(ctx, cudaMemcpyAsync(res, d_prev, DCB_DEVICE_RESULT_BYTES, cudaMemcpyDeviceToDevice, s));
@@ -834,9 +967,10 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
             return DCB_OK;
         }
         NEED(ctx, num_tiles < (1ll << 31), "too many tiles for one launch");
-        dcb_status st = ensure_scratch(p, num_tiles, s);
+        Scratch* scp = nullptr;
+        dcb_status st = ensure_scratch(p, num_tiles, s, &scp);
         if (st) return st;
-        Scratch& sc = p->sc;
+        Scratch& sc = *scp;
         sc.epoch += 1;
         if (sc.epoch >= 0x3fffu) {   // epoch field is 14 bits: wipe the descriptors before reusing a value
             CU(ctx, cudaMemsetAsync(sc.desc, 0, sc.desc_cap * sizeof(unsigned long long), s));
@@ -845,17 +979,29 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         }
         unsigned int epoch = sc.epoch, spin = ctx->spin_limit;
         unsigned int* abort_flag = sc.words + 64;
+        if (ctx->opt_withhold_first_count) {
+            // Time-out test switch: the kernel that handles tile 0 finds this launch's epoch in the word next to the abort
+            // flag and keeps that tile's count to itself, so every bounded wait for it runs out.
+            fill_kernel<<<1, 32, 0, s>>>((unsigned char*)(sc.words + 65), 1, (unsigned long long)epoch, 4);
+            CU(ctx, cudaGetLastError());
+        }
         long long cap = out_cap;
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc,
                         (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag};
         if (launches) *launches += 1;
-        if (pipe) {
+        if (stream_ok || pipe) {
             // Persistent blocks, as many as fit the GPU at once (fewer for a small input); tile ids come from counters[0].
             unsigned int* counters = sc.words + 32;
             void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&epoch, (void*)&spin,
-                             (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters};
-            const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * p->occ_pipe);
-            CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads(p->pipe_ctrl)), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
+                             (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters, (void*)&head};
+            if (stream_ok) {
+                const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_stream));
+                CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps)), pargs,
+                                         (size_t)dcbt::stream_smem_bytes(I, p->stream_rows, p->stream_warps, p->stream_nbuf), s));
+            } else {
+                const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_pipe));
+                CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads(p->pipe_ctrl)), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
+            }
             ctx->launches += 1;
             return DCB_OK;
         }
@@ -863,15 +1009,16 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
     }
     // reductions
     {
-        dcb_status st = ensure_scratch(p, 0, s);
+        Scratch* scp = nullptr;
+        dcb_status st = ensure_scratch(p, 0, s, &scp);
         if (st) return st;
         const int unroll = vec ? p->unroll : p->unroll * 2;
         const int64_t tiles = (n / E + (int64_t)kBlock * unroll - 1) / ((int64_t)kBlock * unroll);
-        int64_t max_grid = (int64_t)ctx->sm_count * (vec ? p->occ_vec : p->occ_scalar);
+        int64_t max_grid = (int64_t)ctx->sm_count * std::min(occ_cap, vec ? p->occ_vec : p->occ_scalar);
         max_grid = std::min<int64_t>(max_grid, kMaxPartials);
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
-        unsigned int* ticket = p->sc.words;
-        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&p->sc.partials, (void*)&ticket, (void*)&res};
+        unsigned int* ticket = scp->words;
+        void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&scp->partials, (void*)&ticket, (void*)&res};
         if (launches) *launches += 1;
         return launch(ctx, fn, grid, args, s);
     }
@@ -967,6 +1114,7 @@ extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const v
     memset(result, 0, sizeof *result);
     cudaStream_t s = pick(ctx, stream);
     const bool plain_map = p->info.terminal == DCB_OP_TOARRAY && !p->info.has_filter;
+    std::lock_guard<std::mutex> run_guard(p->run_mu);   // this pipeline's record, host mirror and events are in use until we return
     CU(ctx, cudaEventRecord(p->ev0, s));
     uint32_t launches = 0;
     if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches))) return st;
@@ -1032,6 +1180,8 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     NEED(ctx, n == 0 || host_in0 != nullptr, "host_in0 is null");
     NEED(ctx, I.n_in == 1 || n == 0 || host_in1 != nullptr, "host_in1 is null for a Zip pipeline");
     memset(result, 0, sizeof *result);
+    std::lock_guard<std::mutex> host_guard(ctx->host_mu);   // the staging buffers and chunk records belong to the context
+    std::lock_guard<std::mutex> run_guard(p->run_mu);
     const bool to_array = I.terminal == DCB_OP_TOARRAY;
     const bool compaction = to_array && I.has_filter;
     const size_t sz0 = (size_t)dcbt::type_size(I.in0), sz1 = I.n_in == 2 ? (size_t)dcbt::type_size(I.in1) : 0;
@@ -1180,7 +1330,8 @@ extern "C" dcb_status dcb_peer_connect_local(dcb_ctx* ctx, int32_t world, int32_
     if ((st = ensure_peer_area(ctx))) return st;
     dcb::PeerTable t = {};
     t.world = world; t.rank = rank; t.spin_limit = ctx->peer_spin_limit; t.state = (dcb::PeerState*)ctx->peer_state;
-    CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
+    CU(ctx, cudaMemsetAsync(ctx->peer_state, 0, sizeof(dcb::PeerState), ctx->stream));
+    CU(ctx, cudaStreamSynchronize(ctx->stream));
     for (int r = 0; r < world; ++r) {
         NEED(ctx, areas[r] != nullptr, "an area pointer is null");
         t.area[r] = (dcb::PeerSlot*)(r == rank ? ctx->peer_area : areas[r]);
@@ -1198,7 +1349,8 @@ extern "C" dcb_status dcb_peer_connect(dcb_ctx* ctx, int32_t world, int32_t rank
     NEED(ctx, handles != nullptr && handle_stride >= sizeof(cudaIpcMemHandle_t), "bad handle table");
     dcb::PeerTable t = {};
     t.world = world; t.rank = rank; t.spin_limit = ctx->peer_spin_limit; t.state = (dcb::PeerState*)ctx->peer_state;
-    CU(ctx, cudaMemset(ctx->peer_state, 0, sizeof(dcb::PeerState)));
+    CU(ctx, cudaMemsetAsync(ctx->peer_state, 0, sizeof(dcb::PeerState), ctx->stream));
+    CU(ctx, cudaStreamSynchronize(ctx->stream));
     for (int r = 0; r < world; ++r) {
         if (r == rank) { t.area[r] = (dcb::PeerSlot*)ctx->peer_area; continue; }
         cudaIpcMemHandle_t h;

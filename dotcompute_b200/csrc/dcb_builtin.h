@@ -13,6 +13,10 @@ struct dcb_builtin_entry {
     int pipe_rows;          // rows per warp it was built with
     int pipe_nbuf;          // shared-memory buffers per input it was built with
     int pipe_ctrl;          // 1 = built with the extra offsets warp
+    const void* k_stream;   // streamed compaction kernel, or null when the query has none
+    int stream_rows;        // rows per worker warp it was built with
+    int stream_warps;       // worker warps per block
+    int stream_nbuf;        // shared-memory slots per input
 };
 
 const dcb_builtin_entry* dcb_builtin_find(const char* key);

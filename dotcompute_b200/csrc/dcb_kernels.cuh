@@ -55,7 +55,9 @@ struct __align__(16) DeviceResult {
     i64 imin;        // 7
     i64 imax;        // 8
     u64 flags;       // 9
-    i64 pad[6];
+    i64 offset;      // 10: after an exchange between GPUs: survivors (elements counted) on lower ranks; else 0
+    i64 local_count; // 11: after an exchange: this GPU's own count (slot 4 then holds the total); else equal to slot 4
+    i64 pad[4];
 };
 
 // Per-block partial of a reduction, also the shared-memory exchange format.
@@ -462,6 +464,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         if constexpr (is_fp<O>::value) { res->fmin = __longlong_as_double(p.mn_bits); res->fmax = __longlong_as_double(p.mx_bits); res->imin = 0; res->imax = 0; }
         else { res->fmin = 0; res->fmax = 0; res->imin = p.mn_bits; res->imax = p.mx_bits; }
         res->flags = p.flags;
+        res->offset = 0; res->local_count = p.count;
         *ticket = 0;   // ready for the next launch on this stream
     }
 }
@@ -503,7 +506,7 @@ template <class C, int BLOCK, bool VEC> struct compact_rows {
 // FULL = the whole tile lies inside the array, so no element needs a bound check.
 template <class C, int ROWS, int E, bool FULL>
 __device__ __forceinline__ int compact_rank_and_stage(const Pack<typename C::in0_t, E> (&a)[ROWS], const Pack<typename C::in1_t, E> (&b)[ROWS],
-                                                      i64 n, i64 warp_base, int lane, typename C::out_t* stage) {
+                                                      i64 n, i64 warp_base, int lane, typename C::out_t* stage, i64 lo = 0) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     // Per-row survivor counts of a lane are packed FIELD bits apiece into 32-bit words, so one shuffle scan ranks
     // several rows at once. A row total is at most 32*E, which fits 8 bits up to E = 4 (128 = 0x80), else 16.
@@ -525,7 +528,10 @@ __device__ __forceinline__ int compact_rank_and_stage(const Pack<typename C::in0
             bool keep;
             if constexpr (C::n_in == 2) keep = C::apply(a[r].e[k], b[r].e[k], val[r][k]);
             else keep = C::apply(a[r].e[k], B(), val[r][k]);
-            if constexpr (!FULL) keep = keep && (warp_base + ((i64)r * 32 + lane) * E + k < n);
+            if constexpr (!FULL) {
+                const i64 idx = warp_base + ((i64)r * 32 + lane) * E + k;
+                keep = keep && idx < n && idx >= lo;
+            }
             bits |= (keep ? 1u : 0u) << k;
         }
         keepbits[r] = bits;
@@ -696,9 +702,10 @@ __device__ __forceinline__ void compact_copy_out(O* __restrict__ out, i64 out_ca
         O* __restrict__ dst = out + base;
         constexpr int VO = (sizeof(O) == 4 || sizeof(O) == 8) ? 16 / (int)sizeof(O) : 1;
         if constexpr (VEC && VO > 1) {
-            // `out` is 16-byte aligned in the vector kernels: a few single elements up to the next 16-byte boundary, then
-            // 16-byte stores (one instruction moves VO elements), then the last few.
-            int head = (int)((VO - (base & (VO - 1))) & (VO - 1));
+            // A few single elements up to the next 16-byte boundary of the destination, then 16-byte stores (one
+            // instruction moves VO elements), then the last few. Works for any element-aligned `out`.
+            const int mis = (int)(((unsigned long long)dst & 15ull) / sizeof(O));
+            int head = (VO - mis) & (VO - 1);
             if (head > warp_run) head = warp_run;
             if (lane < head) dst[lane] = stage[lane];
             const int nvec = (warp_run - head) / VO;
@@ -788,7 +795,10 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
     if (warp == 0) {
         if (tile == 0) {
             if (lane == 0) {
-                desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)tile_total));
+                // abort_flag[1] == epoch withholds this count: a host-driven test of the time-out path (every later tile
+                // then waits, bounded, for a count that never comes)
+                if (*(volatile unsigned int*)(abort_flag + 1) != epoch)
+                    desc_store(desc + tile, desc_make(epoch, ST_INCLUSIVE, (u64)tile_total));
                 s_prefix = prev ? prev->count : 0;
             }
         } else {
@@ -819,7 +829,10 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
         const i64 total = prefix + tile_total;
         res->count = total; res->count_f = (double)total;
         res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+        res->offset = 0; res->local_count = total;
         res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+        // A tile that gave up left FLAG_TIMEOUT and raised the abort word; do not cover that with a success record.
+        if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->local_count = 0; res->flags = (u64)FLAG_TIMEOUT; }
     }
 }
 
@@ -1306,6 +1319,312 @@ __device__ __forceinline__ void compact_pipe_free_body(const typename C::in0_t* 
         if (finished == gridDim.x - 1) {
             __threadfence();
             if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT; }
+            counters[0] = 0; counters[1] = 0;
+        }
+    }
+}
+
+
+// ------------------------------------------------------------------ compact, streamed: warp-specialised persistent blocks
+// Same result as compact_body, built so that nothing on the data path waits for anything but data.
+//
+// A block is WARPS worker warps, one offsets warp and one loader thread. It works through tiles of WARPS * ROWS * 512
+// bytes whose ids the loader draws from a counter; tile r of the block lives in slot r % NBUF of a ring of shared-memory
+// buffers. Four shared-memory barriers per slot hand a tile from one role to the next; there is no block-wide barrier
+// between the first and the last tile:
+//
+//   loader    waits for `empty` (the slot's previous tile has been written out), draws an id, starts the bulk copy of the
+//             tile's input into the slot (completing on `full`), and asks L2 for a tile some block will draw a few rounds
+//             from now, so that the copies themselves are served from L2;
+//   worker w  waits for `full`, ranks its 1/WARPS of the tile and stages the survivors in place, over the input it has just
+//             read (hence sizeof(out) <= sizeof(in0)), leaves its count in shared memory and arrives on `ranked`; then it
+//             turns to the tile it ranked LAG rounds ago, waits for `offs` (normally long complete), copies its run to the
+//             output with 16-byte stores and arrives on `empty`. Workers never wait for each other;
+//   offsets   waits for `ranked`, publishes the tile's count (one relaxed 64-bit store), then finishes the tile of the round
+//             before: its output offset is the offset after the block's previous tile plus the counts of the tiles drawn
+//             in between, a known range of descriptors read with all loads in flight at once (their tiles were ranked a
+//             round ago as well, so the counts are normally there); it leaves one offset per worker in shared memory and
+//             arrives on `offs`.
+//
+// The look-back is therefore one round trip to L2 beside the workers, LAG rounds before a worker asks for its result. Progress:
+// a tile's offset needs only counts of tiles with smaller ids; an id is drawn by a running block at the moment its copy
+// is started, and ranking never waits for another block, so the smallest id not yet counted is always about to be.
+// Nothing is assumed about how many blocks are resident. Every wait is bounded: polls of a descriptor by `spin_limit`,
+// waits on the block's own barriers and copies by a fixed number of clock cycles; a wait that runs out marks the block dead, raises the
+// epoch-tagged abort word for the other blocks, and the launch ends with FLAG_TIMEOUT in the record.
+//
+// Alignment: bulk copies need 16-byte aligned sources, so the kernel works in a shifted index space that starts `head`
+// elements before in0 (at the 16-byte boundary below it; in1 must be displaced by the same number of elements). Tiles
+// that are not wholly inside [head, head + n) - the first one if head > 0, the last one if ragged - are read with plain
+// bounds-checked loads. `out` needs element alignment only.
+//
+// `counters[0]` hands out tile ids, `counters[1]` counts finished blocks; both are zero at launch and the last block
+// to finish zeroes them again. `abort_flag[1] == epoch` withholds the count of tile 0 (a host-driven test of the time-out
+// path: every offset then waits for a count that never comes). Launch with (WARPS + 2) * 32 threads and
+// NBUF * tile bytes of dynamic shared memory for each input.
+// Limit of one wait on a block's own barrier or bulk copy, in SM clock cycles (about two seconds). It is measured with
+// the SM's cycle counter, which costs a few cycles to read; the nanosecond timer shared by the whole GPU takes microseconds
+// per read, which a wait on the data path cannot afford.
+#ifndef DCB_STREAM_WAIT_CYCLES
+#define DCB_STREAM_WAIT_CYCLES 4000000000ll
+#endif
+__device__ __forceinline__ void l2_prefetch_bulk(const void* src_global, u32 bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
+}
+
+template <class C, int WARPS, int ROWS, int LAG, int NBUF, int DEPTH, int AHEAD_BYTES, int DRAW_AHEAD>
+__device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                    i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
+                                                    u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
+                                                    const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
+                                                    unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters, u32 head) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
+    static_assert(LAG >= 1 && NBUF >= LAG + 2 && NBUF <= 16, "NBUF = LAG + 1 + tiles on their way in");
+    static_assert(WARPS >= 1 && WARPS <= 30 && DEPTH >= 1, "one offsets lane per worker warp");
+    constexpr int E = 16 / (int)sizeof(A);
+    constexpr int WARP_ELEMS = ROWS * 32 * E;
+    constexpr int TILE = WARPS * WARP_ELEMS;
+    constexpr u32 BYTES_A = (u32)(TILE * sizeof(A));
+    constexpr u32 BYTES_B = C::n_in == 2 ? (u32)(TILE * sizeof(B)) : 0u;
+    static_assert(BYTES_A % 16 == 0 && BYTES_B % 16 == 0, "bulk copies move multiples of 16 bytes");
+    constexpr i64 AHEAD_TILES = AHEAD_BYTES > 0 ? ((i64)AHEAD_BYTES / (i64)BYTES_A > 0 ? (i64)AHEAD_BYTES / (i64)BYTES_A : 1) : 0;
+
+    extern __shared__ __align__(128) unsigned char s_dyn[];   // NBUF buffers of in0, then NBUF buffers of in1
+    // Round r of the block uses slot r % NBUF and phase (r / NBUF) & 1 of each barrier.
+    __shared__ __align__(8) u64 s_full[NBUF], s_ranked[NBUF], s_offs[NBUF], s_empty[NBUF];
+    __shared__ i64 s_tile[NBUF];                              // tile id held by the slot (num_tiles = none left)
+    __shared__ int s_cnt[NBUF][WARPS];                        // survivors per worker of that tile
+    __shared__ i64 s_off[NBUF][WARPS];                        // output offset of each worker's run; -1 = gave up
+    __shared__ int s_dead;                                    // a wait ran out somewhere in this block
+
+    const int warp_id = (int)(threadIdx.x >> 5), lane = (int)(threadIdx.x & 31);
+    volatile int* dead = &s_dead;
+    const i64 lo = (i64)head, hi = n + (i64)head;             // the array in the shifted index space
+    const A* in0a = in0 - head;
+    const B* in1a = in1 - (C::n_in == 2 ? head : 0u);
+
+    // Bounded wait for phase `parity` of one of the block's barriers: false when another warp of the block gave up or
+    // the fixed time limit passed (one try may itself suspend the thread for a while).
+    auto wait = [&](u64* bar, u32 parity, bool heed_dead) -> bool {
+        if (mbar_try_wait(bar, parity)) return true;
+        const i64 t0 = clock64();
+        for (u32 i = 0; i < (1u << 30); ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            if (heed_dead && *dead) return false;
+            if ((i & 15u) == 15u && clock64() - t0 > DCB_STREAM_WAIT_CYCLES) return false;
+        }
+        return false;
+    };
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int st = 0; st < NBUF; ++st) {
+            mbar_init(&s_full[st], 1u); mbar_init(&s_ranked[st], (u32)WARPS); mbar_init(&s_offs[st], 1u); mbar_init(&s_empty[st], (u32)WARPS);
+        }
+        s_dead = 0;
+        fence_async_smem();                                   // the barriers exist before a copy can complete on them
+    }
+    __syncthreads();
+
+    i64 issued = 0;                                           // loader thread: rounds it has started
+    if (warp_id == 1) {
+        // ---------------------------------------------------------------- loader (one thread)
+        if (lane == 0) {
+            int st = 0; u32 ph = 0;
+            for (i64 r = 0;; ++r) {
+                // DRAW_AHEAD > 0 paces the draws: the id of round r is not asked for before round r - DRAW_AHEAD has been
+                // ranked, so a block never holds ids far ahead of the tiles it is ranking (other blocks' offsets wait
+                // for the counts of all smaller ids). 0 = draw as soon as a slot is free.
+                if (DRAW_AHEAD > 0 && r >= DRAW_AHEAD) {
+                    const i64 rr = r - DRAW_AHEAD;
+                    if (!wait(&s_ranked[(int)(rr % NBUF)], (u32)((rr / NBUF) & 1), true)) { *dead = 1; break; }
+                }
+                // The id is asked for before the wait for the slot: the counter's round trip overlaps that wait.
+                i64 t = (i64)atomicAdd(counters, 1u);
+                if (t > num_tiles) t = num_tiles;
+                if (r >= NBUF && !wait(&s_empty[st], ph ^ 1u, true)) { *dead = 1; break; }
+                s_tile[st] = t;
+                const bool whole = t < num_tiles && t * TILE >= lo && (t + 1) * TILE <= hi;
+                if (whole) {
+                    mbar_expect_tx(&s_full[st], BYTES_A + BYTES_B);
+                    bulk_load(s_dyn + (size_t)st * BYTES_A, in0a + t * TILE, BYTES_A, &s_full[st]);
+                    if constexpr (C::n_in == 2)
+                        bulk_load(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B, in1a + t * TILE, BYTES_B, &s_full[st]);
+                } else {
+                    mbar_arrive(&s_full[st]);                 // ragged tile (plain loads) or no tile left: the id alone
+                }
+                issued = r + 1;
+                if (t >= num_tiles) break;
+                if constexpr (AHEAD_TILES > 0) {
+                    const i64 ta = t + AHEAD_TILES;
+                    if ((ta + 1) * TILE <= hi) {
+                        l2_prefetch_bulk(in0a + ta * TILE, BYTES_A);
+                        if constexpr (C::n_in == 2) l2_prefetch_bulk(in1a + ta * TILE, BYTES_B);
+                    }
+                }
+                if (++st == NBUF) { st = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp_id == 0) {
+        // ---------------------------------------------------------------- offsets warp
+        const i64 base_prev = prev ? prev->count : 0;
+        i64 last_tile = -1, run_incl = 0;                     // the block's previous tile, survivors up to and including it
+        bool pending = false;                                 // a tile whose count is published and whose offset is not yet
+        i64 p_tile = 0; int p_st = 0, p_excl = 0, p_total = 0;
+        int st = 0; u32 ph = 0;
+        for (;;) {
+            if (!wait(&s_ranked[st], ph, true)) { *dead = 1; break; }
+            const i64 tile = s_tile[st];
+            const bool valid = tile < num_tiles;
+            int cnt = 0, incl = 0, total = 0;
+            if (valid) {
+                cnt = lane < WARPS ? s_cnt[st][lane] : 0;
+                incl = cnt;
+#pragma unroll
+                for (int dd = 1; dd < 32; dd <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, dd);
+                    if (lane >= dd) incl += t;
+                }
+                total = __shfl_sync(0xffffffffu, incl, 31);
+                if (lane == 0 && !(tile == 0 && *(volatile unsigned int*)(abort_flag + 1) == epoch))
+                    desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)total));
+            }
+            if (pending) {
+                // Finish the tile of the round before: sum the counts of (last_tile, p_tile). Its neighbours in id order
+                // were ranked a round ago too, so their counts are normally all there: one round trip to L2 with every
+                // load in flight at once. Counts that are missing are asked for again together, not one after the other.
+                const i64 p_lo = last_tile + 1;
+                u64 d[DEPTH];
+#pragma unroll
+                for (int u = 0; u < DEPTH; ++u) {
+                    const i64 idx = p_lo + (i64)u * 32 + lane;
+                    d[u] = idx < p_tile ? desc_load(desc + idx) : 0ull;
+                }
+                bool failed = false;
+                for (u32 polls = 0;;) {
+                    bool stale = false;
+#pragma unroll
+                    for (int u = 0; u < DEPTH; ++u)
+                        stale = stale || (p_lo + (i64)u * 32 + lane < p_tile && desc_status(d[u], epoch) == ST_INVALID);
+                    if (!__any_sync(0xffffffffu, stale)) break;
+                    if (++polls > spin_limit || *dead || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
+                    __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
+#pragma unroll
+                    for (int u = 0; u < DEPTH; ++u) {
+                        const i64 idx = p_lo + (i64)u * 32 + lane;
+                        if (idx < p_tile && desc_status(d[u], epoch) == ST_INVALID) d[u] = desc_load(desc + idx);
+                    }
+                }
+                i64 sum = 0;
+#pragma unroll
+                for (int u = 0; u < DEPTH; ++u)
+                    if (p_lo + (i64)u * 32 + lane < p_tile) sum += (i64)(d[u] & DESC_VALUE_MASK);
+#pragma unroll
+                for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+                if (!failed && p_lo + 32 * DEPTH < p_tile)    // a longer range (the block's first tile, or a block that fell behind)
+                    sum += compact_range_sum(desc, p_lo + 32 * DEPTH, p_tile, lane, epoch, spin_limit, abort_flag, failed);
+                const i64 exclusive = run_incl + sum;
+                if (lane < WARPS) s_off[p_st][lane] = failed ? -1 : base_prev + exclusive + p_excl;
+                __syncwarp();
+                if (lane == 0) {
+                    if (!failed && p_tile == num_tiles - 1) {
+                        const i64 total_all = base_prev + exclusive + p_total;
+                        res->count = total_all; res->count_f = (double)total_all;
+                        res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+                        res->offset = 0; res->local_count = total_all;
+                        res->flags = total_all > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+                    }
+                    if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
+                    mbar_arrive(&s_offs[p_st]);               // the workers read s_off after this
+                }
+                if (failed) break;
+                run_incl = exclusive + p_total;
+                last_tile = p_tile;
+                pending = false;
+            }
+            if (!valid) break;                                // the round after the block's last tile
+            pending = true; p_tile = tile; p_st = st; p_excl = incl - cnt; p_total = total;
+            if (++st == NBUF) { st = 0; ph ^= 1u; }
+        }
+    } else {
+        // ---------------------------------------------------------------- workers
+        const int w = warp_id - 2;
+        i64 nvalid = (i64)1 << 62;                            // rounds in which this block has a tile
+        int st = 0, sj = 0; u32 ph = 0, pj = 0;               // slot and phase of round k, and of round k - LAG
+        for (i64 k = 0; k < nvalid + LAG; ++k) {
+            if (k < nvalid) {
+                if (!wait(&s_full[st], ph, true)) { *dead = 1; break; }
+                const i64 tile = s_tile[st];
+                if (tile >= num_tiles) {
+                    nvalid = k;
+                } else {
+                    const i64 warp_base = tile * TILE + (i64)w * WARP_ELEMS;
+                    A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A) + w * WARP_ELEMS;
+                    const B* bufB = reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + w * WARP_ELEMS;
+                    O* stage = reinterpret_cast<O*>(bufA);
+                    Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
+                    int run;
+                    if (tile * TILE >= lo && (tile + 1) * TILE <= hi) {
+#pragma unroll
+                        for (int r = 0; r < ROWS; ++r) {
+                            a[r].load_shared(bufA + (r * 32 + lane) * E);
+                            if constexpr (C::n_in == 2) b[r].load_shared(bufB + (r * 32 + lane) * E);
+                        }
+                        __syncwarp();                         // every lane holds its packs before any lane overwrites the run
+                        run = compact_rank_and_stage<C, ROWS, E, true>(a, b, hi, warp_base, lane, stage);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+                            for (int e = 0; e < E; ++e) {
+                                const i64 idx = warp_base + ((i64)r * 32 + lane) * E + e;
+                                const bool in_range = idx >= lo && idx < hi;
+                                a[r].e[e] = in_range ? in0a[idx] : A();
+                                if constexpr (C::n_in == 2) b[r].e[e] = in_range ? in1a[idx] : B();
+                            }
+                        }
+                        run = compact_rank_and_stage<C, ROWS, E, false>(a, b, hi, warp_base, lane, stage, lo);
+                    }
+                    if (lane == 0) s_cnt[st][w] = run;
+                }
+                __syncwarp();                                 // the staged run and its count are written
+                if (lane == 0) mbar_arrive(&s_ranked[st]);    // also for the round without a tile: it ends the offsets warp
+                if (++st == NBUF) { st = 0; ph ^= 1u; }
+            }
+            if (k >= LAG) {
+                if (k - LAG < nvalid) {                       // write the tile ranked LAG rounds ago, give its slot back
+                    if (!wait(&s_offs[sj], pj, true)) { *dead = 1; break; }
+                    const i64 off = s_off[sj][w];
+                    if (off < 0) { *dead = 1; break; }
+                    const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)sj * BYTES_A) + w * WARP_ELEMS);
+                    compact_copy_out<O, true>(out, out_cap, off, s_cnt[sj][w], lane, stage0);
+                    fence_async_smem();                       // this warp's accesses to the slot come before the next copy into it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s_empty[sj]);
+                }
+                if (++sj == NBUF) { sj = 0; pj ^= 1u; }
+            }
+        }
+    }
+
+    __syncthreads();
+    if (s_dead) {
+        // Tell the blocks still waiting. Copies this block started must land before its shared memory is given to another
+        // block: wait for the rounds that may still be on their way, each with the fixed limit.
+        if (threadIdx.x == 0) atomicExch(abort_flag, epoch);
+        if (threadIdx.x == 32)
+            for (i64 r = issued > NBUF ? issued - NBUF : 0; r < issued; ++r)
+                (void)wait(&s_full[(int)(r % NBUF)], (u32)((r / NBUF) & 1), false);
+    }
+    // Sign off. The last block to do so resets the counters for the next launch and has the final say on the record.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int finished = atomicAdd(counters + 1, 1u);
+        if (finished == gridDim.x - 1) {
+            __threadfence();
+            if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->local_count = 0; res->flags = (u64)FLAG_TIMEOUT; }
             counters[0] = 0; counters[1] = 0;
         }
     }

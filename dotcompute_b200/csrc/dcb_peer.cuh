@@ -76,8 +76,10 @@ __device__ __forceinline__ void peer_exchange_body(const PeerTable& pt, DeviceRe
         } else {
             PeerSlot g = slots[0];
             const bool fp = (g.flags & SLOT_IS_FP) != 0, u64cmp = (g.flags & SLOT_IS_U64) != 0;
+            i64 below = pt.rank > 0 ? slots[0].count : 0;   // elements counted on lower ranks: this rank's output offset
             for (int r = 1; r < pt.world; ++r) {       // rank order: the same arithmetic on every GPU
                 const PeerSlot& o = slots[r];
+                if (r < pt.rank) below += o.count;
                 g.fsum += o.fsum;
                 const u64 lo = g.isum_lo + o.isum_lo;
                 g.isum_hi += o.isum_hi + (lo < o.isum_lo ? 1 : 0);
@@ -100,6 +102,7 @@ __device__ __forceinline__ void peer_exchange_body(const PeerTable& pt, DeviceRe
             if (fp) { rec->fmin = __longlong_as_double(g.mn_bits); rec->fmax = __longlong_as_double(g.mx_bits); rec->imin = 0; rec->imax = 0; }
             else { rec->fmin = 0; rec->fmax = 0; rec->imin = g.mn_bits; rec->imax = g.mx_bits; }
             rec->flags = g.flags & 0xffffffffull;
+            rec->offset = below; rec->local_count = slots[pt.rank].count;
         }
         pt.state->seq = seq;
     }

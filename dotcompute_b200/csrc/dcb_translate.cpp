@@ -1004,6 +1004,19 @@ int pipe_block_threads(int ctrl) { return kPipeBlock + (ctrl ? 32 : 0); }
 long long pipe_tile_elems(const ChainInfo& info, int rows) { return (long long)(kPipeBlock / 32) * rows * 32 * (16 / type_size(info.in0)); }
 long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf) { return (long long)nbuf * pipe_tile_elems(info, rows) * pipe_bytes_per_elem(info); }
 
+int stream_rows_for(const ChainInfo& info, int warps) {
+    if (info.terminal != OP_TOARRAY || !info.has_filter) return 0;
+    if (type_size(info.out_type) > type_size(info.in0)) return 0;
+    const int e = 16 / type_size(info.in0);
+    const int rows = 16384 / (warps * 32 * e * pipe_bytes_per_elem(info));
+    return rows < 1 ? 1 : (rows > 8 ? 8 : rows);
+}
+long long stream_tile_elems(const ChainInfo& info, int rows, int warps) { return (long long)warps * rows * 32 * (16 / type_size(info.in0)); }
+long long stream_smem_bytes(const ChainInfo& info, int rows, int warps, int nbuf) {
+    return (long long)nbuf * stream_tile_elems(info, rows, warps) * pipe_bytes_per_elem(info);
+}
+int stream_block_threads(int warps) { return (warps + 2) * 32; }
+
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
                           const Tuning& tuning, bool with_prelude) {
     const int block = tuning.block, unroll = tuning.unroll;
@@ -1057,6 +1070,19 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                           : "    dcb::compact_pipe_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) + ", " +
                                 std::to_string(tuning.pipe_nbuf) + ", " + std::to_string(tuning.pipe_ctrl ? 1 : 0) + ">(") + cast_in() + ", n, (" + C +
                      "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters);\n}\n";
+            }
+            if (v == 0 && tuning.stream && stream_rows_for(info, tuning.stream_warps) > 0) {
+                const int srow = tuning.stream_rows > 0 ? tuning.stream_rows : stream_rows_for(info, tuning.stream_warps);
+                const std::string ST = std::to_string(stream_block_threads(tuning.stream_warps));
+                const std::string sbounds = tuning.stream_min_blocks > 0 ? ST + ", " + std::to_string(tuning.stream_min_blocks) : ST;
+                s += "extern \"C\" __global__ void __launch_bounds__(" + sbounds + ") dcb_compact_stream" + suffix +
+                     "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
+                     "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag, "
+                     "unsigned int* counters, unsigned int head) {\n"
+                     "    dcb::compact_stream_body<" + C + ", " + std::to_string(tuning.stream_warps) + ", " + std::to_string(srow) + ", " +
+                     std::to_string(tuning.stream_lag) + ", " + std::to_string(tuning.stream_nbuf) + ", " + std::to_string(tuning.stream_depth) + ", " +
+                     std::to_string(tuning.stream_ahead_mb) + " << 20, " + std::to_string(tuning.stream_draw_ahead) + ">(" + cast_in() + ", n, (" + C +
+                     "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters, head);\n}\n";
             }
         } else {
             // Keep the register count where 6 (one input) or 4 (Zip) blocks share an SM: measured as fast as 8 blocks, and

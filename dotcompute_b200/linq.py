@@ -50,6 +50,18 @@ class CompiledPipeline:
     def handle(self):
         return self._h
 
+    def Dispose(self) -> None:
+        """Give the reference back (the native cache keeps the compiled kernels until it needs the room)."""
+        h, self._h = self._h, None
+        if h is not None and h.value and not getattr(self.acc, "_disposed", True):
+            N.lib().dcb_pipeline_destroy(h)
+
+    def __del__(self):
+        try:
+            self.Dispose()
+        except Exception:       # interpreter shutdown: the library may already be gone
+            pass
+
     @property
     def Source(self) -> str:
         need = C.c_size_t()

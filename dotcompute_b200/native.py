@@ -25,7 +25,8 @@ PIPE_FORCE_JIT = 1
 RES_SAW_NAN, RES_TRUNCATED, RES_TIMEOUT, RES_OVERFLOW = 1, 2, 4, 8
 DEVICE_RESULT_BYTES = 128
 SLOT_FSUM, SLOT_COUNT_F, SLOT_ISUM_LO, SLOT_ISUM_HI, SLOT_COUNT = 0, 1, 2, 3, 4
-SLOT_FMIN, SLOT_FMAX, SLOT_IMIN, SLOT_IMAX, SLOT_FLAGS, SLOT_NSLOTS = 5, 6, 7, 8, 9, 16
+SLOT_FMIN, SLOT_FMAX, SLOT_IMIN, SLOT_IMAX, SLOT_FLAGS, SLOT_OFFSET, SLOT_LOCAL_COUNT, SLOT_NSLOTS = 5, 6, 7, 8, 9, 10, 11, 16
+OPT_COMPACT_KERNEL, OPT_FORCE_SCALAR, OPT_BLOCKS_PER_SM, OPT_WITHHOLD_FIRST_COUNT, OPT_CACHE_MAX_ENTRIES, OPT_CACHE_ENTRIES = 1, 2, 3, 4, 5, 6
 
 
 class Op(C.Structure):
@@ -65,6 +66,8 @@ PROTOTYPES = {
     "dcb_set_stream": (_i32, [_vp, _vp]),
     "dcb_stream_sync": (_i32, [_vp, _vp]),
     "dcb_set_spin_limit": (_i32, [_vp, _u32]),
+    "dcb_set_option": (_i32, [_vp, _i32, _i64]),
+    "dcb_get_option": (_i32, [_vp, _i32, C.POINTER(_i64)]),
     "dcb_alloc": (_i32, [_vp, _sz, _pp]),
     "dcb_free": (_i32, [_vp, _vp]),
     "dcb_buf_wrap": (_i32, [_vp, _vp, _sz, _pp]),

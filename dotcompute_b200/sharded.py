@@ -295,19 +295,41 @@ class ShardedQuery:
                                                C.c_void_p(stream_ptr)), self.acc.handle)
         return rec
 
+    def enqueue_compact(self, out: UnifiedBuffer, stream, rec=None):
+        """Compaction of this rank's shard into `out` on `stream` (a torch stream), then the exchange of the survivor counts.
+        Fused route: the one-warp peer-store kernel on the same stream leaves, in the record, the global total
+        (SLOT_COUNT), this rank's own count (SLOT_LOCAL_COUNT) and the number of survivors on lower ranks (SLOT_OFFSET),
+        with no collective and no host round trip. Returns the record tensor; it is complete when `stream` gets there."""
+        pipe = self.pipeline(N.OP_TOARRAY)
+        if rec is None:
+            rec = self.record_tensor()
+        n = self.local.Length if self.second is None else min(self.local.Length, self.second.Length)
+        in1 = C.c_void_p(self.second.GetDeviceMemory()) if self.second is not None else None
+        sh = C.c_void_p(_stream_handle(stream))
+        N.check(N.lib().dcb_pipeline_run_async(pipe.handle, C.c_void_p(self.local.GetDeviceMemory()), in1, n,
+                                               C.c_void_p(out.GetDeviceMemory()), out.Length, C.c_void_p(rec.data_ptr()), None, sh),
+                self.acc.handle)
+        if self.fused:
+            N.check(N.lib().dcb_peer_exchange_async(self.acc.handle, C.c_void_p(rec.data_ptr()), pipe.info.out_type, sh), self.acc.handle)
+        return rec
+
     def ToArray(self):
         """Compacts the local shard. Returns (local survivors as a host array, this rank's offset in the global
         result, global survivor count). Concatenating the local arrays in rank order gives the single-GPU result."""
         import torch
         pipe = self.pipeline(N.OP_TOARRAY)
-        n = self.local.Length
+        n = self.local.Length if self.second is None else min(self.local.Length, self.second.Length)
         out = self.acc.Memory.AllocateAsync(max(n, 1), pipe.out_dtype)
         try:
             stream = torch.cuda.current_stream()
             if pipe.has_filter:
-                rec = self.compact_local(out, _stream_handle(stream))
+                rec = self.enqueue_compact(out, stream)
                 host = rec.cpu().numpy()
                 finalize_record(host, N.OP_TOARRAY, pipe.info.out_type)
+                if self.fused:
+                    local_count, offset, total = int(host[N.SLOT_LOCAL_COUNT]), int(host[N.SLOT_OFFSET]), int(host[N.SLOT_COUNT])
+                    arr = out.CopyToAsync(count=local_count) if local_count else np.empty(0, pipe.out_dtype)
+                    return arr, offset, total
                 local_count = int(host[N.SLOT_COUNT])
             else:
                 in1 = C.c_void_p(self.second.GetDeviceMemory()) if self.second is not None else None

@@ -163,6 +163,9 @@ enum {
     DCB_SLOT_IMIN = 7,   /* int64 (raw bits of the element for U64)                 */
     DCB_SLOT_IMAX = 8,   /* int64                                                   */
     DCB_SLOT_FLAGS = 9,  /* uint64: DCB_RES_* bits plus NaN bookkeeping             */
+    DCB_SLOT_OFFSET = 10,/* int64: after dcb_peer_exchange_async, the sum of the counts of all lower ranks, i.e. where this
+                            GPU's compacted output starts in the global, rank-ordered result; 0 without an exchange */
+    DCB_SLOT_LOCAL_COUNT = 11, /* int64: this GPU's own count (after an exchange DCB_SLOT_COUNT holds the global total) */
     DCB_SLOT_NSLOTS = 16
 };
 #define DCB_DEVICE_RESULT_BYTES 128
@@ -193,6 +196,24 @@ dcb_status dcb_stream_sync(dcb_ctx* ctx, void* stream);
 /* Upper bound on polls of one device-side wait (a look-back wait inside the compaction kernel, a wait for a peer's
  * partial in the exchange kernel) before it gives up and reports DCB_ERR_TIMEOUT (defaults 1<<22 and 1<<20). */
 dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls);
+
+/* Per-context switches. Their initial values are read from the environment once, at dcb_init (DCB200_COMPACT_KERNEL,
+ * DCB200_FORCE_SCALAR, DCB200_BLOCKS_PER_SM, DCB200_CACHE_MAX_ENTRIES); nothing reads the environment at launch time.
+ * They stand where the reference has CompilationOptions / KernelCache settings
+ * (src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:132, new KernelCache(maxEntries: 100)). */
+enum {
+    DCB_OPT_COMPACT_KERNEL = 1,       /* 0 = automatic (the streamed kernel where the query allows), 1 = always the
+                                         one-tile-per-block look-back kernel, 2 = the round-based pipelined kernel */
+    DCB_OPT_FORCE_SCALAR = 2,         /* 1 = scalar kernel variants even for 16-byte aligned buffers                   */
+    DCB_OPT_BLOCKS_PER_SM = 3,        /* cap on resident blocks per SM used to size persistent grids; 0 = what fits    */
+    DCB_OPT_WITHHOLD_FIRST_COUNT = 4, /* test switch for the time-out path, driven from the host: the next compactions keep
+                                         the survivor count of their first tile to themselves, so every bounded look-back
+                                         wait for it runs out and the run ends with DCB_ERR_TIMEOUT (no fault, no trap)   */
+    DCB_OPT_CACHE_MAX_ENTRIES = 5,    /* compiled pipelines kept per context (default 100, least recently used first out) */
+    DCB_OPT_CACHE_ENTRIES = 6         /* read-only: compiled pipelines in the cache now                                 */
+};
+dcb_status dcb_set_option(dcb_ctx* ctx, int32_t option, int64_t value);
+dcb_status dcb_get_option(dcb_ctx* ctx, int32_t option, int64_t* out_value);
 
 /* ------------------------------------------------------------------------- memory */
 
@@ -258,6 +279,8 @@ dcb_status dcb_translate_kernel_method(const char* csharp_method, char* cuda_out
  * context under a key that contains the full lambda text (the reference's key leaves it out,
  * src/Extensions/DotCompute.Linq/CodeGeneration/KernelCache.cs:297-351). */
 dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc* desc, dcb_pipeline** out_pipeline);
+/* Gives back one reference obtained from dcb_pipeline_compile. The pipeline stays cached; once nobody holds it, it is a
+ * candidate for eviction when the cache is full (DCB_OPT_CACHE_MAX_ENTRIES; KernelCache.cs:297-351 has the same bound). */
 dcb_status dcb_pipeline_destroy(dcb_pipeline* p);
 dcb_status dcb_pipeline_info_get(const dcb_pipeline* p, dcb_pipeline_info* out_info);
 /* The generated CUDA source (the text NVRTC saw, or would see for a precompiled pipeline). */

@@ -5,7 +5,7 @@ variable the library reads at every launch.
 import numpy as np
 import pytest
 
-from dotcompute_b200 import AsComputeQueryable
+from dotcompute_b200 import AsComputeQueryable, native as N
 from oracle.linq_oracle import Enumerable
 
 pytestmark = pytest.mark.gpu
@@ -16,10 +16,11 @@ def rng(seed):
 
 
 @pytest.fixture
-def pipe(monkeypatch):
+def pipe(acc):
     def switch(on: bool):
-        monkeypatch.setenv("DCB200_COMPACT_PIPE", "1" if on else "0")
-    return switch
+        acc.SetOption(N.OPT_COMPACT_KERNEL, 0 if on else 1)      # 0 = the streamed kernel, 1 = one tile per block
+    yield switch
+    acc.SetOption(N.OPT_COMPACT_KERNEL, 0)
 
 
 def both(pipe, make_query):
