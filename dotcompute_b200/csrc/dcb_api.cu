@@ -48,7 +48,8 @@ struct Scratch {
     unsigned int* words = nullptr;      // 512 bytes: [0] reduce ticket, [32] [33] tile-id and finished-block counters of the
                                         // persistent compaction kernels, [64] compaction abort flag, [65] "withhold the first
                                         // count" word of the time-out test (separate 128-byte lines)
-    unsigned long long* desc = nullptr; // look-back descriptors
+    unsigned long long* desc = nullptr; // look-back descriptors of the one-tile-per-block kernel (64-bit), followed by
+    unsigned int* cdesc = nullptr;      // the 32-bit count descriptors of the streamed kernel (same allocation)
     size_t desc_cap = 0;
     unsigned int epoch = 0;
 };
@@ -109,8 +110,6 @@ struct dcb_pipeline {
     cudaLibrary_t lib = nullptr;
     const void* k_vec = nullptr;
     const void* k_scalar = nullptr;
-    const void* k_pipe = nullptr;        // pipelined compaction kernel (null: the query has none)
-    int pipe_rows = 0, pipe_nbuf = 0, pipe_ctrl = 0, occ_pipe = 1;   // its rows per warp, buffers per input, extra warp, resident blocks per SM
     bool precompiled = false;
     int unroll = 4;
     int occ_vec = 1, occ_scalar = 1;     // resident blocks per SM
@@ -217,8 +216,11 @@ dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s, Sc
         size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
         cap = std::max(cap, sc.desc_cap * 2);
         if (sc.desc) { CU(ctx, cudaStreamSynchronize(s)); CU(ctx, cudaFree(sc.desc)); sc.desc = nullptr; sc.desc_cap = 0; }
-        CU(ctx, cudaMalloc(&sc.desc, (cap + 2) * sizeof(unsigned long long)));
-        CU(ctx, cudaMemsetAsync(sc.desc, 0, (cap + 2) * sizeof(unsigned long long), s));
+        cap = (cap + 3) & ~(size_t)3;
+        const size_t bytes = cap * sizeof(unsigned long long) + (cap + 8) * sizeof(unsigned int);   // the streamed kernel reads 16 bytes at a time
+        CU(ctx, cudaMalloc(&sc.desc, bytes));
+        CU(ctx, cudaMemsetAsync(sc.desc, 0, bytes, s));
+        sc.cdesc = reinterpret_cast<unsigned int*>(sc.desc + cap);
         sc.desc_cap = cap;
         sc.epoch = 0;
     }
@@ -233,13 +235,6 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     tuning.compact_rows = env_int("DCB200_COMPACT_ROWS", 0);
     tuning.compact_min_blocks = env_int("DCB200_COMPACT_MINBLOCKS", tuning.compact_min_blocks);
     p->compact_block = tuning.compact_block;
-    tuning.pipe_rows = env_int("DCB200_PIPE_ROWS", 0);
-    tuning.pipe_min_blocks = env_int("DCB200_PIPE_MINBLOCKS", tuning.pipe_min_blocks);
-    tuning.pipe_lag = env_int("DCB200_PIPE_LAG", tuning.pipe_lag);
-    tuning.pipe_nbuf = env_int("DCB200_PIPE_NBUF", tuning.pipe_nbuf);
-    p->pipe_nbuf = tuning.pipe_nbuf;
-    tuning.pipe_ctrl = env_int("DCB200_PIPE_CTRL", tuning.pipe_ctrl);
-    p->pipe_ctrl = tuning.pipe_ctrl;
     tuning.stream = env_int("DCB200_STREAM", tuning.stream);
     tuning.stream_warps = env_int("DCB200_STREAM_WARPS", tuning.stream_warps);
     tuning.stream_rows = env_int("DCB200_STREAM_ROWS", 0);
@@ -253,7 +248,6 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     p->stream_nbuf = tuning.stream_nbuf;
     p->stream_rows = (tuning.stream && dcbt::stream_rows_for(p->info, tuning.stream_warps) > 0)
                          ? (tuning.stream_rows > 0 ? tuning.stream_rows : dcbt::stream_rows_for(p->info, tuning.stream_warps)) : 0;
-    p->pipe_rows = dcbt::pipe_rows_for(p->info) > 0 ? (tuning.pipe_rows > 0 ? tuning.pipe_rows : dcbt::pipe_rows_for(p->info)) : 0;
     p->unroll = tuning.unroll;
     p->jit_rows = tuning.compact_rows;
     p->source = dcbt::build_program(p->info, "", kKernelsHeaderText, tuning, true);
@@ -294,11 +288,6 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     CU(ctx, cudaLibraryGetKernel(&ks, p->lib, (std::string(stem) + "scalar").c_str()));
     p->k_vec = (const void*)kv;
     p->k_scalar = (const void*)ks;
-    if (p->pipe_rows > 0) {
-        cudaKernel_t kp = nullptr;
-        CU(ctx, cudaLibraryGetKernel(&kp, p->lib, "dcb_compact_pipe"));
-        p->k_pipe = (const void*)kp;
-    }
     if (p->stream_rows > 0) {
         cudaKernel_t kst = nullptr;
         CU(ctx, cudaLibraryGetKernel(&kst, p->lib, "dcb_compact_stream"));
@@ -317,13 +306,7 @@ dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
     else { (void)cudaGetLastError(); p->occ_vec = 4; }
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_scalar, blk, 0) == cudaSuccess && occ > 0) p->occ_scalar = occ;
     else { (void)cudaGetLastError(); p->occ_scalar = 4; }
-    if (p->k_pipe) {
-        // More than 48 KB of dynamic shared memory has to be asked for once per kernel.
-        const int dyn = (int)dcbt::pipe_smem_bytes(p->info, p->pipe_rows, p->pipe_nbuf);
-        if (cudaFuncSetAttribute(p->k_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_pipe, dcbt::pipe_block_threads(p->pipe_ctrl), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_pipe = occ;
-        else { (void)cudaGetLastError(); p->k_pipe = nullptr; }   // this device cannot run it: the one-tile-per-block kernel stays
-    }
+    // More than 48 KB of dynamic shared memory has to be asked for once per kernel.
     if (p->k_stream) {
         const int dyn = (int)dcbt::stream_smem_bytes(p->info, p->stream_rows, p->stream_warps, p->stream_nbuf);
         if (cudaFuncSetAttribute(p->k_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
@@ -537,7 +520,7 @@ extern "C" dcb_status dcb_set_option(dcb_ctx* ctx, int32_t option, int64_t value
     std::lock_guard<std::mutex> g(ctx->mu);
     switch (option) {
         case DCB_OPT_COMPACT_KERNEL:
-            NEED(ctx, value >= 0 && value <= 2, "DCB_OPT_COMPACT_KERNEL takes 0 (automatic), 1 (one tile per block) or 2 (round-based)");
+            NEED(ctx, value >= 0 && value <= 1, "DCB_OPT_COMPACT_KERNEL takes 0 (automatic) or 1 (one tile per block)");
             ctx->opt_compact_kernel = (int)value; return DCB_OK;
         case DCB_OPT_FORCE_SCALAR: ctx->opt_force_scalar = value != 0; return DCB_OK;
         case DCB_OPT_BLOCKS_PER_SM:
@@ -837,10 +820,6 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->k_scalar = b->k_scalar;
         p->unroll = b->unroll;
         p->compact_block = b->compact_block;
-        p->k_pipe = b->k_pipe;
-        p->pipe_rows = b->pipe_rows;
-        p->pipe_nbuf = b->pipe_nbuf;
-        p->pipe_ctrl = b->pipe_ctrl;
         p->k_stream = b->k_stream;
         p->stream_rows = b->stream_rows;
         p->stream_warps = b->stream_warps;
@@ -946,17 +925,15 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
     }
     if (to_array) {
         // Which kernel. The streamed kernel takes any element-aligned pointers as long as both inputs sit at the same
-        // element offset from a 16-byte boundary (its bulk copies start at that boundary); the round-based pipelined kernel
-        // needs every pointer 16-byte aligned; the one-tile-per-block kernel takes anything (scalar variant if unaligned).
+        // element offset from a 16-byte boundary (its bulk copies start at that boundary); the one-tile-per-block kernel
+        // takes anything (scalar variant if unaligned).
         const size_t sz0 = (size_t)dcbt::type_size(I.in0), sz1 = I.n_in == 2 ? (size_t)dcbt::type_size(I.in1) : 1;
         unsigned int head = (unsigned int)(((uintptr_t)in0 % 16) / sz0);
         const bool stream_ok = p->k_stream && ctx->opt_compact_kernel == 0 && !ctx->opt_force_scalar && (uintptr_t)in0 % sz0 == 0 &&
                                (I.n_in == 1 || ((uintptr_t)in1 - (uintptr_t)head * sz1) % 16 == 0);
-        const bool pipe = !stream_ok && vec && p->k_pipe && ctx->opt_compact_kernel != 1 && (I.n_in == 1 || aligned_to(in1, 16));
         const int rows = vec ? p->rows_vec : p->rows_scalar;
         if (!stream_ok) head = 0;
         const int64_t tile = stream_ok ? (int64_t)dcbt::stream_tile_elems(I, p->stream_rows, p->stream_warps)
-                           : pipe      ? (int64_t)dcbt::pipe_tile_elems(I, p->pipe_rows)
                                        : (int64_t)(p->compact_block / 32) * rows * 32 * E;
         long long num_tiles = (n + (int64_t)head + tile - 1) / tile;
         if (n == 0) num_tiles = 0;
@@ -972,8 +949,8 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         if (st) return st;
         Scratch& sc = *scp;
         sc.epoch += 1;
-        if (sc.epoch >= 0x3fffu) {   // epoch field is 14 bits: wipe the descriptors before reusing a value
-            CU(ctx, cudaMemsetAsync(sc.desc, 0, sc.desc_cap * sizeof(unsigned long long), s));
+        if (sc.epoch >= 0xfffu) {    // the narrower epoch field is 12 bits: wipe the descriptors before reusing a value
+            CU(ctx, cudaMemsetAsync(sc.desc, 0, sc.desc_cap * sizeof(unsigned long long) + (sc.desc_cap + 8) * sizeof(unsigned int), s));
             CU(ctx, cudaMemsetAsync(sc.words, 0, 512, s));
             sc.epoch = 1;
         }
@@ -989,19 +966,14 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc,
                         (void*)&epoch, (void*)&spin, (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag};
         if (launches) *launches += 1;
-        if (stream_ok || pipe) {
+        if (stream_ok) {
             // Persistent blocks, as many as fit the GPU at once (fewer for a small input); tile ids come from counters[0].
             unsigned int* counters = sc.words + 32;
-            void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.desc, (void*)&epoch, (void*)&spin,
+            void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.cdesc, (void*)&epoch, (void*)&spin,
                              (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters, (void*)&head};
-            if (stream_ok) {
-                const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_stream));
-                CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps)), pargs,
-                                         (size_t)dcbt::stream_smem_bytes(I, p->stream_rows, p->stream_warps, p->stream_nbuf), s));
-            } else {
-                const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_pipe));
-                CU(ctx, cudaLaunchKernel(p->k_pipe, dim3(grid), dim3(dcbt::pipe_block_threads(p->pipe_ctrl)), pargs, (size_t)dcbt::pipe_smem_bytes(I, p->pipe_rows, p->pipe_nbuf), s));
-            }
+            const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_stream));
+            CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps)), pargs,
+                                     (size_t)dcbt::stream_smem_bytes(I, p->stream_rows, p->stream_warps, p->stream_nbuf), s));
             ctx->launches += 1;
             return DCB_OK;
         }

@@ -9,10 +9,6 @@ struct dcb_builtin_entry {
     const void* k_scalar;   // kernel for any alignment
     int unroll;             // packs per thread per tile the kernels were built with
     int compact_block;      // threads per block of the compaction kernels
-    const void* k_pipe;     // pipelined compaction kernel, or null when the query has none
-    int pipe_rows;          // rows per warp it was built with
-    int pipe_nbuf;          // shared-memory buffers per input it was built with
-    int pipe_ctrl;          // 1 = built with the extra offsets warp
     const void* k_stream;   // streamed compaction kernel, or null when the query has none
     int stream_rows;        // rows per worker warp it was built with
     int stream_warps;       // worker warps per block

@@ -8,7 +8,7 @@
 //   map_body      Select/Zip only, ToArray       : out[i] = f(in[i])
 //   reduce_body   any chain, Sum/Min/Max/Avg/Count: one read of the input, nothing written but a record
 //   compact_body  chain with a Where, ToArray     : stable stream compaction, single pass
-//   compact_pipe_body  the same, persistent blocks whose input arrives by asynchronous bulk copies
+//   compact_stream_body  the same, warp-specialised persistent blocks whose input arrives by asynchronous bulk copies
 //
 // All three are HBM-bound streaming kernels: 128-bit loads with a streaming cache hint, several
 // independent loads in flight per thread, no tensor cores. This file is compiled both by nvcc
@@ -36,6 +36,15 @@ template <typename T> struct is_unsigned_t {
     static constexpr bool value = same_t<T, unsigned char>::value || same_t<T, unsigned short>::value ||
                                   same_t<T, unsigned int>::value || same_t<T, u64>::value || same_t<T, bool>::value;
 };
+
+// The bits of a value in an unsigned integer of the same size (what memcpy would give).
+template <typename U, typename T>
+__device__ __forceinline__ void memcpy_bits(U& dst, const T& src) {
+    static_assert(sizeof(U) == sizeof(T), "same size");
+    union { T t; U u; } c;
+    c.t = src;
+    dst = c.u;
+}
 
 // Reduction selector bits.
 enum : int { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8 };
@@ -572,42 +581,6 @@ __device__ __forceinline__ int compact_rank_and_stage(const Pack<typename C::in0
     return warp_run;
 }
 
-// Chain, ranks and staging of one warp's run that lies in shared memory, element-wise: the run is taken as rows of 32
-// consecutive elements, lane l handling element 32*r + l of row r, so a row's survivors are ranked with one ballot and
-// land in consecutive words of `stage` (no shuffle scan, no bank conflicts). `stage` may be the start of the run itself
-// when sizeof(out) <= sizeof(in0): a row is written only after it, and every row before it, has been read. Returns the
-// number of survivors staged, in source order.
-template <class C, int NROWS>
-__device__ __forceinline__ int compact_rank_rows_and_stage(const typename C::in0_t* run0, const typename C::in1_t* run1, int lane,
-                                                           typename C::out_t* stage) {
-    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
-    // rows held in registers at a time: the largest of 16, 8, 4, 2, 1 that divides the run (the whole run if it is short)
-    constexpr int CHUNK = NROWS <= 16 ? NROWS : (NROWS % 16 == 0 ? 16 : (NROWS % 8 == 0 ? 8 : (NROWS % 4 == 0 ? 4 : (NROWS % 2 == 0 ? 2 : 1))));
-    static_assert(NROWS % CHUNK == 0, "whole chunks");
-    const u32 below = (1u << lane) - 1u;
-    int base = 0;
-#pragma unroll 1
-    for (int c = 0; c < NROWS; c += CHUNK) {
-        A a[CHUNK]; B b[CHUNK];
-#pragma unroll
-        for (int r = 0; r < CHUNK; ++r) {
-            a[r] = run0[(c + r) * 32 + lane];
-            if constexpr (C::n_in == 2) b[r] = run1[(c + r) * 32 + lane];
-        }
-        __syncwarp();                                         // every lane holds its elements before any lane overwrites the rows
-#pragma unroll
-        for (int r = 0; r < CHUNK; ++r) {
-            O v; bool keep;
-            if constexpr (C::n_in == 2) keep = C::apply(a[r], b[r], v); else keep = C::apply(a[r], B(), v);
-            const u32 m = __ballot_sync(0xffffffffu, keep);
-            if (keep) stage[base + __popc(m & below)] = v;
-            base += __popc(m);
-        }
-        __syncwarp();
-    }
-    return base;
-}
-
 // Loads of one warp's run from global memory, then compact_rank_and_stage.
 template <class C, int BLOCK, int ROWS, bool VEC, bool FULL>
 __device__ __forceinline__ int compact_count_and_stage(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
@@ -837,7 +810,7 @@ __device__ __forceinline__ void compact_body(const typename C::in0_t* __restrict
 }
 
 
-// ------------------------------------------------------------------ compact, pipelined: persistent blocks fed by bulk copies
+// ------------------------------------------------------------------ bulk copies, shared-memory barriers, descriptor range sums
 // Asynchronous bulk copies (the TMA unit, untiled form) and the shared-memory barriers they complete on.
 __device__ __forceinline__ u32 smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(u64* bar, u32 arrivals) {
@@ -854,23 +827,6 @@ __device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
-}
-__device__ __forceinline__ u64 global_timer_ns() {
-    u64 t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait for phase `parity` of `bar`: false when the phase has not completed after `limit` tries or, since one
-// try may itself suspend the thread for a while, after `limit` microseconds (two seconds at most), whichever is first.
-__device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const u64 max_ns = (u64)limit * 1000ull < 2000000000ull ? (u64)limit * 1000ull : 2000000000ull;
-    const u64 t0 = global_timer_ns();
-    for (u32 tries = 0; tries < limit; ++tries) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > max_ns) break;
-    }
-    return false;
 }
 // Global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completing on `bar`.
 __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_global, u32 bytes, u64* bar) {
@@ -918,413 +874,6 @@ __device__ __forceinline__ i64 compact_range_sum(const u64* __restrict__ desc, i
     return sum;
 }
 
-// Same result as compact_body, other schedule: a software pipeline over the tiles of a persistent block.
-//
-// About one block per SM slot stays resident and works through tiles whose ids it draws from a counter. In round k the
-// block (1) ranks tile k, whose input a bulk copy brought into shared memory while earlier rounds ran, and stages the
-// survivors in place, over the input it has just read (hence sizeof(out) <= sizeof(in0)); after the round's one block
-// barrier (2) one thread draws the id of tile k+PRE and starts its copies into the buffer tile k-LAG-1 left, (3) warp 0
-// publishes the count of tile k and works out the output offset of tile k-LAG+1, whose predecessors published their
-// counts a round or more ago, so it rarely has to wait, and (4) all warps write tile k-LAG, whose offset was worked out
-// a round earlier. The HBM reads never pause for a look-back. NBUF = LAG + 1 + PRE buffers per input.
-//
-// Offsets: the block knows the offset after its own previous tile; the offset of its next tile adds the counts of the
-// tiles drawn in between (compact_range_sum). Descriptors therefore carry counts only.
-//
-// Progress: a tile's offset waits only for counts of tiles with smaller ids; ids are drawn in increasing order by blocks
-// that are already running, and ranking a tile never waits for another block, so the smallest id whose count is missing
-// always belongs to a block that is about to rank it. No assumption about how many blocks are resident. All waits are
-// bounded all the same. LAG > PRE is required: a block starts with PRE + 1 neighbouring ids and ranks them over its
-// first PRE + 1 rounds; the offset of the next block's first tile needs all of them, and with LAG > PRE it is asked for
-// only after that many rounds (asked for earlier, every block would wait for the block before it, one after another).
-//
-// `counters[0]` hands out tile ids, `counters[1]` counts finished blocks; both must be zero at launch and the last block
-// to finish zeroes them again. That block also turns the record into FLAG_TIMEOUT if any block gave up.
-// Launch with BLOCK + 32 * CTRL threads and NBUF * TILE * (sizeof(in0) [+ sizeof(in1)]) bytes of dynamic shared memory.
-template <class C, int BLOCK, int ROWS, int LAG, int NBUF, int CTRL>
-__device__ __forceinline__ void compact_pipe_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
-                                                  i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
-                                                  u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
-                                                  const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
-                                                  unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters) {
-    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
-    static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
-    constexpr int PRE = NBUF - LAG - 1;
-    static_assert(PRE >= 1 && LAG > PRE && NBUF <= 16, "NBUF = LAG + 1 + PRE with LAG > PRE >= 1");
-    constexpr int E = 16 / (int)sizeof(A);
-    constexpr int WARPS = BLOCK / 32;
-    constexpr int WARP_ELEMS = ROWS * 32 * E;
-    constexpr int TILE = WARPS * WARP_ELEMS;
-    constexpr u32 BYTES_A = (u32)(TILE * sizeof(A));
-    constexpr u32 BYTES_B = C::n_in == 2 ? (u32)(TILE * sizeof(B)) : 0u;
-    static_assert(BYTES_A % 16 == 0 && BYTES_B % 16 == 0, "bulk copies move multiples of 16 bytes");
-
-    extern __shared__ __align__(128) unsigned char s_dyn[];   // NBUF buffers of in0, then NBUF buffers of in1
-    __shared__ __align__(8) u64 s_bar[NBUF];                  // round r completes phase (r / NBUF) & 1 of s_bar[r % NBUF]
-    __shared__ i64 s_tile[NBUF];                              // tile id of the round held in each buffer (num_tiles = none)
-    __shared__ int s_tot[NBUF][WARPS];                        // survivors per warp of that tile
-    __shared__ i64 s_prefix[2];                               // output offset of the tile of round j at [j & 1]; -1 = gave up
-    __shared__ int s_dead;                                    // a copy did not arrive within the limit
-
-    // CTRL = 1 adds a warp in front that only publishes counts and works out offsets (BLOCK + 32 threads in all); with
-    // CTRL = 0 the first ranking warp does that on top of its share of the tile. `warp` counts ranking warps; -1 = the extra warp.
-    const int warp = (int)(threadIdx.x >> 5) - CTRL, lane = threadIdx.x & 31;
-    const bool offsets_warp = CTRL ? warp < 0 : warp == 0;
-    const bool ranks = warp >= 0;
-    constexpr int FETCHER = (CTRL + (WARPS > 1 ? 1 : 0)) * 32;   // lane 0 of the second ranking warp: it does not work on offsets
-    bool exhausted = false;                                   // used by the fetching thread only
-
-    // Draws the id of the tile this block handles in round r and starts the copies of its input. The round's barrier
-    // completes in every case, and s_tile is written before the arrival: whoever has waited for the barrier may read the
-    // id. A whole tile completes it with its bytes; the ragged last tile (read with plain loads) and "no tile left"
-    // complete it at once.
-    auto fetch = [&](i64 r) {
-        i64 t = num_tiles;
-        if (!exhausted) {
-            t = (i64)atomicAdd(counters, 1u);
-            if (t >= num_tiles) { t = num_tiles; exhausted = true; }
-        }
-        const int st = (int)(r % NBUF);
-        s_tile[st] = t;
-        if (t < num_tiles && (t + 1) * TILE <= n) {
-            mbar_expect_tx(&s_bar[st], BYTES_A + BYTES_B);
-            bulk_load(s_dyn + (size_t)st * BYTES_A, in0 + t * TILE, BYTES_A, &s_bar[st]);
-            if constexpr (C::n_in == 2)
-                bulk_load(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B, in1 + t * TILE, BYTES_B, &s_bar[st]);
-        } else {
-            mbar_arrive(&s_bar[st]);
-        }
-    };
-
-    if (threadIdx.x == FETCHER) {
-#pragma unroll
-        for (int st = 0; st < NBUF; ++st) mbar_init(&s_bar[st], 1u);
-        s_dead = 0;
-        fence_async_smem();                                   // the barriers exist before a copy can complete on them
-        for (i64 r = 0; r < PRE; ++r) fetch(r);
-    }
-    __syncthreads();
-
-    const i64 base_prev = prev ? prev->count : 0;
-    i64 last_tile = -1, run_incl = 0;                         // warp 0: the block's previous tile, survivors up to and including it
-    i64 nvalid = (i64)1 << 62;                                // rounds in which this block has a tile (known once an id ran past the end)
-    i64 k = 0;
-    i64 copies_upto = -1;                                     // when giving up: last round whose copies may still be in flight
-    bool gave_up = false;
-    for (;; ++k) {
-        const int st = (int)(k % NBUF);
-        const bool arrived = mbar_wait(&s_bar[st], (u32)((k / NBUF) & 1), spin_limit);   // the round's id, and its input if it has a whole tile
-        if (!arrived) s_dead = 1;                             // seen by all after the barrier below
-        const i64 tile = arrived ? s_tile[st] : num_tiles;
-        if (tile >= num_tiles && nvalid > k) nvalid = k;
-        const bool have_k = k < nvalid;
-        const i64 j0 = k - LAG;                               // the round whose tile is written now
-        if (!have_k && j0 >= nvalid) break;                   // nothing left to rank, nothing left to write
-
-        // (1) rank tile k and stage its survivors in place
-        if (have_k && ranks) {
-            const i64 tile_base = tile * TILE;
-            A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A);
-            O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
-            int warp_run;
-            if (tile_base + TILE <= n) {
-#ifdef DCB_PIPE_PACK_RANKS
-                Pack<A, E> a[ROWS]; Pack<B, E> b[ROWS];
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r) {
-                    const int idx = warp * WARP_ELEMS + (r * 32 + lane) * E;
-                    a[r].load_shared(bufA + idx);
-                    if constexpr (C::n_in == 2)
-                        b[r].load_shared(reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + idx);
-                }
-                __syncwarp();                                 // every lane holds its packs before any lane overwrites the run
-                warp_run = compact_rank_and_stage<C, ROWS, E, true>(a, b, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
-#else
-                warp_run = compact_rank_rows_and_stage<C, ROWS * E>(
-                    bufA + warp * WARP_ELEMS,
-                    reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + warp * WARP_ELEMS, lane, stage);
-#endif
-            } else {
-                warp_run = compact_count_and_stage<C, BLOCK, ROWS, true, false>(in0, in1, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
-            }
-            if (lane == 0) s_tot[st][warp] = warp_run;
-        }
-        __syncthreads();   // counts of tile k visible; everyone is done writing tile k-LAG-1; s_prefix of tile k-LAG visible
-        if (s_dead) { gave_up = true; copies_upto = k + PRE - 1; break; }
-
-        // (2) refill the buffer tile k-LAG-1 left with the tile of round k+PRE
-        if (threadIdx.x == FETCHER) fetch(k + PRE);
-
-        if (offsets_warp) {
-            // (3) publish the count of tile k, then the output offset of tile k-LAG+1, for the next round
-            if (have_k && lane == 0) {
-                int tot = 0;
-#pragma unroll
-                for (int w = 0; w < WARPS; ++w) tot += s_tot[st][w];
-                desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tot));
-            }
-            const i64 j1 = k - LAG + 1;
-            if (j1 >= 0 && j1 < nvalid) {
-                const int s1 = (int)(j1 % NBUF);
-                const i64 t1 = s_tile[s1];
-                int tot1 = 0;
-#pragma unroll
-                for (int w = 0; w < WARPS; ++w) tot1 += s_tot[s1][w];
-                bool failed = false;
-                const i64 between = compact_range_sum(desc, last_tile + 1, t1, lane, epoch, spin_limit, abort_flag, failed);
-                const i64 exclusive = run_incl + between;
-                run_incl = exclusive + tot1;
-                last_tile = t1;
-                if (lane == 0) {
-                    s_prefix[j1 & 1] = failed ? -1 : base_prev + exclusive;
-                    if (!failed && t1 == num_tiles - 1) {
-                        const i64 total = base_prev + exclusive + tot1;
-                        res->count = total; res->count_f = (double)total;
-                        res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
-                        res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
-                    }
-                }
-            }
-        }
-
-        // (4) write tile k-LAG, then hand its buffer back to the copy engine's view of shared memory
-        if (j0 >= 0 && j0 < nvalid) {
-            const int s0 = (int)(j0 % NBUF);
-            const i64 prefix = s_prefix[j0 & 1];
-            if (prefix < 0) { gave_up = true; copies_upto = k + PRE; break; }
-            if (!ranks) continue;                             // the extra warp has no run to write
-            int warp_off = 0;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) warp_off += (w < warp) ? s_tot[s0][w] : 0;
-            const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)s0 * BYTES_A) + warp * WARP_ELEMS);
-            compact_copy_out<O, true>(out, out_cap, prefix + warp_off, s_tot[s0][warp], lane, stage0);
-            fence_async_smem();
-        }
-    }
-
-    if (gave_up) {
-        // Tell the tiles still waiting. Copies this block started must land before its shared memory is given to another
-        // block: wait for the rounds that were started, again with a limit.
-        if (threadIdx.x == 0) atomicExch(abort_flag, epoch);
-        __syncthreads();
-        if (threadIdx.x == FETCHER)
-            for (i64 j = k + 1; j <= copies_upto; ++j) (void)mbar_wait(&s_bar[(int)(j % NBUF)], (u32)((j / NBUF) & 1), spin_limit);
-    }
-    // Sign off. The last block to do so resets the counters for the next launch and has the final say on the record.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned int finished = atomicAdd(counters + 1, 1u);
-        if (finished == gridDim.x - 1) {
-            __threadfence();
-            if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT; }
-            counters[0] = 0; counters[1] = 0;
-        }
-    }
-}
-
-// Experimental variant of compact_pipe_body (built only when a pipeline is compiled with the extra-warp setting 2): the
-// warp that works out offsets does not take part in the round's barrier. The ranking warps meet at a barrier of their
-// own, the first of them publishes the tile's count, and the offsets warp follows at its own pace, one tile after the
-// other, handing each offset over through a shared-memory barrier; a ranking warp waits for it only if the offset of the
-// tile it is about to write, ranked LAG rounds ago, is still missing. Same buffers, same id drawing, same bounded waits.
-// Launch with BLOCK + 32 threads.
-template <class C, int BLOCK, int ROWS, int LAG, int NBUF>
-__device__ __forceinline__ void compact_pipe_free_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
-                                                       i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
-                                                       u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
-                                                       const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
-                                                       unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters) {
-    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
-    static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
-    constexpr int PRE = NBUF - LAG - 1;
-    static_assert(PRE >= 1 && LAG > PRE && NBUF <= 16, "NBUF = LAG + 1 + PRE with LAG > PRE >= 1");
-    static_assert(BLOCK >= 64 && BLOCK % 32 == 0, "at least two ranking warps");
-    constexpr int E = 16 / (int)sizeof(A);
-    constexpr int WARPS = BLOCK / 32;
-    constexpr int WARP_ELEMS = ROWS * 32 * E;
-    constexpr int TILE = WARPS * WARP_ELEMS;
-    constexpr u32 BYTES_A = (u32)(TILE * sizeof(A));
-    constexpr u32 BYTES_B = C::n_in == 2 ? (u32)(TILE * sizeof(B)) : 0u;
-    static_assert(BYTES_A % 16 == 0 && BYTES_B % 16 == 0, "bulk copies move multiples of 16 bytes");
-
-    extern __shared__ __align__(128) unsigned char s_dyn[];   // NBUF buffers of in0, then NBUF buffers of in1
-    // Round r uses slot r % NBUF and phase (r / NBUF) & 1 of: s_full (the copies have landed, the id is known),
-    // s_ranked (the counts of the tile are in s_tot), s_offset (s_prefix is valid).
-    __shared__ __align__(8) u64 s_full[NBUF], s_ranked[NBUF], s_offset[NBUF];
-    __shared__ i64 s_tile[NBUF];
-    __shared__ int s_tot[NBUF][WARPS];
-    __shared__ i64 s_prefix[NBUF];                            // -1 = the offsets warp gave up
-    __shared__ int s_dead;                                    // a wait ran out somewhere in this block
-
-    const int warp = (int)(threadIdx.x >> 5) - 1, lane = threadIdx.x & 31;   // ranking warps 0 .. WARPS-1; -1 = the offsets warp
-    const bool ranks = warp >= 0;
-    constexpr int PUBLISHER = 32;                             // lane 0 of the first ranking warp
-    constexpr int FETCHER = 64;                               // lane 0 of the second ranking warp
-    volatile int* dead = &s_dead;
-    bool exhausted = false;                                   // fetching thread only
-    i64 fetched_upto = -1;                                    // fetching thread only: last round it started
-
-    auto fetch = [&](i64 r) {
-        i64 t = num_tiles;
-        if (!exhausted) {
-            t = (i64)atomicAdd(counters, 1u);
-            if (t >= num_tiles) { t = num_tiles; exhausted = true; }
-        }
-        const int st = (int)(r % NBUF);
-        s_tile[st] = t;
-        fetched_upto = r;
-        if (t < num_tiles && (t + 1) * TILE <= n) {
-            mbar_expect_tx(&s_full[st], BYTES_A + BYTES_B);
-            bulk_load(s_dyn + (size_t)st * BYTES_A, in0 + t * TILE, BYTES_A, &s_full[st]);
-            if constexpr (C::n_in == 2)
-                bulk_load(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B, in1 + t * TILE, BYTES_B, &s_full[st]);
-        } else {
-            mbar_arrive(&s_full[st]);
-        }
-    };
-    // Bounded wait for round `r` of a barrier; ends early when another warp of the block has given up, and sleeps between
-    // tries so that a waiting warp does not take issue slots from the warps it waits for.
-    auto wait = [&](u64* bar, i64 r) -> bool {
-        const u32 parity = (u32)((r / NBUF) & 1);
-        if (mbar_try_wait(bar, parity)) return true;
-        const u64 max_ns = (u64)spin_limit * 1000ull < 2000000000ull ? (u64)spin_limit * 1000ull : 2000000000ull;
-        const u64 t0 = global_timer_ns();
-        for (u32 tries = 0; tries < spin_limit; ++tries) {
-            __nanosleep(tries < 8 ? 32 : 256);
-            if (mbar_try_wait(bar, parity)) return true;
-            if (*dead || global_timer_ns() - t0 > max_ns) break;
-        }
-        return false;
-    };
-
-    if (threadIdx.x == FETCHER) {
-#pragma unroll
-        for (int st = 0; st < NBUF; ++st) { mbar_init(&s_full[st], 1u); mbar_init(&s_ranked[st], 1u); mbar_init(&s_offset[st], 1u); }
-        s_dead = 0;
-        fence_async_smem();                                   // the barriers exist before a copy can complete on them
-        for (i64 r = 0; r < PRE; ++r) fetch(r);
-    }
-    __syncthreads();
-
-    if (!ranks) {
-        // ---------------------------------------------------------------- the offsets warp, at its own pace
-        const i64 base_prev = prev ? prev->count : 0;
-        i64 last_tile = -1, run_incl = 0;                     // the block's previous tile, survivors up to and including it
-        for (i64 j = 0;; ++j) {
-            const int s1 = (int)(j % NBUF);
-            if (!wait(&s_ranked[s1], j)) { if (lane == 0) { *dead = 1; atomicExch(abort_flag, epoch); } break; }
-            const i64 t1 = s_tile[s1];
-            if (t1 >= num_tiles) break;                       // the round after the block's last tile
-            int tot1 = 0;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) tot1 += s_tot[s1][w];
-            bool failed = false;
-            const i64 between = compact_range_sum(desc, last_tile + 1, t1, lane, epoch, spin_limit, abort_flag, failed);
-            const i64 exclusive = run_incl + between;
-            run_incl = exclusive + tot1;
-            last_tile = t1;
-            __syncwarp();
-            if (lane == 0) {
-                s_prefix[s1] = failed ? -1 : base_prev + exclusive;
-                if (!failed && t1 == num_tiles - 1) {
-                    const i64 total = base_prev + exclusive + tot1;
-                    res->count = total; res->count_f = (double)total;
-                    res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
-                    res->flags = total > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
-                }
-                if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
-                mbar_arrive(&s_offset[s1]);                   // the ranking warps read s_prefix after this
-            }
-            if (failed) break;
-        }
-    } else {
-        // ---------------------------------------------------------------- the ranking warps, one barrier of their own per round
-        i64 nvalid = (i64)1 << 62;                            // rounds in which this block has a tile
-        for (i64 k = 0;; ++k) {
-            const int st = (int)(k % NBUF);
-            const bool arrived = wait(&s_full[st], k);        // the round's id, and its input if it has a whole tile
-            if (!arrived) *dead = 1;                          // acted on by all after the barrier below
-            const i64 tile = arrived ? s_tile[st] : num_tiles;
-            if (tile >= num_tiles && nvalid > k) nvalid = k;
-            const bool have_k = k < nvalid;
-            const i64 j0 = k - LAG;                           // the round whose tile is written now
-
-            if (have_k) {                                     // rank tile k and stage its survivors in place
-                const i64 tile_base = tile * TILE;
-                A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A);
-                O* stage = reinterpret_cast<O*>(bufA + warp * WARP_ELEMS);
-                int warp_run;
-                if (tile_base + TILE <= n)
-                    warp_run = compact_rank_rows_and_stage<C, ROWS * E>(
-                        bufA + warp * WARP_ELEMS,
-                        reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + warp * WARP_ELEMS, lane, stage);
-                else
-                    warp_run = compact_count_and_stage<C, BLOCK, ROWS, true, false>(in0, in1, n, tile_base + (i64)warp * WARP_ELEMS, lane, stage);
-                if (lane == 0) s_tot[st][warp] = warp_run;
-            }
-            // The ranking warps only (the offsets warp is elsewhere): counts of tile k visible, everyone done writing tile
-            // k-LAG-1. Every decision to leave the loop is taken after this barrier, from values all threads agree on: the
-            // barrier itself ORs what each thread saw of s_dead, because the offsets warp may set it at any moment and
-            // two threads reading it one after the other could otherwise part ways, one of them waiting here for ever.
-            unsigned int any_dead;
-            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                         : "=r"(any_dead) : "r"((unsigned int)*dead), "n"(BLOCK) : "memory");
-            if (any_dead) break;
-            if (!have_k && j0 >= nvalid) break;               // nothing left to rank, nothing left to write
-
-            if (threadIdx.x == FETCHER) fetch(k + PRE);       // refill the buffer tile k-LAG-1 left
-            if (threadIdx.x == PUBLISHER && (have_k || k == nvalid)) {
-                if (have_k) {
-                    int tot = 0;
-#pragma unroll
-                    for (int w = 0; w < WARPS; ++w) tot += s_tot[st][w];
-                    desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)tot));
-                }
-                mbar_arrive(&s_ranked[st]);                   // also for the first round without a tile: it ends the offsets warp
-            }
-
-            if (j0 >= 0 && j0 < nvalid) {                     // write tile k-LAG, then hand its buffer back to the copy engine
-                const int s0 = (int)(j0 % NBUF);
-                const bool known = wait(&s_offset[s0], j0);
-                const i64 prefix = known ? s_prefix[s0] : -1;
-                if (prefix < 0) {
-                    *dead = 1;                                // acted on by all after the next barrier
-                } else {
-                    int warp_off = 0;
-#pragma unroll
-                    for (int w = 0; w < WARPS; ++w) warp_off += (w < warp) ? s_tot[s0][w] : 0;
-                    const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)s0 * BYTES_A) + warp * WARP_ELEMS);
-                    compact_copy_out<O, true>(out, out_cap, prefix + warp_off, s_tot[s0][warp], lane, stage0);
-                    fence_async_smem();
-                }
-            }
-        }
-    }
-
-    __syncthreads();
-    if (s_dead) {
-        // Tell the tiles still waiting. Copies this block started must land before its shared memory is given to another
-        // block: wait for the rounds that may still be on their way, again with a limit each.
-        if (threadIdx.x == 0) atomicExch(abort_flag, epoch);
-        if (threadIdx.x == FETCHER)
-            for (i64 r = fetched_upto - NBUF + 1 > 0 ? fetched_upto - NBUF + 1 : 0; r <= fetched_upto; ++r)
-                (void)mbar_wait(&s_full[(int)(r % NBUF)], (u32)((r / NBUF) & 1), spin_limit);
-    }
-    // Sign off. The last block to do so resets the counters for the next launch and has the final say on the record.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned int finished = atomicAdd(counters + 1, 1u);
-        if (finished == gridDim.x - 1) {
-            __threadfence();
-            if (*(volatile unsigned int*)abort_flag == epoch) { res->count = 0; res->count_f = 0; res->flags = (u64)FLAG_TIMEOUT; }
-            counters[0] = 0; counters[1] = 0;
-        }
-    }
-}
-
-
 // ------------------------------------------------------------------ compact, streamed: warp-specialised persistent blocks
 // Same result as compact_body, built so that nothing on the data path waits for anything but data.
 //
@@ -1340,13 +889,14 @@ __device__ __forceinline__ void compact_pipe_free_body(const typename C::in0_t* 
 //             read (hence sizeof(out) <= sizeof(in0)), leaves its count in shared memory and arrives on `ranked`; then it
 //             turns to the tile it ranked LAG rounds ago, waits for `offs` (normally long complete), copies its run to the
 //             output with 16-byte stores and arrives on `empty`. Workers never wait for each other;
-//   offsets   waits for `ranked`, publishes the tile's count (one relaxed 64-bit store), then finishes the tile of the round
-//             before: its output offset is the offset after the block's previous tile plus the counts of the tiles drawn
-//             in between, a known range of descriptors read with all loads in flight at once (their tiles were ranked a
-//             round ago as well, so the counts are normally there); it leaves one offset per worker in shared memory and
-//             arrives on `offs`.
+//   offsets   waits for `ranked`, publishes the tile's count (one relaxed 64-bit store), then works on the two tiles before
+//             it. A tile's output offset is the offset after the block's previous tile plus the counts of the tiles
+//             drawn in between, a known range of descriptors read with all loads in flight at once. Those loads are
+//             issued one round after the tile was ranked (by then its neighbours in id order have published their
+//             counts) and summed one round later still (a round trip to L2 takes about a round), so the warp never
+//             waits for memory; it leaves one offset per worker in shared memory and arrives on `offs`.
 //
-// The look-back is therefore one round trip to L2 beside the workers, LAG rounds before a worker asks for its result. Progress:
+// A tile's offset is thus ready two rounds after the tile was ranked, which is when a worker asks for it (LAG = 2). Progress:
 // a tile's offset needs only counts of tiles with smaller ids; an id is drawn by a running block at the moment its copy
 // is started, and ranking never waits for another block, so the smallest id not yet counted is always about to be.
 // Nothing is assumed about how many blocks are resident. Every wait is bounded: polls of a descriptor by `spin_limit`,
@@ -1365,9 +915,161 @@ __device__ __forceinline__ void compact_pipe_free_body(const typename C::in0_t* 
 // Limit of one wait on a block's own barrier or bulk copy, in SM clock cycles (about two seconds). It is measured with
 // the SM's cycle counter, which costs a few cycles to read; the nanosecond timer shared by the whole GPU takes microseconds
 // per read, which a wait on the data path cannot afford.
+#ifndef DCB_STREAM_VEC_OUT
+#define DCB_STREAM_VEC_OUT 0
+#endif
 #ifndef DCB_STREAM_WAIT_CYCLES
 #define DCB_STREAM_WAIT_CYCLES 4000000000ll
 #endif
+// Store of one survivor into a warp's staging run in shared memory, as straight-line code: the store and the advance
+// of the write position are predicated on bit `mask` of `keepbits` (a branch per element, which is what the plain C++
+// form compiles to, costs several times as many instructions). `addr` is a shared-space byte address.
+template <typename O>
+__device__ __forceinline__ void stage_if(u32& addr, const O& v, u32 keepbits, u32 mask) {
+    if constexpr (sizeof(O) == 4) {
+        u32 w; memcpy_bits(w, v);
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %2, %3;\n\tsetp.ne.b32 p, t, 0;\n\t@p st.shared.b32 [%0], %1;\n\t@p add.u32 %0, %0, 4;\n\t}"
+                     : "+r"(addr) : "r"(w), "r"(keepbits), "r"(mask) : "memory");
+    } else if constexpr (sizeof(O) == 8) {
+        u64 w; memcpy_bits(w, v);
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %2, %3;\n\tsetp.ne.b32 p, t, 0;\n\t@p st.shared.b64 [%0], %1;\n\t@p add.u32 %0, %0, 8;\n\t}"
+                     : "+r"(addr) : "l"(w), "r"(keepbits), "r"(mask) : "memory");
+    } else if constexpr (sizeof(O) == 2) {
+        unsigned short w; memcpy_bits(w, v);
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %2, %3;\n\tsetp.ne.b32 p, t, 0;\n\t@p st.shared.b16 [%0], %1;\n\t@p add.u32 %0, %0, 2;\n\t}"
+                     : "+r"(addr) : "h"(w), "r"(keepbits), "r"(mask) : "memory");
+    } else {
+        unsigned char b; memcpy_bits(b, v);
+        const u32 w = b;
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %2, %3;\n\tsetp.ne.b32 p, t, 0;\n\t@p st.shared.u8 [%0], %1;\n\t@p add.u32 %0, %0, 1;\n\t}"
+                     : "+r"(addr) : "r"(w), "r"(keepbits), "r"(mask) : "memory");
+    }
+}
+
+// Chain, ranks and staging of one warp's run of a tile for the streamed kernel: as compact_rank_and_stage, with the
+// whole run inside the array (no bound checks) and the survivors stored by stage_if.
+template <class C, int ROWS, int E>
+__device__ __forceinline__ int stream_rank_and_stage(const Pack<typename C::in0_t, E> (&a)[ROWS], const Pack<typename C::in1_t, E> (&b)[ROWS],
+                                                     int lane, u32 stage_addr) {
+    typedef typename C::in1_t B; typedef typename C::out_t O;
+    constexpr int FIELD = (32 * E <= 128) ? 8 : 16;
+    constexpr int PER_WORD = 32 / FIELD;
+    constexpr int WORDS = (ROWS + PER_WORD - 1) / PER_WORD;
+    constexpr u32 FMASK = (FIELD == 8) ? 0xffu : 0xffffu;
+    O val[ROWS][E];
+    u32 keepbits[ROWS];
+    u32 packed[WORDS];
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) packed[w] = 0;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        u32 bits = 0;
+#pragma unroll
+        for (int k = 0; k < E; ++k) {
+            bool keep;
+            if constexpr (C::n_in == 2) keep = C::apply(a[r].e[k], b[r].e[k], val[r][k]);
+            else keep = C::apply(a[r].e[k], B(), val[r][k]);
+            bits |= keep ? (1u << k) : 0u;
+        }
+        keepbits[r] = bits;
+        packed[r / PER_WORD] += (u32)__popc(bits) << ((r % PER_WORD) * FIELD);
+    }
+    u32 incl[WORDS];
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) {
+        u32 v = packed[w];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += t;
+        }
+        incl[w] = v;
+    }
+    int row_start = 0;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int w = r / PER_WORD, sh = (r % PER_WORD) * FIELD;
+        const u32 tot_word = __shfl_sync(0xffffffffu, incl[w], 31);
+        const int before = (int)(((incl[w] - packed[w]) >> sh) & FMASK);
+        u32 addr = stage_addr + (u32)(row_start + before) * (u32)sizeof(O);
+#pragma unroll
+        for (int k = 0; k < E; ++k) stage_if<O>(addr, val[r][k], keepbits[r], 1u << k);
+        row_start += (int)((tot_word >> sh) & FMASK);
+    }
+    return row_start;
+}
+
+// Count descriptors of the streamed kernel: one 32-bit word per tile = epoch(12) | written(1) | count(19), four to a
+// 16-byte load, so that the counts of 128 tiles come back with one instruction per warp.
+__device__ __forceinline__ u32 cdesc_make(u32 epoch, u32 count) { return ((epoch & 0xfffu) << 20) | 0x80000u | (count & 0x7ffffu); }
+__device__ __forceinline__ bool cdesc_written(u32 d, u32 epoch) { return (d >> 19) == (((epoch & 0xfffu) << 1) | 1u); }
+__device__ __forceinline__ void cdesc_store(u32* p, u32 v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cdesc_load4(const u32* p, u32 (&v)[4]) {
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(p) : "memory");
+}
+// Loads of the window of D4 * 128 descriptors that starts at the 16-byte boundary at or below tile `lo`, cut at `hi`.
+template <int D4>
+__device__ __forceinline__ void cdesc_issue(const u32* __restrict__ cdesc, i64 lo, i64 hi, int lane, u32 (&d)[D4][4]) {
+    const i64 base = lo & ~(i64)3;
+    const int span = (int)(hi - base < (i64)D4 * 128 ? hi - base : (i64)D4 * 128);   // descriptors of the window that matter
+#pragma unroll
+    for (int u = 0; u < D4; ++u) {
+        const int rel = (u * 32 + lane) * 4;
+        if (rel < span) cdesc_load4(cdesc + base + rel, d[u]);
+        else { d[u][0] = 0; d[u][1] = 0; d[u][2] = 0; d[u][3] = 0; }
+    }
+}
+// Sum of the counts of tiles [lo, hi) by one whole warp; `d` holds the loads cdesc_issue made for (lo, hi). Counts that
+// were not there yet are asked for again, all together, with a bounded number of polls; a range longer than one window
+// is finished window by window. Returns the sum in every lane, or sets `failed`.
+template <int D4>
+__device__ __forceinline__ i64 cdesc_finish(const u32* __restrict__ cdesc, i64 lo, i64 hi, int lane, u32 epoch, u32 spin_limit,
+                                            const unsigned int* abort_flag, volatile int* dead, u32 (&d)[D4][4], bool& failed) {
+    i64 total = 0;
+    for (;;) {
+        const i64 base = lo & ~(i64)3;
+        const int first = (int)(lo - base);
+        const int span = (int)(hi - base < (i64)D4 * 128 ? hi - base : (i64)D4 * 128);
+        for (u32 polls = 0;;) {
+            bool stale = false;
+#pragma unroll
+            for (int u = 0; u < D4; ++u) {
+                const int rel = (u * 32 + lane) * 4;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) stale = stale || (rel + e >= first && rel + e < span && !cdesc_written(d[u][e], epoch));
+            }
+            if (!__any_sync(0xffffffffu, stale)) break;
+            if (++polls > spin_limit || *dead || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
+            __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
+#pragma unroll
+            for (int u = 0; u < D4; ++u) {
+                const int rel = (u * 32 + lane) * 4;
+                bool again = false;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) again = again || (rel + e >= first && rel + e < span && !cdesc_written(d[u][e], epoch));
+                if (again) cdesc_load4(cdesc + base + rel, d[u]);
+            }
+        }
+        if (failed) break;
+        int sum = 0;                                          // at most D4 * 128 counts below 2^19 each
+#pragma unroll
+        for (int u = 0; u < D4; ++u) {
+            const int rel = (u * 32 + lane) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum += (rel + e >= first && rel + e < span) ? (int)(d[u][e] & 0x7ffffu) : 0;
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        total += sum;
+        lo = base + (i64)D4 * 128;
+        if (lo >= hi) break;
+        cdesc_issue<D4>(cdesc, lo, hi, lane, d);              // the rare long range: the next window, waited for in place
+    }
+    return total;
+}
+
 __device__ __forceinline__ void l2_prefetch_bulk(const void* src_global, u32 bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
 }
@@ -1380,8 +1082,9 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                                                     unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters, u32 head) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
-    static_assert(LAG >= 1 && NBUF >= LAG + 2 && NBUF <= 16, "NBUF = LAG + 1 + tiles on their way in");
-    static_assert(WARPS >= 1 && WARPS <= 30 && DEPTH >= 1, "one offsets lane per worker warp");
+    static_assert(LAG >= 2 && NBUF >= LAG + 2 && NBUF <= 16, "an offset is ready two rounds after its tile was ranked; NBUF = LAG + 1 + tiles on their way in");
+    static_assert(WARPS >= 1 && WARPS <= 30 && DEPTH >= 1 && DEPTH <= 8, "one offsets lane per worker warp; DEPTH * 128 tiles per window");
+    static_assert(WARPS * ROWS * 32 * (16 / (int)sizeof(typename C::in0_t)) < (1 << 19), "a tile's count must fit the descriptor");
     constexpr int E = 16 / (int)sizeof(A);
     constexpr int WARP_ELEMS = ROWS * 32 * E;
     constexpr int TILE = WARPS * WARP_ELEMS;
@@ -1406,10 +1109,15 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
 
     // Bounded wait for phase `parity` of one of the block's barriers: false when another warp of the block gave up or
     // the fixed time limit passed (one try may itself suspend the thread for a while).
+    // A waiting warp sleeps between tries: a warp that spins takes issue slots from the very warps it is waiting for.
+#ifndef DCB_STREAM_WAIT_SLEEP_NS
+#define DCB_STREAM_WAIT_SLEEP_NS 100
+#endif
     auto wait = [&](u64* bar, u32 parity, bool heed_dead) -> bool {
         if (mbar_try_wait(bar, parity)) return true;
         const i64 t0 = clock64();
         for (u32 i = 0; i < (1u << 30); ++i) {
+            if (DCB_STREAM_WAIT_SLEEP_NS > 0) __nanosleep(DCB_STREAM_WAIT_SLEEP_NS);
             if (mbar_try_wait(bar, parity)) return true;
             if (heed_dead && *dead) return false;
             if ((i & 15u) == 15u && clock64() - t0 > DCB_STREAM_WAIT_CYCLES) return false;
@@ -1427,6 +1135,18 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
     }
     __syncthreads();
 
+    // DCB_STREAM_STATS = 1 / 2 / 3 (profiling builds only) adds up, over all blocks, clock cycles the offsets warp / worker 0
+    // / the loader spent in each of its waits and work phases, in the four spare slots of the record.
+#ifdef DCB_STREAM_STATS
+    i64 stat[4] = {0, 0, 0, 0};
+#define DCB_STAT_BEGIN const i64 stat_t0 = clock64()
+#define DCB_STAT_END(role, i) do { if (DCB_STREAM_STATS == (role)) stat[i] += clock64() - stat_t0; } while (0)
+#define DCB_STAT_ADD(role, i, v) do { if (DCB_STREAM_STATS == (role)) stat[i] += (v); } while (0)
+#else
+#define DCB_STAT_BEGIN
+#define DCB_STAT_END(role, i)
+#define DCB_STAT_ADD(role, i, v)
+#endif
     i64 issued = 0;                                           // loader thread: rounds it has started
     if (warp_id == 1) {
         // ---------------------------------------------------------------- loader (one thread)
@@ -1443,7 +1163,9 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                 // The id is asked for before the wait for the slot: the counter's round trip overlaps that wait.
                 i64 t = (i64)atomicAdd(counters, 1u);
                 if (t > num_tiles) t = num_tiles;
-                if (r >= NBUF && !wait(&s_empty[st], ph ^ 1u, true)) { *dead = 1; break; }
+                { DCB_STAT_BEGIN;
+                  if (r >= NBUF && !wait(&s_empty[st], ph ^ 1u, true)) { *dead = 1; break; }
+                  DCB_STAT_END(3, 0); DCB_STAT_ADD(3, 1, 1); }
                 s_tile[st] = t;
                 const bool whole = t < num_tiles && t * TILE >= lo && (t + 1) * TILE <= hi;
                 if (whole) {
@@ -1469,12 +1191,22 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
     } else if (warp_id == 0) {
         // ---------------------------------------------------------------- offsets warp
         const i64 base_prev = prev ? prev->count : 0;
-        i64 last_tile = -1, run_incl = 0;                     // the block's previous tile, survivors up to and including it
-        bool pending = false;                                 // a tile whose count is published and whose offset is not yet
-        i64 p_tile = 0; int p_st = 0, p_excl = 0, p_total = 0;
+        i64 last_tile = -1, run_incl = 0;                     // the block's previous finished tile, survivors up to and including it
+        // Two tiles are in the works besides the one just ranked: `c_` has its descriptor loads in flight (issued a round
+        // ago, summed now), `i_` was ranked a round ago and gets its loads issued now. A round trip to L2 takes about as
+        // long as a round, so it is never waited for; and a tile's loads go out a round after its neighbours in id order
+        // published their counts, so they rarely come back empty.
+        bool c_have = false, i_have = false;
+        i64 c_tile = 0, c_lo = 0, i_tile = 0;
+        int c_st = 0, c_excl = 0, c_total = 0, i_st = 0, i_excl = 0, i_total = 0;
+        u32 d[DEPTH][4];
+        u32* cdesc = reinterpret_cast<u32*>(desc);            // this kernel's descriptors are 32-bit counts
         int st = 0; u32 ph = 0;
-        for (;;) {
-            if (!wait(&s_ranked[st], ph, true)) { *dead = 1; break; }
+        bool failed = false;
+        for (bool more = true; more && !failed;) {
+            { DCB_STAT_BEGIN;
+              if (!wait(&s_ranked[st], ph, true)) { *dead = 1; break; }
+              DCB_STAT_END(1, 0); DCB_STAT_ADD(1, 3, 1); }
             const i64 tile = s_tile[st];
             const bool valid = tile < num_tiles;
             int cnt = 0, incl = 0, total = 0;
@@ -1488,64 +1220,46 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                 }
                 total = __shfl_sync(0xffffffffu, incl, 31);
                 if (lane == 0 && !(tile == 0 && *(volatile unsigned int*)(abort_flag + 1) == epoch))
-                    desc_store(desc + tile, desc_make(epoch, ST_AGGREGATE, (u64)total));
+                    cdesc_store(cdesc + tile, cdesc_make(epoch, (u32)total));
             }
-            if (pending) {
-                // Finish the tile of the round before: sum the counts of (last_tile, p_tile). Its neighbours in id order
-                // were ranked a round ago too, so their counts are normally all there: one round trip to L2 with every
-                // load in flight at once. Counts that are missing are asked for again together, not one after the other.
-                const i64 p_lo = last_tile + 1;
-                u64 d[DEPTH];
-#pragma unroll
-                for (int u = 0; u < DEPTH; ++u) {
-                    const i64 idx = p_lo + (i64)u * 32 + lane;
-                    d[u] = idx < p_tile ? desc_load(desc + idx) : 0ull;
-                }
-                bool failed = false;
-                for (u32 polls = 0;;) {
-                    bool stale = false;
-#pragma unroll
-                    for (int u = 0; u < DEPTH; ++u)
-                        stale = stale || (p_lo + (i64)u * 32 + lane < p_tile && desc_status(d[u], epoch) == ST_INVALID);
-                    if (!__any_sync(0xffffffffu, stale)) break;
-                    if (++polls > spin_limit || *dead || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
-                    __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
-#pragma unroll
-                    for (int u = 0; u < DEPTH; ++u) {
-                        const i64 idx = p_lo + (i64)u * 32 + lane;
-                        if (idx < p_tile && desc_status(d[u], epoch) == ST_INVALID) d[u] = desc_load(desc + idx);
+            more = valid;
+            // After the block's last tile the two tiles still in the works are finished one after the other.
+            for (int pass = 0; pass < (valid ? 1 : 3) && !failed; ++pass) {
+                if (c_have) {
+                    DCB_STAT_BEGIN;
+                    // Sum the counts of (last_tile, c_tile): the loads went out a round ago.
+                    const i64 sum = cdesc_finish<DEPTH>(cdesc, c_lo, c_tile, lane, epoch, spin_limit, abort_flag, dead, d, failed);
+                    DCB_STAT_END(1, 1);
+                    const i64 exclusive = run_incl + sum;
+                    if (lane < WARPS) s_off[c_st][lane] = failed ? -1 : base_prev + exclusive + c_excl;
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (!failed && c_tile == num_tiles - 1) {
+                            const i64 total_all = base_prev + exclusive + c_total;
+                            res->count = total_all; res->count_f = (double)total_all;
+                            res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+                            res->offset = 0; res->local_count = total_all;
+                            res->flags = total_all > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+                        }
+                        if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
+                        mbar_arrive(&s_offs[c_st]);           // the workers read s_off after this
                     }
+                    run_incl = exclusive + c_total;
+                    last_tile = c_tile;
+                    c_have = false;
+                    DCB_STAT_END(1, 2);
                 }
-                i64 sum = 0;
-#pragma unroll
-                for (int u = 0; u < DEPTH; ++u)
-                    if (p_lo + (i64)u * 32 + lane < p_tile) sum += (i64)(d[u] & DESC_VALUE_MASK);
-#pragma unroll
-                for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
-                if (!failed && p_lo + 32 * DEPTH < p_tile)    // a longer range (the block's first tile, or a block that fell behind)
-                    sum += compact_range_sum(desc, p_lo + 32 * DEPTH, p_tile, lane, epoch, spin_limit, abort_flag, failed);
-                const i64 exclusive = run_incl + sum;
-                if (lane < WARPS) s_off[p_st][lane] = failed ? -1 : base_prev + exclusive + p_excl;
-                __syncwarp();
-                if (lane == 0) {
-                    if (!failed && p_tile == num_tiles - 1) {
-                        const i64 total_all = base_prev + exclusive + p_total;
-                        res->count = total_all; res->count_f = (double)total_all;
-                        res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
-                        res->offset = 0; res->local_count = total_all;
-                        res->flags = total_all > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
-                    }
-                    if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
-                    mbar_arrive(&s_offs[p_st]);               // the workers read s_off after this
+                if (i_have && !failed) {
+                    c_lo = last_tile + 1;
+                    cdesc_issue<DEPTH>(cdesc, c_lo, i_tile, lane, d);
+                    c_have = true; c_tile = i_tile; c_st = i_st; c_excl = i_excl; c_total = i_total;
+                    i_have = false;
                 }
-                if (failed) break;
-                run_incl = exclusive + p_total;
-                last_tile = p_tile;
-                pending = false;
             }
-            if (!valid) break;                                // the round after the block's last tile
-            pending = true; p_tile = tile; p_st = st; p_excl = incl - cnt; p_total = total;
-            if (++st == NBUF) { st = 0; ph ^= 1u; }
+            if (valid) {
+                i_have = true; i_tile = tile; i_st = st; i_excl = incl - cnt; i_total = total;
+                if (++st == NBUF) { st = 0; ph ^= 1u; }
+            }
         }
     } else {
         // ---------------------------------------------------------------- workers
@@ -1554,11 +1268,14 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
         int st = 0, sj = 0; u32 ph = 0, pj = 0;               // slot and phase of round k, and of round k - LAG
         for (i64 k = 0; k < nvalid + LAG; ++k) {
             if (k < nvalid) {
-                if (!wait(&s_full[st], ph, true)) { *dead = 1; break; }
+                { DCB_STAT_BEGIN;
+                  if (!wait(&s_full[st], ph, true)) { *dead = 1; break; }
+                  if (w == 0) DCB_STAT_END(2, 0); }
                 const i64 tile = s_tile[st];
                 if (tile >= num_tiles) {
                     nvalid = k;
                 } else {
+                    DCB_STAT_BEGIN;
                     const i64 warp_base = tile * TILE + (i64)w * WARP_ELEMS;
                     A* bufA = reinterpret_cast<A*>(s_dyn + (size_t)st * BYTES_A) + w * WARP_ELEMS;
                     const B* bufB = reinterpret_cast<const B*>(s_dyn + (size_t)NBUF * BYTES_A + (size_t)st * BYTES_B) + w * WARP_ELEMS;
@@ -1572,7 +1289,7 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                             if constexpr (C::n_in == 2) b[r].load_shared(bufB + (r * 32 + lane) * E);
                         }
                         __syncwarp();                         // every lane holds its packs before any lane overwrites the run
-                        run = compact_rank_and_stage<C, ROWS, E, true>(a, b, hi, warp_base, lane, stage);
+                        run = stream_rank_and_stage<C, ROWS, E>(a, b, lane, smem_addr(stage));
                     } else {
 #pragma unroll
                         for (int r = 0; r < ROWS; ++r) {
@@ -1587,6 +1304,7 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                         run = compact_rank_and_stage<C, ROWS, E, false>(a, b, hi, warp_base, lane, stage, lo);
                     }
                     if (lane == 0) s_cnt[st][w] = run;
+                    if (w == 0) DCB_STAT_END(2, 1);
                 }
                 __syncwarp();                                 // the staged run and its count are written
                 if (lane == 0) mbar_arrive(&s_ranked[st]);    // also for the round without a tile: it ends the offsets warp
@@ -1594,20 +1312,30 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
             }
             if (k >= LAG) {
                 if (k - LAG < nvalid) {                       // write the tile ranked LAG rounds ago, give its slot back
-                    if (!wait(&s_offs[sj], pj, true)) { *dead = 1; break; }
+                    { DCB_STAT_BEGIN;
+                      if (!wait(&s_offs[sj], pj, true)) { *dead = 1; break; }
+                      if (w == 0) DCB_STAT_END(2, 2); }
+                    DCB_STAT_BEGIN;
                     const i64 off = s_off[sj][w];
                     if (off < 0) { *dead = 1; break; }
                     const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)sj * BYTES_A) + w * WARP_ELEMS);
-                    compact_copy_out<O, true>(out, out_cap, off, s_cnt[sj][w], lane, stage0);
+                    // Consecutive lanes move consecutive survivors: no bank conflicts on the way out of shared memory, whole
+                    // 128-byte lines on the way into L2 (16-byte stores would read shared memory four lanes to a bank).
+                    compact_copy_out<O, DCB_STREAM_VEC_OUT != 0>(out, out_cap, off, s_cnt[sj][w], lane, stage0);
                     fence_async_smem();                       // this warp's accesses to the slot come before the next copy into it
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&s_empty[sj]);
+                    if (w == 0) DCB_STAT_END(2, 3);
                 }
                 if (++sj == NBUF) { sj = 0; pj ^= 1u; }
             }
         }
     }
 
+#ifdef DCB_STREAM_STATS
+    if (lane == 0 && (warp_id == 0 ? DCB_STREAM_STATS == 1 : (warp_id == 1 ? DCB_STREAM_STATS == 3 : (warp_id == 2 && DCB_STREAM_STATS == 2))))
+        for (int i = 0; i < 4; ++i) atomicAdd((u64*)&res->pad[i], (u64)stat[i]);
+#endif
     __syncthreads();
     if (s_dead) {
         // Tell the blocks still waiting. Copies this block started must land before its shared memory is given to another

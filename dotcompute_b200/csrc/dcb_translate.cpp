@@ -988,21 +988,8 @@ static std::string replace_all(std::string s, const std::string& a, const std::s
 }
 
 namespace {
-const int kPipeBlock = 256;
 int pipe_bytes_per_elem(const ChainInfo& info) { return type_size(info.in0) + (info.n_in == 2 ? type_size(info.in1) : 0); }
 }  // namespace
-
-int pipe_rows_for(const ChainInfo& info) {
-    if (info.terminal != OP_TOARRAY || !info.has_filter) return 0;
-    if (type_size(info.out_type) > type_size(info.in0)) return 0;
-    const int e = 16 / type_size(info.in0);
-    // one buffer of every input: at most 16 KB, so that four of them leave room for three blocks per SM
-    const int rows = 16384 / (kPipeBlock * e * pipe_bytes_per_elem(info));
-    return rows < 1 ? 0 : (rows > 8 ? 8 : rows);
-}
-int pipe_block_threads(int ctrl) { return kPipeBlock + (ctrl ? 32 : 0); }
-long long pipe_tile_elems(const ChainInfo& info, int rows) { return (long long)(kPipeBlock / 32) * rows * 32 * (16 / type_size(info.in0)); }
-long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf) { return (long long)nbuf * pipe_tile_elems(info, rows) * pipe_bytes_per_elem(info); }
 
 int stream_rows_for(const ChainInfo& info, int warps) {
     if (info.terminal != OP_TOARRAY || !info.has_filter) return 0;
@@ -1055,22 +1042,6 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                  "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag) {\n"
                  "    dcb::compact_body<" + C + ", " + CB + ", " + rows + ", " + vec + ">(" + cast_in() + ", n, (" + C +
                  "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
-            const int prow = tuning.pipe_rows > 0 ? tuning.pipe_rows : pipe_rows_for(info);
-            if (v == 0 && pipe_rows_for(info) > 0) {
-                const std::string PB = std::to_string(kPipeBlock);
-                const std::string PT = std::to_string(pipe_block_threads(tuning.pipe_ctrl));
-                const std::string pbounds = tuning.pipe_min_blocks > 0 ? PT + ", " + std::to_string(tuning.pipe_min_blocks) : PT;
-                s += "extern \"C\" __global__ void __launch_bounds__(" + pbounds + ") dcb_compact_pipe" + suffix +
-                     "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
-                     "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag, "
-                     "unsigned int* counters) {\n" +
-                     (tuning.pipe_ctrl == 2
-                          ? "    dcb::compact_pipe_free_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) +
-                                ", " + std::to_string(tuning.pipe_nbuf) + ">("
-                          : "    dcb::compact_pipe_body<" + C + ", " + PB + ", " + std::to_string(prow) + ", " + std::to_string(tuning.pipe_lag) + ", " +
-                                std::to_string(tuning.pipe_nbuf) + ", " + std::to_string(tuning.pipe_ctrl ? 1 : 0) + ">(") + cast_in() + ", n, (" + C +
-                     "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters);\n}\n";
-            }
             if (v == 0 && tuning.stream && stream_rows_for(info, tuning.stream_warps) > 0) {
                 const int srow = tuning.stream_rows > 0 ? tuning.stream_rows : stream_rows_for(info, tuning.stream_warps);
                 const std::string ST = std::to_string(stream_block_threads(tuning.stream_warps));

@@ -68,34 +68,20 @@ struct Tuning {
     int compact_block = 256;    // threads per block of the compaction kernels
     int compact_rows = 0;       // rows per warp in the compaction tile; 0 = automatic (dcb::compact_rows_for)
     int compact_min_blocks = 4; // second argument of __launch_bounds__ for the compaction kernels; 0 = none
-    int pipe_rows = 0;          // rows per warp in the pipelined compaction kernel; 0 = automatic (pipe_rows_for)
-    int pipe_lag = 2;           // rounds between ranking a tile and writing it
-    int pipe_nbuf = 4;          // shared-memory buffers per input: lag + 1 + tiles on their way in (fewer than lag)
-    int pipe_ctrl = 1;          // 1 = an extra warp for counts and offsets (288 threads per block instead of 256);
-                                // 2 = that warp outside the round's barrier (experimental, dcb::compact_pipe_free_body)
-    int pipe_min_blocks = 3;    // second argument of __launch_bounds__ for the pipelined compaction kernel; 0 = none
     // streamed compaction kernel (dcb::compact_stream_body)
     int stream = 1;             // 1 = build it (as dcb_compact_stream) when the query allows
-    int stream_warps = 8;       // worker warps per block (the block has two more warps: offsets and loader)
+    int stream_warps = 4;       // worker warps per block (the block has two more warps: offsets and loader)
     int stream_rows = 0;        // rows of 32 packs per worker and tile; 0 = automatic (stream_rows_for)
-    int stream_lag = 2;         // rounds between ranking a tile and writing it
-    int stream_nbuf = 4;        // shared-memory slots per input
-    int stream_depth = 16;      // descriptors per lane the offsets warp loads a round ahead (32 * depth tiles)
+    int stream_lag = 3;         // rounds between ranking a tile and writing it (its offset is ready after two)
+    int stream_nbuf = 6;        // shared-memory slots per input: lag + 1 + tiles on their way in
+    int stream_depth = 4;       // 16-byte descriptor loads per lane of the offsets warp (128 * depth tiles per window)
     int stream_ahead_mb = 12;   // distance of the L2 prefetch in front of the tile being drawn; 0 = none
     int stream_draw_ahead = 0;  // rounds the draw of a tile id may run ahead of ranking; 0 = as soon as a slot is free
-    int stream_min_blocks = 3;  // second argument of __launch_bounds__; 0 = none
+    int stream_min_blocks = 2;  // second argument of __launch_bounds__; 0 = none
 };
 
-// Rows per warp of the pipelined compaction kernel (dcb::compact_pipe_body, 256 threads, 16-byte packs of the
-// first input), or 0 when the query cannot use it: it stages survivors over the input it has read, so the output element
-// must not be larger than the first input's, and its two input buffers per block must fit shared memory.
-int pipe_rows_for(const ChainInfo& info);
-// Elements per tile, and dynamic shared memory per block of that kernel with `nbuf` buffers per input.
-long long pipe_tile_elems(const ChainInfo& info, int rows);
-long long pipe_smem_bytes(const ChainInfo& info, int rows, int nbuf);
-int pipe_block_threads(int ctrl);   // threads per block that kernel is launched with
-// The same for the streamed compaction kernel (dcb::compact_stream_body): rows per worker warp such that one slot (a
-// tile of every input) holds at most 16 KB, or 0 when the query cannot use the kernel (no Where, or an output element
+// Shape of the streamed compaction kernel (dcb::compact_stream_body): rows per worker warp such that one slot (a
+// tile of every input) holds at most 16 KB (six slots, two blocks per SM), or 0 when the query cannot use the kernel (no Where, or an output element
 // wider than the first input's, which rules out staging in place).
 int stream_rows_for(const ChainInfo& info, int warps);
 long long stream_tile_elems(const ChainInfo& info, int rows, int warps);

@@ -203,7 +203,7 @@ dcb_status dcb_set_spin_limit(dcb_ctx* ctx, uint32_t max_polls);
  * (src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:132, new KernelCache(maxEntries: 100)). */
 enum {
     DCB_OPT_COMPACT_KERNEL = 1,       /* 0 = automatic (the streamed kernel where the query allows), 1 = always the
-                                         one-tile-per-block look-back kernel, 2 = the round-based pipelined kernel */
+                                         one-tile-per-block look-back kernel                                          */
     DCB_OPT_FORCE_SCALAR = 2,         /* 1 = scalar kernel variants even for 16-byte aligned buffers                   */
     DCB_OPT_BLOCKS_PER_SM = 3,        /* cap on resident blocks per SM used to size persistent grids; 0 = what fits    */
     DCB_OPT_WITHHOLD_FIRST_COUNT = 4, /* test switch for the time-out path, driven from the host: the next compactions keep

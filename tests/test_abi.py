@@ -119,19 +119,19 @@ def test_generated_source_shape():
     assert a.splitlines()[1] != b.splitlines()[1] and a.splitlines()[1].startswith("// key:")
 
 
-def test_pipelined_compaction_kernel_is_generated_where_it_applies():
+def test_streamed_compaction_kernel_is_generated_where_it_applies():
     """The persistent, bulk-copy fed compaction kernel stages survivors over the input it has read, so it exists only
     for queries whose output element is no wider than the first input's; every compaction query keeps the
-    one-tile-per-block kernels (vector and scalar) for unaligned buffers."""
+    one-tile-per-block kernels (vector and scalar) as the route for everything else."""
     src = generate_source(np.int64, [(N.OP_WHERE, "k => (k & 0xF) == 3"), (N.OP_TOARRAY, None)])
-    assert "dcb::compact_pipe_body<dcb_chain, 256, 4, 2, 4, 1>" in src and "__launch_bounds__(288, 3) dcb_compact_pipe(" in src
+    assert "dcb::compact_stream_body<dcb_chain, 4, 8, 3, 6, " in src and "__launch_bounds__(192, 2) dcb_compact_stream(" in src
     assert "dcb_compact_vec(" in src and "dcb_compact_scalar(" in src
     src = generate_source(np.float32, [(N.OP_ZIP, "(x, y) => x * y"), (N.OP_WHERE, "v => v > 0f"), (N.OP_TOARRAY, None)], np.float32)
-    assert "dcb::compact_pipe_body<dcb_chain, 256, 2, 2, 4, 1>" in src      # two inputs: half the rows, same bytes per buffer
+    assert "dcb::compact_stream_body<dcb_chain, 4, 4, 3, 6, " in src          # two inputs: half the rows, same bytes per slot
     src = generate_source(np.int32, [(N.OP_WHERE, "x => x > 7"), (N.OP_SELECT, "x => (long)x * 3L"), (N.OP_TOARRAY, None)])
-    assert "compact_pipe_body" not in src and "dcb_compact_vec(" in src       # widening Select: no in-place staging
+    assert "compact_stream_body" not in src and "dcb_compact_vec(" in src     # widening Select: no in-place staging
     src = generate_source(np.float32, [(N.OP_WHERE, "x => x > 0.5f"), (N.OP_SUM, None)])
-    assert "compact_pipe_body" not in src and "dcb_reduce_vec(" in src
+    assert "compact_stream_body" not in src and "dcb_reduce_vec(" in src
 
 
 def test_operator_order_rules():

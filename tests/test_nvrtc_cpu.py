@@ -97,20 +97,3 @@ def test_translated_kernel_method_compiles(name):
     reg = translate_kernel_method(KERNEL_METHODS[name])
     res, log = compile_for_sm100a(reg.CudaSource)
     assert res == nvrtc.nvrtcResult.NVRTC_SUCCESS, reg.CudaSource + "\n" + log[:2000]
-
-
-@pytest.mark.parametrize("dt0,dt1,ops,body", [
-    (np.float32, None, [(N.OP_WHERE, "x => x > 0.5f"), (N.OP_SELECT, "x => x * x + 3f"), (N.OP_TOARRAY, None)], "256, 4, 2, 4"),
-    (np.float32, np.float32, [(N.OP_ZIP, "(a, b) => a * b"), (N.OP_WHERE, "v => v > 0f"), (N.OP_TOARRAY, None)], "256, 2, 2, 4"),
-], ids=["f32", "zip"])
-def test_experimental_compaction_variant_compiles(dt0, dt1, ops, body):
-    """The variant whose offsets warp stays outside the round's barrier (pipe setting 2) is not built by default; keep it
-    compiling so that it can be switched on for a measurement."""
-    with open(HEADER) as f:
-        header = f.read()
-    src = generate_source(dt0, ops, dt1)
-    default_call = f"dcb::compact_pipe_body<dcb_chain, {body}, 1>("
-    assert default_call in src
-    src = src.replace(default_call, f"dcb::compact_pipe_free_body<dcb_chain, {body}>(")
-    res, log = compile_for_sm100a(src.replace('#include "dcb_kernels.cuh"', header))
-    assert res == nvrtc.nvrtcResult.NVRTC_SUCCESS, log[:3000]
