@@ -730,7 +730,46 @@ def main() -> int:
         n_chunks = -(-n_local * 4 // (32 << 20))
         e2e = {"value": n_total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": n_total * 4,
                "d2h_bytes_per_step": 128 * n_chunks * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "wall_ms_per_step": wall_ms / e2e_steps, "host_placement": numa_note,
-               "note": "pinned host shard -> 32 MiB chunked H2D overlapped with per-chunk kernels -> records D2H; PCIe-bound"}
+               "note": "pinned host shard -> 32 MiB chunks through a three-slot staging ring, H2D overlapped with per-chunk kernels -> records D2H; PCIe-bound"}
+        if not args.no_extras:
+            # The ToArray half end to end: host shard in, compacted host array out (two-slot output ring, D2H of each chunk's
+            # survivors one chunk behind the kernels, overlapping the uploads).
+            pipe_arr = q.pipeline(N.OP_TOARRAY)
+            out_pinned = acc.Memory.AllocatePinned(n_local, np.float32)
+            ra = N.Result()
+
+            def e2e_arr_step():
+                N.check(N.lib().dcb_pipeline_run_host(pipe_arr.handle, C.c_void_p(pinned.ptr), None, n_local, C.c_void_p(out_pinned.ptr), n_local,
+                                                      C.byref(ra)), acc.handle)
+                return int(ra.count)
+
+            e2e_arr_step()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            arr_steps = max(2, min(e2e_steps, 4))
+            for _ in range(arr_steps):
+                cnt_local = e2e_arr_step()
+            a1.record()
+            barrier()
+            ta = torch.tensor([a0.elapsed_time(a1) / arr_steps, float(cnt_local)], dtype=torch.float64, device=device)
+            tmax = ta.clone()
+            if world > 1:
+                dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                dist.all_reduce(ta, op=dist.ReduceOp.SUM)
+            arr_ok = None
+            if not args.no_check:
+                import oracle
+                want_arr = oracle.c_oracle().where_gt_select_sq_add(pinned.array, THRESHOLD, ADDEND)
+                arr_ok = bool(cnt_local == want_arr.size and np.array_equal(out_pinned.array[:cnt_local].view(np.uint32), want_arr.view(np.uint32)))
+                okt = torch.tensor([1 if arr_ok else 0], dtype=torch.int32, device=device)
+                if world > 1:
+                    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+                arr_ok = bool(int(okt[0]))
+            e2e["toarray"] = {"value": n_total / (float(tmax[0]) * 1e-3), "unit": UNIT, "ms_per_step": float(tmax[0]), "steps": arr_steps,
+                              "h2d_bytes_per_step": n_total * 4, "d2h_bytes_per_step": int(float(ta[1])) * 4 + 128 * n_chunks * world,
+                              "parity": arr_ok}
+            out_pinned.Dispose()
 
     # ---- config 5's ToArray half and the other reductions, through the same exchange; the NCCL all-reduce beside it
     toarray = reductions_ok = reductions_detail = nccl_arm = None

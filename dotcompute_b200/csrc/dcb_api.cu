@@ -81,10 +81,16 @@ struct dcb_ctx {
     int opt_cache_max = 100;               // DCB_OPT_CACHE_MAX_ENTRIES (the reference: new KernelCache(maxEntries: 100))
     uint64_t cache_clock = 0;              // use counter behind the cache's least-recently-used order
     std::mutex host_mu;                    // serialises dcb_pipeline_run_host: the staging buffers belong to the context
-    void* stage_in[2] = {nullptr, nullptr};
-    size_t stage_in_cap[2] = {0, 0};
-    void* stage_out = nullptr;
-    size_t stage_out_cap = 0;
+    // Staging ring of the host path: kRingIn chunk buffers per input, kRingOut chunk buffers for the output, with the
+    // events that hand a slot from the copy engine to the kernel and back. Allocated on first use, kept until shutdown.
+    void* ring_in[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};
+    void* ring_out[2] = {nullptr, nullptr};
+    size_t ring_in_bytes = 0, ring_out_bytes = 0;
+    cudaEvent_t ev_copied[3] = {nullptr, nullptr, nullptr};    // H2D of the chunk in input slot i has landed
+    cudaEvent_t ev_computed[3] = {nullptr, nullptr, nullptr};  // the kernel that read input slot i is done
+    cudaEvent_t ev_filled[2] = {nullptr, nullptr};             // the kernel that wrote output slot i is done
+    cudaEvent_t ev_drained[2] = {nullptr, nullptr};            // D2H of output slot i is done
+    cudaEvent_t ev_record[2] = {nullptr, nullptr};             // the record of the chunk in output slot i is on the host
     void* host_recs = nullptr;             // pinned: per-chunk records of the host path (grow-only)
     void* dev_recs = nullptr;
     size_t recs_cap = 0;                   // in records
@@ -458,8 +464,14 @@ extern "C" dcb_status dcb_shutdown(dcb_ctx* ctx) {
     for (void* p : ctx->peer_opened) cudaIpcCloseMemHandle(p);
     if (ctx->peer_area) cudaFree(ctx->peer_area);
     if (ctx->peer_state) cudaFree(ctx->peer_state);
-    for (int i = 0; i < 2; ++i) if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
-    if (ctx->stage_out) cudaFree(ctx->stage_out);
+    for (int i = 0; i < 2; ++i) for (int j = 0; j < 3; ++j) if (ctx->ring_in[i][j]) cudaFree(ctx->ring_in[i][j]);
+    for (int i = 0; i < 2; ++i) if (ctx->ring_out[i]) cudaFree(ctx->ring_out[i]);
+    for (int i = 0; i < 3; ++i) { if (ctx->ev_copied[i]) cudaEventDestroy(ctx->ev_copied[i]); if (ctx->ev_computed[i]) cudaEventDestroy(ctx->ev_computed[i]); }
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->ev_filled[i]) cudaEventDestroy(ctx->ev_filled[i]);
+        if (ctx->ev_drained[i]) cudaEventDestroy(ctx->ev_drained[i]);
+        if (ctx->ev_record[i]) cudaEventDestroy(ctx->ev_record[i]);
+    }
     if (ctx->dev_recs) cudaFree(ctx->dev_recs);
     if (ctx->host_recs) cudaFreeHost(ctx->host_recs);
     cudaStreamDestroy(ctx->own_stream);
@@ -889,7 +901,7 @@ dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cuda
 }
 
 dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
-                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches) {
+                          void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, uint32_t run_flags = 0) {
     dcb_ctx* ctx = p->ctx;
     const dcbt::ChainInfo& I = p->info;
     NEED(ctx, n >= 0, "element count is negative");
@@ -969,8 +981,9 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         if (stream_ok) {
             // Persistent blocks, as many as fit the GPU at once (fewer for a small input); tile ids come from counters[0].
             unsigned int* counters = sc.words + 32;
+            unsigned int kernel_flags = (run_flags & DCB_RUN_TAKE) ? (unsigned int)dcb::STREAM_TAKE : 0u;
             void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.cdesc, (void*)&epoch, (void*)&spin,
-                             (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters, (void*)&head};
+                             (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters, (void*)&head, (void*)&kernel_flags};
             const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_stream));
             CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps)), pargs,
                                      (size_t)dcbt::stream_smem_bytes(I, p->stream_rows, p->stream_warps, p->stream_nbuf), s));
@@ -1023,6 +1036,11 @@ extern "C" dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, co
             return DCB_OK;
         case DCB_OP_COUNT:
             r->i64 = d->count; r->u64 = (uint64_t)d->count;
+            return DCB_OK;
+        case DCB_OP_FIRST_INDEX:
+        case DCB_OP_LAST_INDEX:
+            r->i64 = d->count == 0 ? -1 : (terminal == DCB_OP_FIRST_INDEX ? d->imin : d->imax);
+            r->u64 = (uint64_t)r->i64;
             return DCB_OK;
         case DCB_OP_SUM:
         case DCB_OP_AVERAGE: {
@@ -1078,6 +1096,19 @@ extern "C" dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, c
 
 extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,
                                        int64_t out_cap, dcb_result* result, void* stream) {
+    return dcb_pipeline_run_ex(p, in0, in1, n, out, out_cap, 0u, result, stream);
+}
+
+// Take(k): more survivors than k is what was asked for, not an error; the count reported is what was written.
+static dcb_status finish_take(dcb_status st, int64_t cap, dcb_result* result) {
+    if (st == DCB_ERR_OUTPUT_TOO_SMALL) st = DCB_OK;
+    if (st == DCB_OK && result->count > cap) result->count = cap;
+    result->flags &= ~(uint32_t)DCB_RES_TRUNCATED;
+    return st;
+}
+
+extern "C" dcb_status dcb_pipeline_run_ex(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,
+                                          int64_t out_cap, uint32_t flags, dcb_result* result, void* stream) {
     if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
     dcb_ctx* ctx = p->ctx;
     dcb_status st = use(ctx);
@@ -1089,8 +1120,10 @@ extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const v
     std::lock_guard<std::mutex> run_guard(p->run_mu);   // this pipeline's record, host mirror and events are in use until we return
     CU(ctx, cudaEventRecord(p->ev0, s));
     uint32_t launches = 0;
-    if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches))) return st;
-    if (ctx->peers.world > 1 && p->info.terminal != DCB_OP_TOARRAY) {   // blocking call: exchange on the same stream
+    const bool take = (flags & DCB_RUN_TAKE) != 0 && p->info.terminal == DCB_OP_TOARRAY && p->info.has_filter;
+    if ((st = run_async_impl(p, in0, in1, n, out, out_cap, nullptr, nullptr, s, &launches, take ? DCB_RUN_TAKE : 0u))) return st;
+    const bool index_terminal = p->info.terminal == DCB_OP_FIRST_INDEX || p->info.terminal == DCB_OP_LAST_INDEX;   // indices are local to a shard
+    if (ctx->peers.world > 1 && p->info.terminal != DCB_OP_TOARRAY && !index_terminal) {   // blocking call: exchange on the same stream
         if ((st = dcb_peer_exchange_async(ctx, p->d_result, p->info.out_type, (void*)s))) return st;
         launches += 1;
     }
@@ -1101,22 +1134,27 @@ extern "C" dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const v
     CU(ctx, cudaEventElapsedTime(&ms, p->ev0, p->ev1));
     result->launches = launches; result->kernel_ms = ms; result->total_ms = ms;
     if (plain_map) { result->count = n; return DCB_OK; }
-    return dcb_result_finalize(p, p->h_record, result);
+    st = dcb_result_finalize(p, p->h_record, result);
+    return take ? finish_take(st, out_cap, result) : st;
 }
 
 namespace {
 
-dcb_status grow(dcb_ctx* ctx, void** buf, size_t* cap, size_t need) {
-    if (need <= *cap) return DCB_OK;
-    if (*buf) { CU(ctx, cudaDeviceSynchronize()); CU(ctx, cudaFree(*buf)); *buf = nullptr; *cap = 0; }
-    CU(ctx, cudaMalloc(buf, need));
-    *cap = need;
-    return DCB_OK;
-}
-
 // Fold the per-chunk records of a chunked reduction in chunk order (deterministic).
-void fold_records(const dcbt::ChainInfo& I, const dcb::DeviceResult* recs, int n, dcb::DeviceResult* out) {
+void fold_records(const dcbt::ChainInfo& I, const dcb::DeviceResult* recs, int n, int64_t chunk, dcb::DeviceResult* out) {
     *out = recs[0];
+    if (I.terminal == DCB_OP_FIRST_INDEX || I.terminal == DCB_OP_LAST_INDEX) {
+        // a chunk reports indices relative to its own start
+        out->imin = 0x7fffffffffffffffLL; out->imax = -1; out->count = 0;
+        for (int i = 0; i < n; ++i) {
+            if (recs[i].count == 0) continue;
+            out->count += recs[i].count;
+            out->imin = std::min<int64_t>(out->imin, recs[i].imin + (int64_t)i * chunk);
+            out->imax = std::max<int64_t>(out->imax, recs[i].imax + (int64_t)i * chunk);
+        }
+        out->count_f = (double)out->count;
+        return;
+    }
     for (int i = 1; i < n; ++i) {
         const dcb::DeviceResult& r = recs[i];
         out->fsum += r.fsum;
@@ -1142,6 +1180,11 @@ void fold_records(const dcbt::ChainInfo& I, const dcb::DeviceResult* recs, int n
 
 extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
                                             void* host_out, int64_t host_out_cap, dcb_result* result) {
+    return dcb_pipeline_run_host_ex(p, host_in0, host_in1, n, host_out, host_out_cap, 0u, result);
+}
+
+extern "C" dcb_status dcb_pipeline_run_host_ex(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
+                                               void* host_out, int64_t host_out_cap, uint32_t flags, dcb_result* result) {
     if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
     dcb_ctx* ctx = p->ctx;
     dcb_status st = use(ctx);
@@ -1156,6 +1199,7 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     std::lock_guard<std::mutex> run_guard(p->run_mu);
     const bool to_array = I.terminal == DCB_OP_TOARRAY;
     const bool compaction = to_array && I.has_filter;
+    const bool take = (flags & DCB_RUN_TAKE) != 0 && compaction;
     const size_t sz0 = (size_t)dcbt::type_size(I.in0), sz1 = I.n_in == 2 ? (size_t)dcbt::type_size(I.in1) : 0;
     const size_t szo = (size_t)dcbt::type_size(I.out_type);
     if (to_array) {
@@ -1163,12 +1207,36 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
         if (!I.has_filter) NEED(ctx, host_out_cap >= n, "output capacity below the element count");
     }
     // Chunks are whole tiles of the widest kernel shape so that every chunk but the last starts 16-byte aligned.
-    int64_t chunk = (int64_t)(kHostChunkBytes / std::max(sz0, sz1));
+    int64_t chunk = (int64_t)(kHostChunkBytes / std::max(std::max(sz0, sz1), szo));
     chunk = std::max<int64_t>(chunk - chunk % 16384, 16384);
     const int n_chunks = (int)std::max<int64_t>(1, (n + chunk - 1) / chunk);
-    if ((st = grow(ctx, &ctx->stage_in[0], &ctx->stage_in_cap[0], std::max<size_t>((size_t)n * sz0, 256)))) return st;
-    if (I.n_in == 2 && (st = grow(ctx, &ctx->stage_in[1], &ctx->stage_in_cap[1], std::max<size_t>((size_t)n * sz1, 256)))) return st;
-    if (to_array && (st = grow(ctx, &ctx->stage_out, &ctx->stage_out_cap, std::max<size_t>((size_t)n * szo, 256)))) return st;
+    constexpr int kRingIn = 3, kRingOut = 2;
+    // The ring: whatever the size of the query, the device holds three chunks of every input and two of the output.
+    {
+        const size_t in_bytes = (size_t)chunk * std::max(sz0, sz1), out_bytes = (size_t)chunk * szo;
+        if (ctx->ring_in_bytes < in_bytes || (I.n_in == 2 && !ctx->ring_in[1][0])) {
+            CU(ctx, cudaDeviceSynchronize());
+            for (int i = 0; i < 2; ++i) for (int j = 0; j < kRingIn; ++j) if (ctx->ring_in[i][j]) { cudaFree(ctx->ring_in[i][j]); ctx->ring_in[i][j] = nullptr; }
+            for (int i = 0; i < I.n_in; ++i) for (int j = 0; j < kRingIn; ++j) CU(ctx, cudaMalloc(&ctx->ring_in[i][j], std::max(in_bytes, ctx->ring_in_bytes)));
+            ctx->ring_in_bytes = std::max(in_bytes, ctx->ring_in_bytes);
+        }
+        if (to_array && ctx->ring_out_bytes < out_bytes) {
+            CU(ctx, cudaDeviceSynchronize());
+            for (int j = 0; j < kRingOut; ++j) { if (ctx->ring_out[j]) cudaFree(ctx->ring_out[j]); ctx->ring_out[j] = nullptr; CU(ctx, cudaMalloc(&ctx->ring_out[j], out_bytes)); }
+            ctx->ring_out_bytes = out_bytes;
+        }
+        if (!ctx->ev_copied[0]) {
+            for (int j = 0; j < kRingIn; ++j) {
+                CU(ctx, cudaEventCreateWithFlags(&ctx->ev_copied[j], cudaEventDisableTiming));
+                CU(ctx, cudaEventCreateWithFlags(&ctx->ev_computed[j], cudaEventDisableTiming));
+            }
+            for (int j = 0; j < kRingOut; ++j) {
+                CU(ctx, cudaEventCreateWithFlags(&ctx->ev_filled[j], cudaEventDisableTiming));
+                CU(ctx, cudaEventCreateWithFlags(&ctx->ev_drained[j], cudaEventDisableTiming));
+                CU(ctx, cudaEventCreateWithFlags(&ctx->ev_record[j], cudaEventDisableTiming));
+            }
+        }
+    }
     // Per-chunk records: device array + pinned host mirror, kept on the context and grown when a larger input comes.
     if ((size_t)n_chunks > ctx->recs_cap) {
         CU(ctx, cudaDeviceSynchronize());
@@ -1184,78 +1252,100 @@ extern "C" dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in
     dcb::DeviceResult* h_recs = (dcb::DeviceResult*)ctx->host_recs;
 
     cudaStream_t cs = ctx->copy_stream, ks = ctx->stream, os = ctx->out_stream;
-    std::vector<cudaEvent_t> copied((size_t)n_chunks), computed((size_t)n_chunks);
-    for (int c = 0; c < n_chunks; ++c) {
-        cudaEventCreateWithFlags(&copied[c], cudaEventDisableTiming);
-        cudaEventCreateWithFlags(&computed[c], cudaEventDisableTiming);
-    }
-    auto cleanup = [&]() {
-        for (int c = 0; c < n_chunks; ++c) { cudaEventDestroy(copied[c]); cudaEventDestroy(computed[c]); }
-    };
     cudaEvent_t t0 = p->ev0, t1 = p->ev1;
     uint32_t launches = 0;
     st = DCB_OK;
+    int64_t out_written = 0, survivors = 0;    // compaction: elements copied to host_out so far / counted so far
+    int last_chunk = n_chunks - 1;             // last chunk whose kernel ran (Take may stop earlier)
+    uint64_t flags_seen = 0;
+    // Output of a compaction chunk leaves one chunk behind the kernels: its record (the survivor count) has to reach the
+    // host before the size and the destination of its copy are known.
+    auto drain_compacted = [&](int c) -> cudaError_t {
+        const int so = c % kRingOut;
+        cudaError_t e = cudaEventSynchronize(ctx->ev_record[so]);
+        if (e != cudaSuccess) return e;
+        const dcb::DeviceResult& r = h_recs[c];
+        flags_seen |= r.flags;
+        const int64_t cnt = (r.flags & dcb::FLAG_TIMEOUT) ? 0 : r.count;
+        survivors += cnt;
+        const int64_t room = std::max<int64_t>(0, host_out_cap - out_written);
+        const int64_t ncopy = std::min(cnt, room);
+        if (ncopy > 0) {
+            e = cudaMemcpyAsync((char*)host_out + (size_t)out_written * szo, ctx->ring_out[so], (size_t)ncopy * szo, cudaMemcpyDeviceToHost, os);
+            if (e != cudaSuccess) return e;
+            out_written += ncopy;
+        }
+        return cudaEventRecord(ctx->ev_drained[so], os);
+    };
     cudaError_t ce = cudaEventRecord(t0, ks);
     if (ce == cudaSuccess) ce = cudaStreamWaitEvent(cs, t0, 0);   // copies start after earlier work on the compute stream
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(os, t0, 0);
     for (int c = 0; c < n_chunks && ce == cudaSuccess && st == DCB_OK; ++c) {
-        const int64_t off = (int64_t)c * chunk, len = std::min<int64_t>(chunk, n - off);
-        if (len > 0) {
-            ce = cudaMemcpyAsync((char*)ctx->stage_in[0] + off * sz0, (const char*)host_in0 + off * sz0, (size_t)len * sz0, cudaMemcpyHostToDevice, cs);
+        const int64_t off = (int64_t)c * chunk, len = std::max<int64_t>(0, std::min<int64_t>(chunk, n - off));
+        const int si = c % kRingIn, so = c % kRingOut;
+        if (c >= kRingIn) ce = cudaStreamWaitEvent(cs, ctx->ev_computed[si], 0);   // the slot's previous chunk has been read
+        if (len > 0 && ce == cudaSuccess) {
+            ce = cudaMemcpyAsync(ctx->ring_in[0][si], (const char*)host_in0 + off * sz0, (size_t)len * sz0, cudaMemcpyHostToDevice, cs);
             if (ce == cudaSuccess && I.n_in == 2)
-                ce = cudaMemcpyAsync((char*)ctx->stage_in[1] + off * sz1, (const char*)host_in1 + off * sz1, (size_t)len * sz1, cudaMemcpyHostToDevice, cs);
+                ce = cudaMemcpyAsync(ctx->ring_in[1][si], (const char*)host_in1 + off * sz1, (size_t)len * sz1, cudaMemcpyHostToDevice, cs);
         }
-        if (ce == cudaSuccess) ce = cudaEventRecord(copied[c], cs);
-        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(ks, copied[c], 0);
+        if (ce == cudaSuccess) ce = cudaEventRecord(ctx->ev_copied[si], cs);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(ks, ctx->ev_copied[si], 0);
         if (ce != cudaSuccess) break;
-        const void* a = (const char*)ctx->stage_in[0] + off * sz0;
-        const void* b = I.n_in == 2 ? (const char*)ctx->stage_in[1] + off * sz1 : nullptr;
-        if (compaction) {
-            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), ctx->stage_out, n, d_recs + c, c ? d_recs + c - 1 : nullptr, ks, &launches);
-        } else if (to_array) {
-            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), (char*)ctx->stage_out + off * szo, len, nullptr, nullptr, ks, &launches);
-            if (st == DCB_OK && len > 0) {
-                // results of a plain map leave chunk by chunk on a third stream, overlapping the uploads
-                ce = cudaEventRecord(computed[c], ks);
-                if (ce == cudaSuccess) ce = cudaStreamWaitEvent(os, computed[c], 0);
-                if (ce == cudaSuccess)
-                    ce = cudaMemcpyAsync((char*)host_out + off * szo, (const char*)ctx->stage_out + off * szo, (size_t)len * szo, cudaMemcpyDeviceToHost, os);
+        const void* a = ctx->ring_in[0][si];
+        const void* b = I.n_in == 2 ? ctx->ring_in[1][si] : nullptr;
+        if (to_array) {
+            if (compaction && c >= 1 && (ce = drain_compacted(c - 1)) != cudaSuccess) break;
+            if (take && survivors >= host_out_cap) { last_chunk = c - 1; break; }   // Take(k) is satisfied: this chunk's kernel is not needed
+            if (c >= kRingOut && (ce = cudaStreamWaitEvent(ks, ctx->ev_drained[so], 0)) != cudaSuccess) break;   // the slot's previous output has left
+            if (compaction) {
+                st = run_async_impl(p, a, b, len, ctx->ring_out[so], chunk, d_recs + c, nullptr, ks, &launches);
+                if (st == DCB_OK) ce = cudaMemcpyAsync(h_recs + c, d_recs + c, sizeof(dcb::DeviceResult), cudaMemcpyDeviceToHost, ks);
+                if (st == DCB_OK && ce == cudaSuccess) ce = cudaEventRecord(ctx->ev_record[so], ks);
+            } else {
+                st = run_async_impl(p, a, b, len, ctx->ring_out[so], len, nullptr, nullptr, ks, &launches);
+                if (st == DCB_OK && len > 0) {
+                    // results of a plain map leave chunk by chunk on a third stream, overlapping the uploads
+                    ce = cudaEventRecord(ctx->ev_filled[so], ks);
+                    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(os, ctx->ev_filled[so], 0);
+                    if (ce == cudaSuccess)
+                        ce = cudaMemcpyAsync((char*)host_out + off * szo, ctx->ring_out[so], (size_t)len * szo, cudaMemcpyDeviceToHost, os);
+                    if (ce == cudaSuccess) ce = cudaEventRecord(ctx->ev_drained[so], os);
+                }
             }
         } else {
-            st = run_async_impl(p, a, b, std::max<int64_t>(len, 0), nullptr, 0, d_recs + c, nullptr, ks, &launches);
+            st = run_async_impl(p, a, b, len, nullptr, 0, d_recs + c, nullptr, ks, &launches);
         }
+        if (st == DCB_OK && ce == cudaSuccess) ce = cudaEventRecord(ctx->ev_computed[si], ks);
     }
-    if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
-    if (st != DCB_OK) { cudaDeviceSynchronize(); cleanup(); return st; }
+    if (ce != cudaSuccess) { cudaDeviceSynchronize(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
+    if (st != DCB_OK) { cudaDeviceSynchronize(); return st; }
     const bool plain_map = to_array && !compaction;
-    if (!plain_map) {
-        ce = cudaMemcpyAsync(h_recs, d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaMemcpyDeviceToHost, ks);
-        if (ce == cudaSuccess) ce = cudaStreamSynchronize(ks);
-        if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "reading the records back"); }
-    }
     dcb::DeviceResult total;
     memset(&total, 0, sizeof total);
     if (compaction) {
-        total = h_recs[n_chunks - 1];
-        for (int c = 0; c < n_chunks; ++c) total.flags |= h_recs[c].flags;
-        const int64_t cnt = total.count;
-        if (!(total.flags & dcb::FLAG_TIMEOUT)) {
-            if (cnt > host_out_cap) total.flags |= dcb::FLAG_TRUNCATED;
-            const int64_t ncopy = std::min<int64_t>(cnt, host_out_cap);
-            if (ncopy > 0) ce = cudaMemcpyAsync(host_out, ctx->stage_out, (size_t)ncopy * szo, cudaMemcpyDeviceToHost, ks);
-        }
+        if (last_chunk == n_chunks - 1) ce = drain_compacted(n_chunks - 1);
+        total.count = survivors; total.count_f = (double)survivors; total.local_count = survivors;
+        total.flags = flags_seen & (uint64_t)dcb::FLAG_TIMEOUT;
+        if (survivors > host_out_cap) total.flags |= dcb::FLAG_TRUNCATED;
     } else if (!plain_map) {
-        fold_records(I, h_recs, n_chunks, &total);
+        ce = cudaMemcpyAsync(h_recs, d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaMemcpyDeviceToHost, ks);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(ks);
+        if (ce != cudaSuccess) return cuda_fail(ctx, ce, "reading the records back");
+        fold_records(I, h_recs, n_chunks, chunk, &total);
     }
+    if (ce == cudaSuccess && to_array) ce = cudaStreamWaitEvent(ks, ctx->ev_drained[last_chunk % kRingOut], 0);
+    if (ce == cudaSuccess && to_array && last_chunk >= 1) ce = cudaStreamWaitEvent(ks, ctx->ev_drained[(last_chunk - 1) % kRingOut], 0);
     if (ce == cudaSuccess) ce = cudaEventRecord(t1, ks);
-    if (ce == cudaSuccess && plain_map) ce = cudaStreamSynchronize(os);
+    if (ce == cudaSuccess && to_array) ce = cudaStreamSynchronize(os);
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(ks);
-    if (ce != cudaSuccess) { cleanup(); return cuda_fail(ctx, ce, "dcb_pipeline_run_host"); }
+    if (ce != cudaSuccess) return cuda_fail(ctx, ce, "dcb_pipeline_run_host");
     float ms = 0;
     cudaEventElapsedTime(&ms, t0, t1);
-    cleanup();
     result->launches = launches; result->total_ms = ms; result->kernel_ms = 0;
     if (plain_map) { result->count = n; return DCB_OK; }
-    return dcb_result_finalize(p, &total, result);
+    st = dcb_result_finalize(p, &total, result);
+    return take ? finish_take(st, host_out_cap, result) : st;
 }
 
 // ===================================================================================== peer exchange

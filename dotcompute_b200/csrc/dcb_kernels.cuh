@@ -47,7 +47,7 @@ __device__ __forceinline__ void memcpy_bits(U& dst, const T& src) {
 }
 
 // Reduction selector bits.
-enum : int { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8 };
+enum : int { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8, RED_FIRST = 16, RED_LAST = 32 };   // FIRST / LAST: smallest / largest index of a surviving element
 
 // Flag bits in the record (low bits match DCB_RES_* of the C ABI).
 enum : u32 { FLAG_SAW_NAN = 1u, FLAG_TRUNCATED = 2u, FLAG_TIMEOUT = 4u, FLAG_OVERFLOW = 8u, FLAG_SAW_NUMBER = 16u };
@@ -169,11 +169,13 @@ struct Acc {
     i64 count;
     u32 cnt32;     // per-thread running count; folded into `count` by finish()
     T mn, mx;
+    i64 ifirst, ilast;   // RED_FIRST / RED_LAST: index of the first / last element that passed the chain
     u32 flags;
 
     __device__ __forceinline__ void finish() { count += (i64)cnt32; cnt32 = 0; }
     __device__ __forceinline__ void init() {
         fsum = 0.0; isum_lo = 0; isum_hi = 0; count = 0; cnt32 = 0; flags = 0;
+        ifirst = 0x7fffffffffffffffLL; ilast = -1;
         if constexpr (same_t<T, float>::value) { mn = __int_as_float(0x7f800000); mx = __int_as_float(0xff800000); }
         else if constexpr (same_t<T, double>::value) { mn = __longlong_as_double(0x7ff0000000000000LL); mx = __longlong_as_double(0xfff0000000000000LL); }
         else if constexpr (same_t<T, bool>::value) { mn = true; mx = false; }
@@ -183,7 +185,9 @@ struct Acc {
         else if constexpr (sizeof(T) == 4) { mn = (T)0x7fffffff; mx = (T)(-0x7fffffff - 1); }
         else { mn = (T)0x7fffffffffffffffLL; mx = (T)(-0x7fffffffffffffffLL - 1LL); }
     }
-    __device__ __forceinline__ void add(T v) {
+    __device__ __forceinline__ void add(T v, i64 idx) {
+        if constexpr ((RED & RED_FIRST) != 0) ifirst = idx < ifirst ? idx : ifirst;
+        if constexpr ((RED & RED_LAST) != 0) ilast = idx > ilast ? idx : ilast;
         if constexpr ((RED & RED_SUM) != 0) {
             if constexpr (is_fp<T>::value) {
                 fsum += (double)v;            // fp64 accumulation, as Enumerable.Sum(float) does
@@ -209,7 +213,7 @@ struct Acc {
                 if constexpr ((RED & RED_MAX) != 0) mx = v > mx ? v : mx;
             }
         }
-        if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX)) != 0) cnt32 += 1u;   // Sum alone needs no count
+        if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX | RED_FIRST | RED_LAST)) != 0) cnt32 += 1u;   // Sum alone needs no count
     }
     // Fixed-shape combine: `this` is the left (lower-index) operand.
     __device__ __forceinline__ void merge(const Acc& o) {
@@ -223,12 +227,16 @@ struct Acc {
         }
         if constexpr ((RED & RED_MIN) != 0) mn = o.mn < mn ? o.mn : mn;
         if constexpr ((RED & RED_MAX) != 0) mx = o.mx > mx ? o.mx : mx;
+        if constexpr ((RED & RED_FIRST) != 0) ifirst = o.ifirst < ifirst ? o.ifirst : ifirst;
+        if constexpr ((RED & RED_LAST) != 0) ilast = o.ilast > ilast ? o.ilast : ilast;
         flags |= o.flags;
         count += o.count + (i64)o.cnt32;
     }
     __device__ __forceinline__ Acc shuffled(int lane_mask) const {
         Acc r;
-        r.fsum = 0.0; r.isum_lo = 0; r.isum_hi = 0; r.mn = mn; r.mx = mx; r.cnt32 = 0;
+        r.fsum = 0.0; r.isum_lo = 0; r.isum_hi = 0; r.mn = mn; r.mx = mx; r.cnt32 = 0; r.ifirst = ifirst; r.ilast = ilast;
+        if constexpr ((RED & RED_FIRST) != 0) r.ifirst = __shfl_xor_sync(0xffffffffu, ifirst, lane_mask);
+        if constexpr ((RED & RED_LAST) != 0) r.ilast = __shfl_xor_sync(0xffffffffu, ilast, lane_mask);
         if constexpr ((RED & RED_SUM) != 0) {
             if constexpr (is_fp<T>::value) r.fsum = __shfl_xor_sync(0xffffffffu, fsum, lane_mask);
             else {
@@ -256,7 +264,8 @@ struct Acc {
     __device__ __forceinline__ void to_partial(Partial& p) const {
         p.fsum = fsum; p.isum_lo = isum_lo; p.isum_hi = isum_hi; p.count = count + (i64)cnt32; p.flags = flags;
         p.pad0 = 0; p.pad1 = 0;
-        if constexpr (is_fp<T>::value) { p.mn_bits = __double_as_longlong((double)mn); p.mx_bits = __double_as_longlong((double)mx); }
+        if constexpr ((RED & (RED_FIRST | RED_LAST)) != 0) { p.mn_bits = ifirst; p.mx_bits = ilast; }   // index reductions use the Min / Max slots
+        else if constexpr (is_fp<T>::value) { p.mn_bits = __double_as_longlong((double)mn); p.mx_bits = __double_as_longlong((double)mx); }
         else { p.mn_bits = (i64)mn; p.mx_bits = (i64)mx; }
     }
     // Read from a block's slot only what this reduction accumulates (the slot was written by another block: via L2).
@@ -265,7 +274,9 @@ struct Acc {
             if constexpr (is_fp<T>::value) fsum = __ldcg(&p->fsum);
             else { isum_lo = __ldcg(&p->isum_lo); if constexpr (sizeof(T) == 8) isum_hi = __ldcg(&p->isum_hi); }
         }
-        if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX)) != 0) count = __ldcg(&p->count);
+        if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX | RED_FIRST | RED_LAST)) != 0) count = __ldcg(&p->count);
+        if constexpr ((RED & RED_FIRST) != 0) ifirst = __ldcg(&p->mn_bits);
+        if constexpr ((RED & RED_LAST) != 0) ilast = __ldcg(&p->mx_bits);
         if constexpr ((RED & RED_MIN) != 0) {
             const i64 b = __ldcg(&p->mn_bits);
             if constexpr (is_fp<T>::value) mn = (T)__longlong_as_double(b); else mn = (T)b;
@@ -278,7 +289,9 @@ struct Acc {
     }
     __device__ __forceinline__ void from_partial(const Partial& p) {
         fsum = p.fsum; isum_lo = p.isum_lo; isum_hi = p.isum_hi; count = p.count; cnt32 = 0; flags = p.flags;
-        if constexpr (is_fp<T>::value) { mn = (T)__longlong_as_double(p.mn_bits); mx = (T)__longlong_as_double(p.mx_bits); }
+        ifirst = 0x7fffffffffffffffLL; ilast = -1;
+        if constexpr ((RED & (RED_FIRST | RED_LAST)) != 0) { ifirst = p.mn_bits; ilast = p.mx_bits; mn = T(); mx = T(); }
+        else if constexpr (is_fp<T>::value) { mn = (T)__longlong_as_double(p.mn_bits); mx = (T)__longlong_as_double(p.mx_bits); }
         else { mn = (T)p.mn_bits; mx = (T)p.mx_bits; }
     }
 };
@@ -399,7 +412,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
                 O o; bool keep;
                 if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
                 else keep = C::apply(a[u].e[k], B(), o);
-                if (keep) acc.add(o);
+                if (keep) acc.add(o, (base + (i64)u * BLOCK) * E + k);
             }
         }
     }
@@ -426,7 +439,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
                     O o; bool keep;
                     if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
                     else keep = C::apply(a[u].e[k], B(), o);
-                    if (keep) acc.add(o);
+                    if (keep) acc.add(o, it * E + k);
                 }
             }
         }
@@ -435,7 +448,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     for (i64 i = nitems * E + gtid; i < n; i += gsize) {   // the last n % E elements
         O o; bool keep;
         if constexpr (C::n_in == 2) keep = C::apply(in0[i], in1[i], o); else keep = C::apply(in0[i], B(), o);
-        if (keep) acc.add(o);
+        if (keep) acc.add(o, i);
     }
 
     acc = block_reduce<O, RED, BLOCK>(acc, s_part);
@@ -470,7 +483,8 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         res->fsum = p.fsum; res->count_f = (double)p.count;
         res->isum_lo = (i64)p.isum_lo; res->isum_hi = (sizeof(O) == 8) ? p.isum_hi : ((i64)p.isum_lo < 0 ? -1 : 0);
         res->count = p.count;
-        if constexpr (is_fp<O>::value) { res->fmin = __longlong_as_double(p.mn_bits); res->fmax = __longlong_as_double(p.mx_bits); res->imin = 0; res->imax = 0; }
+        if constexpr ((RED & (RED_FIRST | RED_LAST)) != 0) { res->fmin = 0; res->fmax = 0; res->imin = p.mn_bits; res->imax = p.mx_bits; }
+        else if constexpr (is_fp<O>::value) { res->fmin = __longlong_as_double(p.mn_bits); res->fmax = __longlong_as_double(p.mx_bits); res->imin = 0; res->imax = 0; }
         else { res->fmin = 0; res->fmax = 0; res->imin = p.mn_bits; res->imax = p.mx_bits; }
         res->flags = p.flags;
         res->offset = 0; res->local_count = p.count;
@@ -910,8 +924,11 @@ __device__ __forceinline__ i64 compact_range_sum(const u64* __restrict__ desc, i
 //
 // `counters[0]` hands out tile ids, `counters[1]` counts finished blocks; both are zero at launch and the last block
 // to finish zeroes them again. `abort_flag[1] == epoch` withholds the count of tile 0 (a host-driven test of the time-out
-// path: every offset then waits for a count that never comes). Launch with (WARPS + 2) * 32 threads and
-// NBUF * tile bytes of dynamic shared memory for each input.
+// path: every offset then waits for a count that never comes). With STREAM_TAKE in `run_flags` (Take(k) after a Where,
+// k = out_cap) the scan ends early: the offsets warp that finds a tile starting at or beyond k raises abort_flag[2] to
+// the epoch and leaves a record with a count >= k; loaders look at that word before they draw an id and stop drawing.
+// Ids already drawn are finished as usual (their writes are clipped at k), so nothing waits for a count that never comes.
+// Launch with (WARPS + 2) * 32 threads and NBUF * tile bytes of dynamic shared memory for each input.
 // Limit of one wait on a block's own barrier or bulk copy, in SM clock cycles (about two seconds). It is measured with
 // the SM's cycle counter, which costs a few cycles to read; the nanosecond timer shared by the whole GPU takes microseconds
 // per read, which a wait on the data path cannot afford.
@@ -1070,6 +1087,7 @@ __device__ __forceinline__ i64 cdesc_finish(const u32* __restrict__ cdesc, i64 l
     return total;
 }
 
+enum : u32 { STREAM_TAKE = 1u };
 __device__ __forceinline__ void l2_prefetch_bulk(const void* src_global, u32 bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
 }
@@ -1079,7 +1097,8 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                                                     i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
                                                     u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
                                                     const DeviceResult* __restrict__ prev, DeviceResult* __restrict__ res,
-                                                    unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters, u32 head) {
+                                                    unsigned int* __restrict__ abort_flag, unsigned int* __restrict__ counters, u32 head,
+                                                    u32 run_flags) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
     static_assert(LAG >= 2 && NBUF >= LAG + 2 && NBUF <= 16, "an offset is ready two rounds after its tile was ranked; NBUF = LAG + 1 + tiles on their way in");
@@ -1161,8 +1180,11 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                     if (!wait(&s_ranked[(int)(rr % NBUF)], (u32)((rr / NBUF) & 1), true)) { *dead = 1; break; }
                 }
                 // The id is asked for before the wait for the slot: the counter's round trip overlaps that wait.
-                i64 t = (i64)atomicAdd(counters, 1u);
-                if (t > num_tiles) t = num_tiles;
+                i64 t = num_tiles;
+                if (!((run_flags & STREAM_TAKE) && *(volatile unsigned int*)(abort_flag + 2) == epoch)) {   // Take(k) already satisfied?
+                    t = (i64)atomicAdd(counters, 1u);
+                    if (t > num_tiles) t = num_tiles;
+                }
                 { DCB_STAT_BEGIN;
                   if (r >= NBUF && !wait(&s_empty[st], ph ^ 1u, true)) { *dead = 1; break; }
                   DCB_STAT_END(3, 0); DCB_STAT_ADD(3, 1, 1); }
@@ -1240,6 +1262,16 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                             res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
                             res->offset = 0; res->local_count = total_all;
                             res->flags = total_all > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
+                        }
+                        if (!failed && (run_flags & STREAM_TAKE) && base_prev + exclusive >= out_cap &&
+                            *(volatile unsigned int*)(abort_flag + 2) != epoch) {
+                            // Take(k): everything asked for lies in tiles before this one. Tell the loaders, and leave a
+                            // record in case the array's last tile is never reached.
+                            *(volatile unsigned int*)(abort_flag + 2) = epoch;
+                            const i64 seen = base_prev + exclusive + c_total;
+                            res->count = seen; res->count_f = (double)seen; res->local_count = seen; res->offset = 0;
+                            res->fsum = 0; res->isum_lo = 0; res->isum_hi = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+                            res->flags = seen > out_cap ? (u64)FLAG_TRUNCATED : 0ull;
                         }
                         if (failed) { *dead = 1; atomicExch(abort_flag, epoch); }
                         mbar_arrive(&s_offs[c_st]);           // the workers read s_off after this

@@ -13,9 +13,10 @@
 namespace dcbt {
 
 // Operator and status codes shared with dcb200.h (kept numeric here so this file has no CUDA dependency).
-enum { OP_SELECT = 1, OP_WHERE = 2, OP_ZIP = 3, OP_TOARRAY = 16, OP_SUM = 17, OP_MIN = 18, OP_MAX = 19, OP_AVERAGE = 20, OP_COUNT = 21 };
+enum { OP_SELECT = 1, OP_WHERE = 2, OP_ZIP = 3, OP_TOARRAY = 16, OP_SUM = 17, OP_MIN = 18, OP_MAX = 19, OP_AVERAGE = 20, OP_COUNT = 21,
+       OP_FIRST_INDEX = 22, OP_LAST_INDEX = 23 };
 enum { ST_INVALID_ARGUMENT = 301, ST_NOT_SUPPORTED = 302 };
-enum { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8 };
+enum { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8, RED_FIRST = 16, RED_LAST = 32 };
 
 static const char* kCuda[] = {"void", "signed char", "unsigned char", "short", "unsigned short", "int", "unsigned int",
                               "long long", "unsigned long long", "float", "double", "bool"};
@@ -949,6 +950,8 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
     switch (term.kind) {
         case OP_TOARRAY: info->result_type = cur; info->red_mask = 0; key += "|ToArray"; break;
         case OP_COUNT: info->result_type = T_I64; info->red_mask = RED_COUNT; key += "|Count"; break;
+        case OP_FIRST_INDEX: info->result_type = T_I64; info->red_mask = RED_FIRST; key += "|FirstIndex"; break;
+        case OP_LAST_INDEX: info->result_type = T_I64; info->red_mask = RED_LAST; key += "|LastIndex"; break;
         case OP_MIN: case OP_MAX:
             if (!is_numeric(cur)) { *err = "Min/Max need a numeric element type"; *status = ST_NOT_SUPPORTED; return false; }
             info->result_type = cur; info->red_mask = term.kind == OP_MIN ? RED_MIN : RED_MAX; key += term.kind == OP_MIN ? "|Min" : "|Max"; break;
@@ -962,7 +965,7 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
             if (term.kind == OP_SUM) { info->result_type = cur; key += "|Sum"; }
             else { info->result_type = (cur == T_F32) ? T_F32 : T_F64; key += "|Average"; }
             break;
-        default: *err = "the last operator must be ToArray, Sum, Min, Max, Average or Count"; return false;
+        default: *err = "the last operator must be ToArray, Sum, Min, Max, Average, Count, FirstIndex or LastIndex"; *status = ST_NOT_SUPPORTED; return false;
     }
     std::string s;
     s += "struct dcb_chain@ {\n";
@@ -1049,11 +1052,11 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                 s += "extern \"C\" __global__ void __launch_bounds__(" + sbounds + ") dcb_compact_stream" + suffix +
                      "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
                      "unsigned int epoch, unsigned int spin_limit, long long num_tiles, const void* prev, void* res, unsigned int* abort_flag, "
-                     "unsigned int* counters, unsigned int head) {\n"
+                     "unsigned int* counters, unsigned int head, unsigned int run_flags) {\n"
                      "    dcb::compact_stream_body<" + C + ", " + std::to_string(tuning.stream_warps) + ", " + std::to_string(srow) + ", " +
                      std::to_string(tuning.stream_lag) + ", " + std::to_string(tuning.stream_nbuf) + ", " + std::to_string(tuning.stream_depth) + ", " +
                      std::to_string(tuning.stream_ahead_mb) + " << 20, " + std::to_string(tuning.stream_draw_ahead) + ">(" + cast_in() + ", n, (" + C +
-                     "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters, head);\n}\n";
+                     "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters, head, run_flags);\n}\n";
             }
         } else {
             // Keep the register count where 6 (one input) or 4 (Zip) blocks share an SM: measured as fast as 8 blocks, and

@@ -211,9 +211,9 @@ class ComputeQueryable:
             if to_array:
                 dbuf = acc.Memory.AllocateAsync(max(cap, 1), pipe.out_dtype)
                 try:
-                    st = N.lib().dcb_pipeline_run(pipe.handle, in0, in1, n if pipe.has_filter else cap, C.c_void_p(dbuf.GetDeviceMemory()), cap, C.byref(res), None)
-                    if not (st == 202 and self._take is not None):      # more survivors than Take asked for is not an error
-                        N.check(st, acc.handle)
+                    flags = N.RUN_TAKE if (self._take is not None and pipe.has_filter) else 0   # Take(k): stop scanning once k are known
+                    N.check(N.lib().dcb_pipeline_run_ex(pipe.handle, in0, in1, n if pipe.has_filter else cap, C.c_void_p(dbuf.GetDeviceMemory()), cap,
+                                                        flags, C.byref(res), None), acc.handle)
                     got = min(int(res.count), cap)
                     out = dbuf.CopyToAsync(count=got) if got else np.empty(0, pipe.out_dtype)
                 finally:
@@ -227,9 +227,9 @@ class ComputeQueryable:
                 a1, p1 = self._host_ptr(self._second, n)
             if to_array:
                 out = np.empty(cap, dtype=pipe.out_dtype)
-                st = N.lib().dcb_pipeline_run_host(pipe.handle, p0, p1, n if pipe.has_filter else cap, out.ctypes.data_as(C.c_void_p), cap, C.byref(res))
-                if not (st == 202 and self._take is not None):
-                    N.check(st, acc.handle)
+                flags = N.RUN_TAKE if (self._take is not None and pipe.has_filter) else 0
+                N.check(N.lib().dcb_pipeline_run_host_ex(pipe.handle, p0, p1, n if pipe.has_filter else cap, out.ctypes.data_as(C.c_void_p), cap,
+                                                         flags, C.byref(res)), acc.handle)
                 got = min(int(res.count), cap)
                 out = out[:got]
                 if out.base is not None and got < cap:
@@ -274,12 +274,55 @@ class ComputeQueryable:
             raise errors.ArgumentNullException("type_name")
         return self.Select(f"x => ({type_name})x")
 
+    def _has_where(self) -> bool:
+        return any(kind == N.OP_WHERE for kind, _ in self._ops)
+
+    def _sliced(self, offset: int, length: int) -> "ComputeQueryable":
+        """The same Select / Zip chain over elements [offset, offset + length) of the source(s). Only valid while no Where
+        precedes: a map sends element i of the source to element i of the result."""
+        second = _slice(self._second, offset, length) if self._second is not None else None
+        return ComputeQueryable(_slice(self._source, offset, length), self._acc, self._ops, second, self._force_jit)
+
+    def _materialized(self) -> "ComputeQueryable":
+        """Runs the query so far and continues over its result (for operators that need positions in a filtered sequence)."""
+        return ComputeQueryable(self.ToArray(), self._acc, (), None, self._force_jit)
+
+    def _index_of(self, terminal: int) -> int:
+        """FirstIndex / LastIndex: position in the source of the first / last element that passes every Where (-1: none)."""
+        if self._take is not None:
+            raise errors.NotSupportedException("an index query after Take is not fused; materialise with ToArray first")
+        if self._length() == 0:
+            return -1
+        _pipe, res, _ = self._run(terminal)
+        return int(res.i64)
+
     def Skip(self, count: int) -> "ComputeQueryable":
-        if self._ops:
-            raise errors.NotSupportedException("Skip after Select/Where is not fused; materialise with ToArray first")
-        n = self._length()
+        q = self._materialized() if (self._has_where() or self._take is not None) else self
+        n = q._length()
         k = min(max(int(count), 0), n)
-        return ComputeQueryable(_slice(self._source, k, n - k), self._acc, (), None, self._force_jit)
+        return q._sliced(k, n - k)
+
+    def TakeWhile(self, predicate: str) -> "ComputeQueryable":
+        """Elements up to (not including) the first one that fails `predicate`. One fused pass finds that position (a Min over
+        the indices of failing elements, DCB_OP_FIRST_INDEX); what follows runs over the source cut there. The reference's
+        visitor lists the operator (ExpressionTreeVisitor.cs:248-249, 263-265); its scan kernel is single-block
+        (CudaKernelGenerator.cs:499-576)."""
+        if predicate is None:
+            raise errors.ArgumentNullException("predicate")
+        q = self._materialized() if (self._has_where() or self._take is not None) else self
+        head, body = _split_lambda(predicate)
+        stop = q.Where(f"{head} => !({body})")._index_of(N.OP_FIRST_INDEX)
+        return q if stop < 0 else q._sliced(0, stop)
+
+    def SkipWhile(self, predicate: str) -> "ComputeQueryable":
+        """Elements from the first one that fails `predicate` on (that one included)."""
+        if predicate is None:
+            raise errors.ArgumentNullException("predicate")
+        q = self._materialized() if (self._has_where() or self._take is not None) else self
+        head, body = _split_lambda(predicate)
+        n = q._length()
+        start = q.Where(f"{head} => !({body})")._index_of(N.OP_FIRST_INDEX)
+        return q._sliced(n, 0) if start < 0 else q._sliced(start, n - start)
 
     def Take(self, count: int):
         n = self._length()
@@ -353,6 +396,26 @@ class ComputeQueryable:
         got = q.Take(1).ToArray()
         return got[0] if got.size else got.dtype.type(0)
 
+    def _last(self, predicate, default: bool):
+        q = self.Where(predicate) if predicate is not None else self
+        if q._take is not None:
+            q = q._materialized()
+        idx = q._index_of(N.OP_LAST_INDEX) if q._has_where() else q._length() - 1
+        maps = ComputeQueryable(q._source, q._acc, tuple(op for op in q._ops if op[0] != N.OP_WHERE), q._second, q._force_jit)
+        if idx < 0:
+            if default:
+                return maps._compile(N.OP_TOARRAY).out_dtype.type(0)
+            raise errors.InvalidOperationException("Sequence contains no " + ("matching element" if predicate else "elements"))
+        return maps._sliced(idx, 1).ToArray()[0]          # the Selects of the chain applied to that one element
+
+    def Last(self, predicate: str | None = None):
+        """Last element (that satisfies `predicate`): one fused pass finds its position (a Max over the indices of surviving
+        elements, DCB_OP_LAST_INDEX), then the chain's Selects run on that single element."""
+        return self._last(predicate, False)
+
+    def LastOrDefault(self, predicate: str | None = None):
+        return self._last(predicate, True)
+
     def ElementAt(self, index: int):
         if index < 0:
             raise errors.ArgumentException("index must not be negative")
@@ -374,21 +437,6 @@ class ComputeQueryable:
             raise errors.ArgumentNullException("predicate")
         head, body = _split_lambda(predicate)
         return self.Count(f"{head} => !({body})") == 0
-
-
-class _Materialized:
-    """Result of an operator that had to run the query (Take after Where): a host array with ToArray()."""
-
-    def __init__(self, arr):
-        self._arr = arr
-
-    def ToArray(self):
-        return self._arr
-
-    ToComputeArray = ToArray
-
-    def __iter__(self):
-        return iter(self._arr)
 
 
 def _literal(value, dtype) -> str:
@@ -427,7 +475,7 @@ def ToComputeArray(source) -> np.ndarray:
     """ToComputeArray on a non-compute source is a plain ToArray (ComputeQueryableExtensions.cs:34-41)."""
     if source is None:
         raise errors.ArgumentNullException("source")
-    if isinstance(source, (ComputeQueryable, _Materialized)):
+    if isinstance(source, ComputeQueryable):
         return source.ToArray()
     return np.array(source, copy=True).reshape(-1)
 

@@ -20,8 +20,9 @@ HEADER_PATH = os.path.join(_HERE, "..", "include", "dcb200.h")
 # ---- constants (values mirror dcb200.h) -------------------------------------------------------------------
 T_NONE, T_I8, T_U8, T_I16, T_U16, T_I32, T_U32, T_I64, T_U64, T_F32, T_F64, T_BOOL = range(12)
 OP_SELECT, OP_WHERE, OP_ZIP = 1, 2, 3
-OP_TOARRAY, OP_SUM, OP_MIN, OP_MAX, OP_AVERAGE, OP_COUNT = 16, 17, 18, 19, 20, 21
+OP_TOARRAY, OP_SUM, OP_MIN, OP_MAX, OP_AVERAGE, OP_COUNT, OP_FIRST_INDEX, OP_LAST_INDEX = 16, 17, 18, 19, 20, 21, 22, 23
 PIPE_FORCE_JIT = 1
+RUN_TAKE = 1
 RES_SAW_NAN, RES_TRUNCATED, RES_TIMEOUT, RES_OVERFLOW = 1, 2, 4, 8
 DEVICE_RESULT_BYTES = 128
 SLOT_FSUM, SLOT_COUNT_F, SLOT_ISUM_LO, SLOT_ISUM_HI, SLOT_COUNT = 0, 1, 2, 3, 4
@@ -92,9 +93,11 @@ PROTOTYPES = {
     "dcb_pipeline_generate_source": (_i32, [C.POINTER(PipelineDesc), C.c_char_p, _sz, C.POINTER(_sz), C.c_char_p, _sz]),
     "dcb_pipeline_run_async": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
     "dcb_pipeline_run": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, C.POINTER(Result), _vp]),
+    "dcb_pipeline_run_ex": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _u32, C.POINTER(Result), _vp]),
     "dcb_result_finalize": (_i32, [_vp, _vp, C.POINTER(Result)]),
     "dcb_record_finalize": (_i32, [_i32, _i32, _vp, C.POINTER(Result)]),
     "dcb_pipeline_run_host": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, C.POINTER(Result)]),
+    "dcb_pipeline_run_host_ex": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _u32, C.POINTER(Result)]),
     "dcb_peer_area_create": (_i32, [_vp, _vp, _sz]),
     "dcb_peer_connect": (_i32, [_vp, _i32, _i32, _vp, _sz]),
     "dcb_peer_area_ptr": (_i32, [_vp, _pp, C.POINTER(_sz)]),

@@ -99,7 +99,11 @@ enum {
     DCB_OP_MIN = 18,
     DCB_OP_MAX = 19,
     DCB_OP_AVERAGE = 20,
-    DCB_OP_COUNT = 21    /* also LongCount */
+    DCB_OP_COUNT = 21,   /* also LongCount */
+    DCB_OP_FIRST_INDEX = 22, /* terminal: index (in the source sequence) of the first element that passes every Where, -1 if none.
+                                TakeWhile / SkipWhile (with the negated predicate) and First(predicate) are built on it;
+                                the reference lists them in its visitor (ExpressionTreeVisitor.cs:249,263-265)            */
+    DCB_OP_LAST_INDEX = 23   /* terminal: index of the last such element, -1 if none (Last / LastOrDefault)              */
 };
 
 typedef struct dcb_op {
@@ -307,6 +311,13 @@ dcb_status dcb_pipeline_run_async(dcb_pipeline* p, const void* in0, const void* 
  * (empty-sequence and overflow errors, Average division, rounding to float). */
 dcb_status dcb_pipeline_run(dcb_pipeline* p, const void* in0, const void* in1, int64_t n,
                             void* out, int64_t out_cap, dcb_result* result, void* stream);
+/* The same with flags. DCB_RUN_TAKE: the query is `...Where(...)...Take(k)` and out_cap is k. The compaction stops reading
+ * its input soon after k survivors are known (persistent blocks stop drawing tiles once a tile starts at or beyond k), more
+ * survivors than k is not an error, and result->count is the number of elements written (at most k). The reference's visitor
+ * lists Take (src/Extensions/DotCompute.Linq/Compilation/ExpressionTreeVisitor.cs:263-265); System.Linq stops iterating at k. */
+enum { DCB_RUN_TAKE = 1u };
+dcb_status dcb_pipeline_run_ex(dcb_pipeline* p, const void* in0, const void* in1, int64_t n,
+                               void* out, int64_t out_cap, uint32_t flags, dcb_result* result, void* stream);
 /* Turn a (possibly NCCL-combined) 16-slot record held in HOST memory into a dcb_result: applies what System.Linq's
  * terminal does after its loop (the scalar branch of ComputeQueryProvider.Execute,
  * src/Extensions/DotCompute.Linq/ComputeQueryableExtensions.cs:240-267). */
@@ -321,6 +332,9 @@ dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, const void* h
  * For ToArray, host_out receives result->count elements (capacity host_out_cap). */
 dcb_status dcb_pipeline_run_host(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
                                  void* host_out, int64_t host_out_cap, dcb_result* result);
+/* The same with DCB_RUN_* flags; with DCB_RUN_TAKE no further chunk is uploaded once k survivors have come back. */
+dcb_status dcb_pipeline_run_host_ex(dcb_pipeline* p, const void* host_in0, const void* host_in1, int64_t n,
+                                    void* host_out, int64_t host_out_cap, uint32_t flags, dcb_result* result);
 
 /* ------------------------------------------------------------------ peer exchange */
 

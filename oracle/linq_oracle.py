@@ -47,6 +47,53 @@ class Enumerable:
     def Skip(self, n):
         return Enumerable(self.data[max(n, 0):])
 
+    def _first_failing(self, pred):
+        """Position of the first element that fails `pred` (len if none): a plain sequential loop, as System.Linq's
+        TakeWhile / SkipWhile iterators do it (the vocabulary of ExpressionTreeVisitor.cs:248-249, 263-265)."""
+        for i in range(self.data.size):
+            if not bool(pred(self.data[i])):
+                return i
+        return int(self.data.size)
+
+    def TakeWhile(self, pred):
+        return Enumerable(self.data[: self._first_failing(pred)])
+
+    def SkipWhile(self, pred):
+        return Enumerable(self.data[self._first_failing(pred):])
+
+    def OrderBy(self, key=None):
+        """Stable ascending sort by key (Enumerable.OrderBy is stable; NaN keys order first, as Comparer<float> does)."""
+        keys = self.data if key is None else np.asarray(key(self.data))
+        if keys.dtype.kind == "f":
+            order = np.lexsort((np.arange(keys.size), np.where(np.isnan(keys), -np.inf, keys), ~np.isnan(keys)))
+        else:
+            order = np.argsort(keys, kind="stable")
+        return Enumerable(self.data[order])
+
+    def OrderByDescending(self, key=None):
+        keys = self.data if key is None else np.asarray(key(self.data))
+        if keys.dtype.kind == "f":
+            order = np.lexsort((np.arange(keys.size), np.where(np.isnan(keys), np.inf, -keys), np.isnan(keys)))
+        else:
+            order = np.lexsort((np.arange(keys.size), -keys.astype(np.int64) if keys.dtype.itemsize < 8 else ~keys))
+        return Enumerable(self.data[order])
+
+    def First(self, pred=None):
+        e = self.Where(pred) if pred else self
+        if e.data.size == 0:
+            raise InvalidOperationError("Sequence contains no elements")
+        return e.data[0]
+
+    def Last(self, pred=None):
+        e = self.Where(pred) if pred else self
+        if e.data.size == 0:
+            raise InvalidOperationError("Sequence contains no elements")
+        return e.data[-1]
+
+    def LastOrDefault(self, pred=None):
+        e = self.Where(pred) if pred else self
+        return e.data[-1] if e.data.size else self.data.dtype.type(0)
+
     # terminals -----------------------------------------------------------------------------------------
     def ToArray(self):
         return self.data.copy()

@@ -390,3 +390,59 @@ def test_division_and_sqrt_are_correctly_rounded(acc):
     t = (r.random(1_000_003, dtype=F) * 1e-38).astype(F) + F(1e-39)
     got = AsComputeQueryable(t, acc).Select("x => x / 3f").ToArray()
     assert np.array_equal(got.view(np.uint32), (t / F(3)).view(np.uint32))
+
+
+# --------------------------------------------------------------------------- positions: TakeWhile / SkipWhile / Last / Take that stops early
+@pytest.mark.parametrize("n", [1, 1000, 4097, 1 << 20, 3_000_001])
+def test_takewhile_skipwhile_last(acc, n):
+    """The reference's visitor lists these operators (ExpressionTreeVisitor.cs:248-249, 263-265) and evaluates them with
+    System.Linq; here one fused pass finds the position (first / last index of an element that passes), the rest is a
+    slice. Checked against a sequential loop, for host arrays and device buffers, around tile and chunk boundaries."""
+    x = rng(500 + n % 97).random(n, dtype=F)
+    x[:: max(n // 7, 1)] *= F(0.5)                                   # some early small values
+    cut = F(0.98)
+    for src in (x, acc.Memory.AllocateAndCopyAsync(x)):
+        q = AsComputeQueryable(src, acc)
+        e = Enumerable(x)
+        assert np.array_equal(q.TakeWhile("x => x < 0.98f").ToArray(), e.TakeWhile(lambda v: v < cut).ToArray())
+        assert np.array_equal(q.SkipWhile("x => x < 0.98f").ToArray(), e.SkipWhile(lambda v: v < cut).ToArray())
+        got = q.Select("x => x * 2f").TakeWhile("y => y < 1.96f").Select("y => y + 1f").ToArray()
+        want = e.Select(lambda v: v * F(2)).TakeWhile(lambda v: v < F(1.96)).Select(lambda v: v + F(1)).ToArray()
+        assert np.array_equal(got, want)
+        assert q.TakeWhile("x => x < 2f").Count() == n and q.SkipWhile("x => x < 2f").ToArray().size == 0     # never fails
+        assert q.TakeWhile("x => x < 0f").ToArray().size == 0                                               # fails at once
+        assert q.Last() == x[-1]
+        assert q.Select("x => x * 3f").Last() == x[-1] * F(3)
+        m = x[x > 0.5]
+        if m.size:
+            assert q.Last("x => x > 0.5f") == m[-1]
+            assert q.Where("x => x > 0.5f").Select("x => x * x + 3f").Last() == m[-1] * m[-1] + F(3)
+        with pytest.raises(InvalidOperationException):
+            q.Last("x => x > 5f")
+        assert q.LastOrDefault("x => x > 5f") == F(0)
+        sw = q.Where("x => x > 0.25f").SkipWhile("x => x < 0.9f").ToArray()       # positions in a filtered sequence
+        assert np.array_equal(sw, Enumerable(x).Where(lambda v: v > F(0.25)).SkipWhile(lambda v: v < F(0.9)).ToArray())
+        sk = q.Where("x => x > 0.25f").Skip(5).Take(7).ToArray()
+        assert np.array_equal(sk, x[x > 0.25][5:12])
+    src.Dispose()
+
+
+def test_take_after_where_stops_early(acc):
+    """Take(k) after a Where: the persistent compaction stops drawing tiles once a tile starts at or beyond k, so the cost
+    follows k, not the length of the source; the result is the first k survivors either way, for device and host sources."""
+    import time
+    n = 1 << 27
+    x = rng(77).random(n, dtype=F)
+    buf = acc.Memory.AllocateAndCopyAsync(x)
+    want = x[: 1 << 22][x[: 1 << 22] > 0.5]
+    for k in (1, 1000, 100_000, want.size):
+        got = AsComputeQueryable(buf, acc).Where("x => x > 0.5f").Take(k).ToArray()
+        assert np.array_equal(got, want[:k])
+    q = AsComputeQueryable(buf, acc).Where("x => x > 0.5f")
+    q.Take(1000).ToArray(); q.ToArray()                              # warm both paths
+    t0 = time.perf_counter(); q.Take(1000).ToArray(); t_take = time.perf_counter() - t0
+    t0 = time.perf_counter(); full = q.ToArray(); t_full = time.perf_counter() - t0
+    assert full.size > 1000 and t_take < t_full                      # the full query also copies 256 MB back; Take must not
+    assert np.array_equal(AsComputeQueryable(x, acc).Where("x => x > 0.5f").Take(50_000).ToArray(), want[:50_000])   # host source: uploads stop
+    assert AsComputeQueryable(buf, acc).Where("x => x > 2f").Take(10).ToArray().size == 0
+    buf.Dispose()

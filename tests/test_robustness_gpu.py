@@ -182,3 +182,42 @@ def test_streamed_kernel_on_unaligned_slices(acc, off):
         acc.SetOption(N.OPT_COMPACT_KERNEL, 0)
         buf.Dispose()
         kbuf.Dispose()
+
+
+def test_host_arrays_larger_than_the_staging_ring(built_library):
+    """Host arrays of five staging chunks (the ring holds three input and two output chunks): map, compaction, reduction
+    and Zip give the right answer, and the device memory the context took for all of it stays below 256 MiB (352 MiB with
+    a second input) however large the arrays are."""
+    import torch
+    torch.cuda.init()
+    acc = CudaAccelerator(0)
+    try:
+        n = 5 * (8 << 20) + 12_345
+        x = rng(91).random(n, dtype=F)
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        got = AsComputeQueryable(x, acc).Select("x => x * 2f + 1f").ToArray()
+        assert np.array_equal(got, x * F(2) + F(1))
+        got = AsComputeQueryable(x, acc).Where("x => x > 0.5f").Select("x => x * x + 3f").ToArray()
+        keep = x > 0.5
+        assert np.array_equal(got, x[keep] * x[keep] + F(3))
+        s = AsComputeQueryable(x, acc).Where("x => x > 0.5f").Select("x => x * x + 3f").Sum()
+        w = (x[keep] * x[keep] + F(3)).astype(np.float64)
+        assert abs(float(s) - float(w.sum())) <= 1e-5 * float(w.sum())
+        assert AsComputeQueryable(x, acc).Count("x => x > 0.5f") == int(keep.sum())
+        taken = AsComputeQueryable(x, acc).Where("x => x > 0.5f").Take(10_000_000).ToArray()      # capped output: stops copying, keeps counting
+        assert np.array_equal(taken, x[keep][:10_000_000])
+        acc.Synchronize()
+        used_one_input = free0 - torch.cuda.mem_get_info()[0]
+        assert used_one_input <= (256 << 20), used_one_input
+        y = rng(92).random(n - 1000, dtype=F)
+        got = AsComputeQueryable(x, acc).Zip(y, "(a, b) => a - b").Where("v => v > 0f").ToArray()
+        d = x[: n - 1000] - y
+        assert np.array_equal(got, d[d > 0])
+        acc.Synchronize()
+        assert free0 - torch.cuda.mem_get_info()[0] <= (352 << 20)
+        k = rng(93).integers(-2**62, 2**62, n // 2, dtype=np.int64)
+        assert np.array_equal(AsComputeQueryable(k, acc).Where("k => (k & 0xF) == 3").ToArray(), k[(k & 0xF) == 3])
+        assert AsComputeQueryable(np.empty(0, F), acc).Where("x => x > 0.5f").ToArray().size == 0
+    finally:
+        acc.Dispose()
