@@ -9,14 +9,14 @@ from .errors import (ArgumentException, ArgumentNullException, CudaErrorClass, C
 from .accelerator import (BufferState, CudaAccelerator, CudaMemoryManager, MapMode, MappedMemory, PinnedArray,
                           UnifiedBuffer)
 from .orchestrator import ComputeOrchestrator, KernelParam, KernelRegistrationInfo, KernelRegistry, translate_kernel_method
-from .linq import (AsComputeQueryable, CompiledPipeline, ComputeLinqProvider, ComputeQueryable, ToComputeArray,
+from .linq import (AsComputeQueryable, CompiledPipeline, ComputeLinqProvider, ComputeQueryable, Grouping, ToComputeArray,
                    generate_source, translate_lambda)
 
 __all__ = [
     "ArgumentException", "ArgumentNullException", "CudaErrorClass", "CudaException", "DotComputeException",
     "InvalidOperationException", "NotSupportedException", "ObjectDisposedException", "OverflowException",
     "BufferState", "CudaAccelerator", "CudaMemoryManager", "MapMode", "MappedMemory", "PinnedArray", "UnifiedBuffer",
-    "AsComputeQueryable", "CompiledPipeline", "ComputeLinqProvider", "ComputeQueryable", "ToComputeArray",
+    "AsComputeQueryable", "CompiledPipeline", "ComputeLinqProvider", "ComputeQueryable", "Grouping", "ToComputeArray",
     "generate_source", "translate_lambda",
     "ComputeOrchestrator", "KernelParam", "KernelRegistrationInfo", "KernelRegistry", "translate_kernel_method",
 ]

@@ -365,6 +365,14 @@ class UnifiedBuffer:
             if not self._acc._disposed:
                 N.lib().dcb_free(self._acc._h, self._h)
 
+    def __del__(self):
+        # IDisposable with a finalizer: a buffer nobody disposed is given back when it is collected (views keep their owner
+        # alive through _parent, so an owner is never collected before its slices).
+        try:
+            self.Dispose()
+        except Exception:
+            pass
+
     def __len__(self):
         return self.Length
 

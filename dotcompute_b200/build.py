@@ -55,7 +55,7 @@ def _stale(target, paths):
 
 def sources():
     names = ["dcb_kernels.cuh", "dcb_translate.h", "dcb_translate.cpp", "dcb_api.cu", "dcb_builtin.h",
-             "dcb_builtin_pipelines.txt", "dcb_gen.cpp", "dcb_noalloc.cu", "dcb_peer.cuh", "dcb_internal.h"]
+             "dcb_builtin_pipelines.txt", "dcb_gen.cpp", "dcb_noalloc.cu", "dcb_peer.cuh", "dcb_internal.h", "dcb_relational.cu"]
     out = [os.path.join(CSRC, n) for n in names if os.path.exists(os.path.join(CSRC, n))]
     out.append(os.path.join(HERE, "..", "include", "dcb200.h"))
     out.append(os.path.abspath(__file__))
@@ -87,9 +87,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
     common = [NVCC, *ARCH, "-I" + CSRC, "-lineinfo", "-O3", "-std=c++17", "-fmad=false", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
     objs = [tr_o]
     cu_files = [os.path.join(CSRC, "dcb_api.cu"), gen_cu]
-    noalloc = os.path.join(CSRC, "dcb_noalloc.cu")
-    if os.path.exists(noalloc):
-        cu_files.append(noalloc)
+    for extra in ("dcb_noalloc.cu", "dcb_relational.cu"):
+        if os.path.exists(os.path.join(CSRC, extra)):
+            cu_files.append(os.path.join(CSRC, extra))
     for cu in cu_files:
         o = os.path.join(BUILD, os.path.basename(cu).replace(".cu", ".o"))
         log = os.path.join(BUILD, os.path.basename(cu) + ".ptxas.log")

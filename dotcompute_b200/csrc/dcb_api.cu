@@ -367,6 +367,9 @@ dcb_status desc_to_ops(const dcb_pipeline_desc* desc, std::vector<dcbt::OpSpec>*
 }  // namespace
 
 void dcb_set_thread_error(const char* msg) { snprintf(tl_error, sizeof tl_error, "%s", msg ? msg : ""); }
+int dcb_ctx_make_current(dcb_ctx* ctx) { return (int)use(ctx); }
+void* dcb_ctx_pick_stream(dcb_ctx* ctx, void* stream) { return (void*)pick(ctx, stream); }
+void dcb_ctx_count_launches(dcb_ctx* ctx, int n) { ctx->launches += n; }
 
 // ============================================================================================ status
 extern "C" int32_t dcb_abi_version(void) { return DCB_ABI_VERSION; }

@@ -1,0 +1,646 @@
+// dcb_relational.cu — multi-block OrderBy, GroupBy-with-aggregate and Join for the LINQ surface (see include/dcb200.h).
+//
+// The reference has generators for these three operators whose kernels are single-block or direct-index
+// (src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:613-751 OrderBy, :753-825 GroupBy, :827-900 Join;
+// OrderByKernelGenerator.cs:108, GroupByKernelGenerator.cs:152, JoinKernelGenerator.cs:140-239) and whose CPU semantics
+// are Array.Sort, a Dictionary in insertion order, and a hash probe (CpuKernelGenerator.cs:475-723). Here all three rest
+// on one primitive, a stable least-significant-digit radix sort of (key, index) pairs over any number of blocks:
+//
+//   OrderBy   keys -> order-preserving unsigned bits -> stable sort -> permutation (the caller gathers the elements)
+//   GroupBy   stable sort by key; equal keys are then neighbours in source order: head flags -> group ids (a scan) ->
+//             one warp-aggregated atomic per (warp, group); groups are emitted in order of first occurrence, which is
+//             what enumerating a Dictionary gives
+//   Join      stable sort of the inner keys; every outer element finds its run of equal keys by binary search; counts ->
+//             scan -> pairs written in (outer index, inner index) order, the order of Enumerable.Join
+//
+// Key selectors and result selectors are ordinary fused Select / Zip pipelines run by the caller; the kernels here are
+// fixed-function and compiled ahead of time. All streaming kernels are HBM-bound; a radix pass reads the keys twice
+// (tile histogram, scatter) and moves key and index once: 4 B + 8 B + 8 B per element and pass for 32-bit keys.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/dcb200.h"
+#include "dcb_internal.h"
+
+namespace {
+
+typedef unsigned int u32;
+typedef unsigned long long u64;
+typedef long long i64;
+
+constexpr int kThreads = 256;
+constexpr int kItems = 16;                       // elements per thread and tile in the sort kernels
+constexpr int kTile = kThreads * kItems;         // 4096
+constexpr int kWarps = kThreads / 32;
+constexpr int kScanItems = 16;
+constexpr int kScanTile = kThreads * kScanItems;
+
+#define RCU(call)                                                                                   \
+    do {                                                                                            \
+        cudaError_t e__ = (call);                                                                   \
+        if (e__ != cudaSuccess) {                                                                   \
+            char msg__[256];                                                                        \
+            snprintf(msg__, sizeof msg__, "%s: %s", #call, cudaGetErrorString(e__));                \
+            dcb_set_thread_error(msg__);                                                            \
+            (void)cudaGetLastError();                                                               \
+            return e__ == cudaErrorMemoryAllocation ? DCB_ERR_OUT_OF_MEMORY : DCB_ERR_CUDA;         \
+        }                                                                                           \
+    } while (0)
+
+dcb_status bad(const char* msg) { dcb_set_thread_error(msg); return DCB_ERR_INVALID_ARGUMENT; }
+
+// ---------------------------------------------------------------------------------------------- sortable keys
+// Order-preserving unsigned image of a key. Floating keys follow .NET's comparer: every NaN is equal to every other NaN
+// and below all numbers, -0 equals +0 (so both get one image and the stable sort keeps their source order).
+template <typename K> struct Sortable;
+template <> struct Sortable<u32> {
+    static __device__ __forceinline__ u32 of_f32(float f) {
+        if (f != f) return 0u;
+        if (f == 0.0f) f = 0.0f;
+        const u32 b = __float_as_uint(f);
+        return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    }
+};
+template <int TYPE> struct KeyOf;
+#define KEY32(T, CT, EXPR) template <> struct KeyOf<T> { typedef CT in_t; typedef u32 bits_t; static __device__ __forceinline__ u32 bits(CT v) { return EXPR; } };
+#define KEY64(T, CT, EXPR) template <> struct KeyOf<T> { typedef CT in_t; typedef u64 bits_t; static __device__ __forceinline__ u64 bits(CT v) { return EXPR; } };
+KEY32(DCB_T_I8, signed char, (u32)((int)v + 128))
+KEY32(DCB_T_U8, unsigned char, (u32)v)
+KEY32(DCB_T_BOOL, unsigned char, (u32)(v != 0))
+KEY32(DCB_T_I16, short, (u32)((int)v + 32768))
+KEY32(DCB_T_U16, unsigned short, (u32)v)
+KEY32(DCB_T_I32, int, (u32)v ^ 0x80000000u)
+KEY32(DCB_T_U32, u32, v)
+KEY32(DCB_T_F32, float, Sortable<u32>::of_f32(v))
+KEY64(DCB_T_I64, i64, (u64)v ^ 0x8000000000000000ull)
+KEY64(DCB_T_U64, u64, v)
+template <> struct KeyOf<DCB_T_F64> {
+    typedef double in_t; typedef u64 bits_t;
+    static __device__ __forceinline__ u64 bits(double f) {
+        if (f != f) return 0ull;
+        if (f == 0.0) f = 0.0;
+        const u64 b = (u64)__double_as_longlong(f);
+        return (b & 0x8000000000000000ull) ? ~b : (b | 0x8000000000000000ull);
+    }
+};
+
+template <int TYPE>
+__global__ void __launch_bounds__(kThreads) prepare_keys(const typename KeyOf<TYPE>::in_t* __restrict__ keys, i64 n, int descending,
+                                                         typename KeyOf<TYPE>::bits_t* __restrict__ bits, u32* __restrict__ idx) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        typename KeyOf<TYPE>::bits_t b = KeyOf<TYPE>::bits(keys[i]);
+        bits[i] = descending ? ~b : b;          // descending = ascending in the complement; ties keep source order either way
+        if (idx) idx[i] = (u32)i;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- radix sort, one pass
+// Tile histogram: counts of the pass's digit in one tile, written digit-major (all tiles of digit 0, then digit 1, ...),
+// so that ONE exclusive scan over that array gives every (digit, tile) its first output position.
+template <typename K>
+__global__ void __launch_bounds__(kThreads) radix_tile_hist(const K* __restrict__ keys, i64 n, int shift, u32 num_tiles, u32* __restrict__ hist) {
+    __shared__ u32 s_hist[256];
+    s_hist[threadIdx.x] = 0;
+    __syncthreads();
+    const i64 base = (i64)blockIdx.x * kTile;
+#pragma unroll 4
+    for (int i = 0; i < kItems; ++i) {
+        const i64 e = base + (i64)i * kThreads + threadIdx.x;
+        if (e < n) atomicAdd(&s_hist[(u32)(keys[e] >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    hist[(size_t)threadIdx.x * num_tiles + blockIdx.x] = s_hist[threadIdx.x];
+}
+
+// Scatter: warp w of a tile owns a contiguous run of kItems * 32 elements; ranks inside the tile follow element order
+// (item, then lane, within a warp; warps in order), so the sort is stable.
+template <typename K>
+__global__ void __launch_bounds__(kThreads) radix_scatter(const K* __restrict__ keys_in, const u32* __restrict__ idx_in, i64 n, int shift,
+                                                          u32 num_tiles, const u32* __restrict__ scanned,
+                                                          K* __restrict__ keys_out, u32* __restrict__ idx_out) {
+    __shared__ u32 s_cnt[kWarps][257];           // per warp and digit: elements seen so far; bin 256 = past the end of the array
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int d = lane; d < 257; d += 32) s_cnt[warp][d] = 0;
+    __syncwarp();
+    const i64 run = (i64)blockIdx.x * kTile + (i64)warp * (kItems * 32);
+    K key[kItems];
+    u32 rank[kItems];
+    const u32 lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const i64 e = run + i * 32 + lane;
+        key[i] = e < n ? keys_in[e] : (K)0;
+    }
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const i64 e = run + i * 32 + lane;
+        const u32 d = e < n ? ((u32)(key[i] >> shift) & 255u) : 256u;
+        const u32 peers = __match_any_sync(0xffffffffu, d);
+        const u32 before = s_cnt[warp][d];
+        __syncwarp();
+        if ((peers & lt) == 0u) s_cnt[warp][d] = before + (u32)__popc(peers);   // the first lane of each group of equal digits
+        __syncwarp();
+        rank[i] = before + (u32)__popc(peers & lt);
+    }
+    __syncthreads();
+    {   // thread d: where this tile's elements of digit d start, and each warp's offset inside that
+        const int d = threadIdx.x;
+        u32 acc = scanned[(size_t)d * num_tiles + blockIdx.x];
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) { const u32 c = s_cnt[w][d]; s_cnt[w][d] = acc; acc += c; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const i64 e = run + i * 32 + lane;
+        if (e < n) {
+            const u32 d = (u32)(key[i] >> shift) & 255u;
+            const u32 pos = s_cnt[warp][d] + rank[i];
+            keys_out[pos] = key[i];
+            idx_out[pos] = idx_in[e];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- exclusive scan of u32
+__global__ void __launch_bounds__(kThreads) scan_tiles(const u32* __restrict__ in, u32* __restrict__ out, i64 n, u32* __restrict__ totals) {
+    __shared__ u32 s_warp[kWarps];
+    const i64 base = (i64)blockIdx.x * kScanTile + (i64)threadIdx.x * kScanItems;
+    u32 v[kScanItems];
+    u32 sum = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) { v[i] = base + i < n ? in[base + i] : 0u; sum += v[i]; }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    u32 incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const u32 t = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += t; }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    u32 warp_off = 0, block_total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) { if (w < warp) warp_off += s_warp[w]; block_total += s_warp[w]; }
+    u32 run = warp_off + incl - sum;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) { if (base + i < n) out[base + i] = run; run += v[i]; }
+    if (threadIdx.x == 0) totals[blockIdx.x] = block_total;
+}
+__global__ void __launch_bounds__(1024) scan_totals(u32* __restrict__ totals, u32 count, u32* __restrict__ grand_total) {
+    // one block: exclusive scan of up to a few hundred thousand block totals, 1024 at a time with a running carry
+    __shared__ u32 s_warp[32];
+    __shared__ u32 s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (u32 base = 0; base < count; base += 1024) {
+        const u32 i = base + threadIdx.x;
+        const u32 v = i < count ? totals[i] : 0u;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        u32 incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { const u32 t = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += t; }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            u32 w = s_warp[lane];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const u32 t = __shfl_up_sync(0xffffffffu, w, d); if (lane >= d) w += t; }
+            s_warp[lane] = w;                    // inclusive over warps
+        }
+        __syncthreads();
+        const u32 carry = s_carry;
+        const u32 warp_off = warp ? s_warp[warp - 1] : 0u;
+        if (i < count) totals[i] = carry + warp_off + incl - v;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = carry + warp_off + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && grand_total) *grand_total = s_carry;
+}
+__global__ void __launch_bounds__(kThreads) scan_add(u32* __restrict__ out, i64 n, const u32* __restrict__ totals) {
+    const u32 add = totals[blockIdx.x];
+    const i64 base = (i64)blockIdx.x * kScanTile + (i64)threadIdx.x * kScanItems;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) if (base + i < n) out[base + i] += add;
+}
+
+// out[i] = sum of in[0..i), in place allowed; *d_total (device, optional) = sum of everything. `d_totals` holds one u32 per scan tile.
+dcb_status exclusive_scan(const u32* d_in, u32* d_out, i64 n, u32* d_totals, u32* d_total, cudaStream_t s) {
+    if (n == 0) { if (d_total) RCU(cudaMemsetAsync(d_total, 0, sizeof(u32), s)); return DCB_OK; }
+    const u32 blocks = (u32)((n + kScanTile - 1) / kScanTile);
+    scan_tiles<<<blocks, kThreads, 0, s>>>(d_in, d_out, n, d_totals);
+    scan_totals<<<1, 1024, 0, s>>>(d_totals, blocks, d_total);
+    scan_add<<<blocks, kThreads, 0, s>>>(d_out, n, d_totals);
+    RCU(cudaGetLastError());
+    return DCB_OK;
+}
+size_t scan_totals_count(i64 n) { return (size_t)((n + kScanTile - 1) / kScanTile) + 1; }
+
+// ---------------------------------------------------------------------------------------------- the sort itself
+struct SortScratch {
+    void* keys[2] = {nullptr, nullptr};
+    u32* idx[2] = {nullptr, nullptr};
+    u32* hist = nullptr;
+    u32* totals = nullptr;
+    cudaStream_t s = nullptr;
+    dcb_status alloc(i64 n, int key_bytes, cudaStream_t stream) {
+        s = stream;
+        const u32 tiles = (u32)((n + kTile - 1) / kTile);
+        const size_t m = (size_t)256 * std::max<u32>(tiles, 1);
+        for (int i = 0; i < 2; ++i) {
+            RCU(cudaMallocAsync(&keys[i], std::max<size_t>((size_t)n * key_bytes, 16), s));
+            RCU(cudaMallocAsync((void**)&idx[i], std::max<size_t>((size_t)n * 4, 16), s));
+        }
+        RCU(cudaMallocAsync((void**)&hist, m * 4, s));
+        RCU(cudaMallocAsync((void**)&totals, scan_totals_count((i64)m) * 4, s));
+        return DCB_OK;
+    }
+    void release() {
+        for (int i = 0; i < 2; ++i) { if (keys[i]) cudaFreeAsync(keys[i], s); if (idx[i]) cudaFreeAsync(idx[i], s); keys[i] = nullptr; idx[i] = nullptr; }
+        if (hist) cudaFreeAsync(hist, s);
+        if (totals) cudaFreeAsync(totals, s);
+        hist = totals = nullptr;
+    }
+};
+
+// Sorts sc.keys[0] / sc.idx[0] (n pairs of sortable bits and payload); returns which of the two buffers holds the result.
+template <typename K>
+dcb_status radix_sort(SortScratch& sc, i64 n, int* result_buf) {
+    const u32 tiles = (u32)((n + kTile - 1) / kTile);
+    int cur = 0;
+    if (n > 0) {
+        for (int shift = 0; shift < (int)sizeof(K) * 8; shift += 8) {
+            radix_tile_hist<K><<<tiles, kThreads, 0, sc.s>>>((const K*)sc.keys[cur], n, shift, tiles, sc.hist);
+            dcb_status st = exclusive_scan(sc.hist, sc.hist, (i64)256 * tiles, sc.totals, nullptr, sc.s);
+            if (st) return st;
+            radix_scatter<K><<<tiles, kThreads, 0, sc.s>>>((const K*)sc.keys[cur], sc.idx[cur], n, shift, tiles, sc.hist,
+                                                           (K*)sc.keys[cur ^ 1], sc.idx[cur ^ 1]);
+            cur ^= 1;
+        }
+        RCU(cudaGetLastError());
+    }
+    *result_buf = cur;
+    return DCB_OK;
+}
+
+template <int TYPE>
+dcb_status prepare(const void* d_keys, i64 n, int descending, void* bits, u32* idx, cudaStream_t s) {
+    if (n == 0) return DCB_OK;
+    const int grid = (int)std::min<i64>((n + kThreads - 1) / kThreads, 148 * 8);
+    prepare_keys<TYPE><<<grid, kThreads, 0, s>>>((const typename KeyOf<TYPE>::in_t*)d_keys, n, descending,
+                                                (typename KeyOf<TYPE>::bits_t*)bits, idx);
+    RCU(cudaGetLastError());
+    return DCB_OK;
+}
+int key_bytes_of(int type) {
+    switch (type) {
+        case DCB_T_I64: case DCB_T_U64: case DCB_T_F64: return 8;
+        case DCB_T_I8: case DCB_T_U8: case DCB_T_BOOL: case DCB_T_I16: case DCB_T_U16: case DCB_T_I32: case DCB_T_U32: case DCB_T_F32: return 4;
+        default: return 0;
+    }
+}
+dcb_status prepare_any(int type, const void* d_keys, i64 n, int descending, void* bits, u32* idx, cudaStream_t s) {
+    switch (type) {
+        case DCB_T_I8: return prepare<DCB_T_I8>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_U8: return prepare<DCB_T_U8>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_BOOL: return prepare<DCB_T_BOOL>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_I16: return prepare<DCB_T_I16>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_U16: return prepare<DCB_T_U16>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_I32: return prepare<DCB_T_I32>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_U32: return prepare<DCB_T_U32>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_F32: return prepare<DCB_T_F32>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_I64: return prepare<DCB_T_I64>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_U64: return prepare<DCB_T_U64>(d_keys, n, descending, bits, idx, s);
+        case DCB_T_F64: return prepare<DCB_T_F64>(d_keys, n, descending, bits, idx, s);
+        default: return bad("unsupported key type");
+    }
+}
+// keys (typed, device) -> sorted sortable bits in sc.keys[*buf] and the stable permutation in sc.idx[*buf]
+dcb_status sort_keys(SortScratch& sc, int key_type, const void* d_keys, i64 n, int descending, int* buf) {
+    dcb_status st = prepare_any(key_type, d_keys, n, descending, sc.keys[0], sc.idx[0], sc.s);
+    if (st) return st;
+    return key_bytes_of(key_type) == 8 ? radix_sort<u64>(sc, n, buf) : radix_sort<u32>(sc, n, buf);
+}
+
+// ---------------------------------------------------------------------------------------------- gather
+template <typename T>
+__global__ void __launch_bounds__(kThreads) gather_kernel(const T* __restrict__ src, const u32* __restrict__ idx, i64 n, T* __restrict__ dst) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = src[idx[i]];
+}
+
+// ---------------------------------------------------------------------------------------------- group by
+enum { AGG_COUNT = 0, AGG_SUM = 1, AGG_MIN = 2, AGG_MAX = 3, AGG_AVERAGE = 4 };
+
+template <typename K>
+__global__ void __launch_bounds__(kThreads) group_heads(const K* __restrict__ sorted, i64 n, u32* __restrict__ heads) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) heads[i] = (i == 0 || sorted[i] != sorted[i - 1]) ? 1u : 0u;
+}
+// Value of element e as a double (floating values) or a 64-bit integer (integer values).
+template <typename V> struct ValueOf {
+    static __device__ __forceinline__ double f(const V* p, u32 e) { return (double)p[e]; }
+    static __device__ __forceinline__ i64 i(const V* p, u32 e) { return (i64)p[e]; }
+};
+__device__ __forceinline__ void atomic_min_f64(double* addr, double v) {
+    u64 old = *(volatile u64*)addr;
+    while (__longlong_as_double((i64)old) > v || __longlong_as_double((i64)old) != __longlong_as_double((i64)old)) {
+        const u64 seen = atomicCAS((u64*)addr, old, (u64)__double_as_longlong(v));
+        if (seen == old) break;
+        old = seen;
+    }
+}
+__device__ __forceinline__ void atomic_max_f64(double* addr, double v) {
+    u64 old = *(volatile u64*)addr;
+    while (__longlong_as_double((i64)old) < v || __longlong_as_double((i64)old) != __longlong_as_double((i64)old)) {
+        const u64 seen = atomicCAS((u64*)addr, old, (u64)__double_as_longlong(v));
+        if (seen == old) break;
+        old = seen;
+    }
+}
+// Sorted position i belongs to group gid[i] (inclusive scan of the head flags, minus one). Lanes of one group are
+// neighbours, so a warp folds each of its groups with a segmented shuffle reduction and issues one atomic per group.
+template <typename V, bool FP>
+__global__ void __launch_bounds__(kThreads) group_reduce(const V* __restrict__ values, const u32* __restrict__ idx, const u32* __restrict__ heads_excl,
+                                                         const u32* __restrict__ heads, i64 n, int agg, u32* __restrict__ first_idx,
+                                                         u32* __restrict__ counts, double* __restrict__ facc, i64* __restrict__ iacc) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    const int lane = threadIdx.x & 31;
+    for (i64 i0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) - lane; i0 < n; i0 += stride) {
+        const i64 i = i0 + lane;
+        const bool live = i < n;
+        const u32 e = live ? idx[i] : 0u;
+        const u32 g = live ? heads_excl[i] + heads[i] - 1u : 0xffffffffu;
+        if (live && heads[i]) first_idx[g] = e;              // stable sort: the head of a group is its first element in the source
+        double fv = 0; i64 iv = 0; u32 c = live ? 1u : 0u;
+        if (live && agg != AGG_COUNT) { if (FP) fv = ValueOf<V>::f(values, e); else iv = ValueOf<V>::i(values, e); }
+        const u32 peers = __match_any_sync(0xffffffffu, g);
+        const int last = 31 - __clz((int)peers);             // lanes of a group are contiguous
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u32 oc = __shfl_down_sync(0xffffffffu, c, d);
+            const double of = __shfl_down_sync(0xffffffffu, fv, d);
+            const i64 oi = __shfl_down_sync(0xffffffffu, iv, d);
+            if (lane + d <= last) {
+                c += oc;
+                if (agg == AGG_MIN) { if (FP) fv = of < fv ? of : fv; else iv = oi < iv ? oi : iv; }
+                else if (agg == AGG_MAX) { if (FP) fv = of > fv ? of : fv; else iv = oi > iv ? oi : iv; }
+                else { fv += of; iv += oi; }
+            }
+        }
+        if (live && (peers & ((1u << lane) - 1u)) == 0u) {   // first lane of the group within this warp
+            atomicAdd(&counts[g], c);
+            if (agg == AGG_SUM || agg == AGG_AVERAGE) { if (FP) atomicAdd(&facc[g], fv); else atomicAdd((u64*)&iacc[g], (u64)iv); }
+            else if (agg == AGG_MIN) { if (FP) atomic_min_f64(&facc[g], fv); else atomicMin(&iacc[g], iv); }
+            else if (agg == AGG_MAX) { if (FP) atomic_max_f64(&facc[g], fv); else atomicMax(&iacc[g], iv); }
+        }
+    }
+}
+__global__ void __launch_bounds__(kThreads) group_init(u32 groups, int agg, bool fp, double* facc, i64* iacc, u32* counts) {
+    for (u32 g = blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += gridDim.x * blockDim.x) {
+        counts[g] = 0;
+        if (agg == AGG_MIN) { facc[g] = __longlong_as_double(0x7ff8000000000000LL); iacc[g] = 0x7fffffffffffffffLL; }
+        else if (agg == AGG_MAX) { facc[g] = __longlong_as_double(0x7ff8000000000000LL); iacc[g] = -0x7fffffffffffffffLL - 1; }
+        else { facc[g] = 0.0; iacc[g] = 0; }
+        (void)fp;
+    }
+}
+// Final order = order of first occurrence: `order` is the argsort of first_idx.
+__global__ void __launch_bounds__(kThreads) group_emit(const u32* __restrict__ order, const u32* __restrict__ first_idx, const u32* __restrict__ counts,
+                                                       const double* __restrict__ facc, const i64* __restrict__ iacc, u32 groups, int agg, bool fp,
+                                                       u32* __restrict__ out_first, i64* __restrict__ out_counts, double* __restrict__ out_f, i64* __restrict__ out_i) {
+    for (u32 j = blockIdx.x * blockDim.x + threadIdx.x; j < groups; j += gridDim.x * blockDim.x) {
+        const u32 g = order[j];
+        out_first[j] = first_idx[g];
+        out_counts[j] = (i64)counts[g];
+        if (fp) out_f[j] = agg == AGG_AVERAGE ? facc[g] / (double)counts[g] : facc[g];
+        else { out_i[j] = iacc[g]; out_f[j] = agg == AGG_AVERAGE ? (double)iacc[g] / (double)counts[g] : (double)iacc[g]; }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- join
+template <typename K>
+__device__ __forceinline__ u32 lower_bound(const K* __restrict__ a, u32 n, K key) {
+    u32 lo = 0, hi = n;
+    while (lo < hi) { const u32 mid = lo + ((hi - lo) >> 1); if (a[mid] < key) lo = mid + 1; else hi = mid; }
+    return lo;
+}
+template <typename K>
+__device__ __forceinline__ u32 upper_bound(const K* __restrict__ a, u32 n, K key) {
+    u32 lo = 0, hi = n;
+    while (lo < hi) { const u32 mid = lo + ((hi - lo) >> 1); if (a[mid] <= key) lo = mid + 1; else hi = mid; }
+    return lo;
+}
+enum { JOIN_INNER = 0, JOIN_SEMI = 2, JOIN_ANTI = 3 };
+template <typename K>
+__global__ void __launch_bounds__(kThreads) join_count(const K* __restrict__ outer_bits, i64 n_outer, const K* __restrict__ inner_sorted, u32 n_inner,
+                                                       int kind, u32* __restrict__ lo_out, u32* __restrict__ cnt_out) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n_outer; i += stride) {
+        const K key = outer_bits[i];
+        const u32 lo = lower_bound(inner_sorted, n_inner, key), hi = upper_bound(inner_sorted, n_inner, key);
+        lo_out[i] = lo;
+        const u32 m = hi - lo;
+        cnt_out[i] = kind == JOIN_INNER ? m : (kind == JOIN_SEMI ? (m ? 1u : 0u) : (m ? 0u : 1u));
+    }
+}
+__global__ void __launch_bounds__(kThreads) join_write(const u32* __restrict__ lo, const u32* __restrict__ cnt, const u32* __restrict__ off, i64 n_outer,
+                                                       const u32* __restrict__ inner_idx_sorted, int kind, i64 out_cap,
+                                                       u32* __restrict__ outer_out, u32* __restrict__ inner_out) {
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n_outer; i += stride) {
+        const u32 c = cnt[i], o = off[i], l = lo[i];
+        for (u32 j = 0; j < c; ++j) {
+            if ((i64)o + j >= out_cap) break;
+            outer_out[o + j] = (u32)i;
+            if (inner_out) inner_out[o + j] = kind == JOIN_INNER ? inner_idx_sorted[l + j] : 0u;
+        }
+    }
+}
+
+int launch_grid(i64 n) { return (int)std::max<i64>(1, std::min<i64>((n + kThreads - 1) / kThreads, 148 * 8)); }
+
+}  // namespace
+
+// ================================================================================================ C ABI
+extern "C" dcb_status dcb_sort_indices(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int64_t n, int32_t descending,
+                                       uint32_t* d_indices, void* stream) {
+    if (!ctx) return bad("ctx is null");
+    dcb_status st = (dcb_status)dcb_ctx_make_current(ctx);
+    if (st) return st;
+    if (n < 0 || n >= (1ll << 32)) return bad("n must lie in [0, 2^32)");
+    if (n > 0 && (!d_keys || !d_indices)) return bad("null pointer");
+    if (key_bytes_of(key_type) == 0) return bad("unsupported key type");
+    cudaStream_t s = (cudaStream_t)dcb_ctx_pick_stream(ctx, stream);
+    dcb_ctx_count_launches(ctx, 1 + 5 * key_bytes_of(key_type));
+    SortScratch sc;
+    if ((st = sc.alloc(n, key_bytes_of(key_type), s))) { sc.release(); return st; }
+    int buf = 0;
+    st = sort_keys(sc, key_type, d_keys, n, descending, &buf);
+    if (st == DCB_OK && n > 0) {
+        cudaError_t e = cudaMemcpyAsync(d_indices, sc.idx[buf], (size_t)n * 4, cudaMemcpyDeviceToDevice, s);
+        if (e != cudaSuccess) st = DCB_ERR_CUDA;
+    }
+    sc.release();
+    return st;
+}
+
+extern "C" dcb_status dcb_gather(dcb_ctx* ctx, int32_t elem_bytes, const void* d_src, const uint32_t* d_indices, int64_t n, void* d_dst, void* stream) {
+    if (!ctx) return bad("ctx is null");
+    if (n < 0) return bad("n is negative");
+    if (n == 0) return DCB_OK;
+    if (!d_src || !d_indices || !d_dst) return bad("null pointer");
+    if (dcb_ctx_make_current(ctx)) return DCB_ERR_CUDA;
+    cudaStream_t s = (cudaStream_t)dcb_ctx_pick_stream(ctx, stream);
+    dcb_ctx_count_launches(ctx, 1);
+    const int grid = launch_grid(n);
+    switch (elem_bytes) {
+        case 1: gather_kernel<unsigned char><<<grid, kThreads, 0, s>>>((const unsigned char*)d_src, d_indices, n, (unsigned char*)d_dst); break;
+        case 2: gather_kernel<unsigned short><<<grid, kThreads, 0, s>>>((const unsigned short*)d_src, d_indices, n, (unsigned short*)d_dst); break;
+        case 4: gather_kernel<u32><<<grid, kThreads, 0, s>>>((const u32*)d_src, d_indices, n, (u32*)d_dst); break;
+        case 8: gather_kernel<u64><<<grid, kThreads, 0, s>>>((const u64*)d_src, d_indices, n, (u64*)d_dst); break;
+        default: return bad("element size must be 1, 2, 4 or 8 bytes");
+    }
+    RCU(cudaGetLastError());
+    return DCB_OK;
+}
+
+template <typename V, bool FP>
+static void launch_group_reduce(const void* values, const u32* idx, const u32* excl, const u32* heads, i64 n, int agg, u32* first_idx, u32* counts,
+                                double* facc, i64* iacc, cudaStream_t s) {
+    group_reduce<V, FP><<<launch_grid(n), kThreads, 0, s>>>((const V*)values, idx, excl, heads, n, agg, first_idx, counts, facc, iacc);
+}
+
+extern "C" dcb_status dcb_group_aggregate(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int32_t value_type, const void* d_values, int64_t n,
+                                          int32_t aggregate, int64_t out_cap, uint32_t* d_out_first, int64_t* d_out_counts, double* d_out_f64,
+                                          int64_t* d_out_i64, int64_t* out_groups, void* stream) {
+    if (!ctx) return bad("ctx is null");
+    if (dcb_ctx_make_current(ctx)) return DCB_ERR_CUDA;
+    if (!out_groups) return bad("out_groups is null");
+    *out_groups = 0;
+    if (n < 0 || n >= (1ll << 32)) return bad("n must lie in [0, 2^32)");
+    if (aggregate < AGG_COUNT || aggregate > AGG_AVERAGE) return bad("unknown aggregate");
+    if (n == 0) return DCB_OK;
+    if (!d_keys || !d_out_first || !d_out_counts || !d_out_f64 || !d_out_i64) return bad("null pointer");
+    if (aggregate != AGG_COUNT && !d_values) return bad("values are null");
+    const int kb = key_bytes_of(key_type);
+    if (kb == 0) return bad("unsupported key type");
+    const bool fp = value_type == DCB_T_F32 || value_type == DCB_T_F64;
+    cudaStream_t s = (cudaStream_t)dcb_ctx_pick_stream(ctx, stream);
+    dcb_ctx_count_launches(ctx, 12 + 5 * kb);
+    SortScratch sc;
+    dcb_status st = sc.alloc(n, kb, s);
+    u32 *heads = nullptr, *excl = nullptr, *totals = nullptr, *d_total = nullptr;
+    u32 *first_idx = nullptr, *counts = nullptr, *order = nullptr;
+    double* facc = nullptr; i64* iacc = nullptr;
+    SortScratch sg;
+    auto cleanup = [&]() {
+        sc.release(); sg.release();
+        for (void* p : {(void*)heads, (void*)excl, (void*)totals, (void*)d_total, (void*)first_idx, (void*)counts, (void*)order, (void*)facc, (void*)iacc})
+            if (p) cudaFreeAsync(p, s);
+    };
+    if (st) { cleanup(); return st; }
+    int buf = 0;
+    if ((st = sort_keys(sc, key_type, d_keys, n, 0, &buf))) { cleanup(); return st; }
+    cudaError_t e = cudaMallocAsync((void**)&heads, (size_t)n * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&excl, (size_t)n * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&totals, scan_totals_count(n) * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&d_total, 16, s);
+    if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_OUT_OF_MEMORY; }
+    if (kb == 8) group_heads<u64><<<launch_grid(n), kThreads, 0, s>>>((const u64*)sc.keys[buf], n, heads);
+    else group_heads<u32><<<launch_grid(n), kThreads, 0, s>>>((const u32*)sc.keys[buf], n, heads);
+    if ((st = exclusive_scan(heads, excl, n, totals, d_total, s))) { cleanup(); return st; }
+    u32 groups = 0;
+    e = cudaMemcpyAsync(&groups, d_total, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_CUDA; }
+    *out_groups = groups;
+    if ((int64_t)groups > out_cap) { cleanup(); dcb_set_thread_error("more groups than the outputs hold"); return DCB_ERR_OUTPUT_TOO_SMALL; }
+    e = cudaMallocAsync((void**)&first_idx, (size_t)groups * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&counts, (size_t)groups * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&order, (size_t)groups * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&facc, (size_t)groups * 8, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&iacc, (size_t)groups * 8, s);
+    if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_OUT_OF_MEMORY; }
+    group_init<<<launch_grid(groups), kThreads, 0, s>>>(groups, aggregate, fp, facc, iacc, counts);
+    const u32* idx = sc.idx[buf];
+    switch (value_type) {
+        case DCB_T_F32: launch_group_reduce<float, true>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_F64: launch_group_reduce<double, true>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_I8: launch_group_reduce<signed char, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_U8: case DCB_T_BOOL: launch_group_reduce<unsigned char, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_I16: launch_group_reduce<short, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_U16: launch_group_reduce<unsigned short, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_I32: launch_group_reduce<int, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_U32: launch_group_reduce<u32, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_I64: launch_group_reduce<i64, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        case DCB_T_U64: launch_group_reduce<i64, false>(d_values, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break;
+        default:
+            if (aggregate == AGG_COUNT) { launch_group_reduce<u32, false>(d_keys, idx, excl, heads, n, aggregate, first_idx, counts, facc, iacc, s); break; }
+            cleanup(); return bad("unsupported value type");
+    }
+    // groups in order of first occurrence: argsort of the groups' first indices
+    if ((st = sg.alloc(groups, 4, s))) { cleanup(); return st; }
+    int gb = 0;
+    if ((st = sort_keys(sg, DCB_T_U32, first_idx, groups, 0, &gb))) { cleanup(); return st; }
+    group_emit<<<launch_grid(groups), kThreads, 0, s>>>(sg.idx[gb], first_idx, counts, facc, iacc, groups, aggregate, fp, d_out_first, (i64*)d_out_counts, d_out_f64, (i64*)d_out_i64);
+    e = cudaGetLastError();
+    cleanup();
+    if (e != cudaSuccess) return DCB_ERR_CUDA;
+    return DCB_OK;
+}
+
+extern "C" dcb_status dcb_join_indices(dcb_ctx* ctx, int32_t key_type, const void* d_outer_keys, int64_t n_outer, const void* d_inner_keys,
+                                       int64_t n_inner, int32_t join_kind, int64_t out_cap, uint32_t* d_outer_out, uint32_t* d_inner_out,
+                                       int64_t* out_pairs, void* stream) {
+    if (!ctx) return bad("ctx is null");
+    if (dcb_ctx_make_current(ctx)) return DCB_ERR_CUDA;
+    if (!out_pairs) return bad("out_pairs is null");
+    *out_pairs = 0;
+    if (n_outer < 0 || n_inner < 0 || n_outer >= (1ll << 32) || n_inner >= (1ll << 32)) return bad("sizes must lie in [0, 2^32)");
+    if (join_kind != JOIN_INNER && join_kind != JOIN_SEMI && join_kind != JOIN_ANTI) return bad("join kind must be inner (0), semi (2) or anti (3)");
+    const int kb = key_bytes_of(key_type);
+    if (kb == 0) return bad("unsupported key type");
+    if (n_outer == 0) return DCB_OK;
+    if (!d_outer_keys || (n_inner > 0 && !d_inner_keys)) return bad("null pointer");
+    cudaStream_t s = (cudaStream_t)dcb_ctx_pick_stream(ctx, stream);
+    dcb_ctx_count_launches(ctx, 6 + 5 * kb);
+    SortScratch sc;
+    void* outer_bits = nullptr;
+    u32 *lo = nullptr, *cnt = nullptr, *off = nullptr, *totals = nullptr, *d_total = nullptr;
+    auto cleanup = [&]() {
+        sc.release();
+        for (void* p : {outer_bits, (void*)lo, (void*)cnt, (void*)off, (void*)totals, (void*)d_total}) if (p) cudaFreeAsync(p, s);
+    };
+    dcb_status st = sc.alloc(n_inner, kb, s);
+    if (st) { cleanup(); return st; }
+    int buf = 0;
+    if ((st = sort_keys(sc, key_type, d_inner_keys, n_inner, 0, &buf))) { cleanup(); return st; }
+    cudaError_t e = cudaMallocAsync(&outer_bits, (size_t)n_outer * kb, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&lo, (size_t)n_outer * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&cnt, (size_t)n_outer * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&off, (size_t)n_outer * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&totals, scan_totals_count(n_outer) * 4, s);
+    if (e == cudaSuccess) e = cudaMallocAsync((void**)&d_total, 16, s);
+    if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_OUT_OF_MEMORY; }
+    if ((st = prepare_any(key_type, d_outer_keys, n_outer, 0, outer_bits, nullptr, s))) { cleanup(); return st; }
+    if (kb == 8) join_count<u64><<<launch_grid(n_outer), kThreads, 0, s>>>((const u64*)outer_bits, n_outer, (const u64*)sc.keys[buf], (u32)n_inner, join_kind, lo, cnt);
+    else join_count<u32><<<launch_grid(n_outer), kThreads, 0, s>>>((const u32*)outer_bits, n_outer, (const u32*)sc.keys[buf], (u32)n_inner, join_kind, lo, cnt);
+    if ((st = exclusive_scan(cnt, off, n_outer, totals, d_total, s))) { cleanup(); return st; }
+    u32 pairs = 0;
+    e = cudaMemcpyAsync(&pairs, d_total, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_CUDA; }
+    *out_pairs = pairs;      // a total beyond 2^32 - 1 is not representable here: the counts are 32-bit
+    if (d_outer_out && pairs > 0) {
+        join_write<<<launch_grid(n_outer), kThreads, 0, s>>>(lo, cnt, off, n_outer, sc.idx[buf], join_kind, out_cap, d_outer_out, d_inner_out);
+        e = cudaGetLastError();
+    }
+    cleanup();
+    if (e != cudaSuccess) return DCB_ERR_CUDA;
+    if ((int64_t)pairs > out_cap && d_outer_out) { dcb_set_thread_error("more pairs than the outputs hold"); return DCB_ERR_OUTPUT_TOO_SMALL; }
+    return DCB_OK;
+}

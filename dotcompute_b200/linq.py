@@ -333,6 +333,127 @@ class ComputeQueryable:
                                     take=k if self._take is None else min(k, self._take))
         return ComputeQueryable(_slice(self._source, 0, k), self._acc, (), None, self._force_jit)
 
+    # ------------------------------------------------------------------ OrderBy / GroupBy / Join (device-resident)
+    def ToBuffer(self) -> UnifiedBuffer:
+        """The query's result as a device buffer (the caller disposes it). A device source without operators is returned as
+        a view of itself; everything else runs the fused kernel into a fresh buffer, with no trip through the host for
+        device sources."""
+        acc = self.Accelerator
+        if not self._ops and self._take is None:
+            src = self._source
+            if isinstance(src, UnifiedBuffer):
+                return src.Slice(0, src.Length)
+            host = src.array if isinstance(src, PinnedArray) else np.ascontiguousarray(np.asarray(src).reshape(-1))
+            return acc.Memory.AllocateAndCopyAsync(host)
+        if not isinstance(self._source, UnifiedBuffer):
+            return acc.Memory.AllocateAndCopyAsync(self.ToArray())
+        pipe = self._compile(N.OP_TOARRAY)
+        n = self._length()
+        cap = n if self._take is None else min(n, self._take)
+        dbuf = acc.Memory.AllocateAsync(max(cap, 1), pipe.out_dtype)
+        res = N.Result()
+        in1 = C.c_void_p(self._second.GetDeviceMemory()) if self._second is not None else None
+        flags = N.RUN_TAKE if (self._take is not None and pipe.has_filter) else 0
+        N.check(N.lib().dcb_pipeline_run_ex(pipe.handle, C.c_void_p(self._source.GetDeviceMemory()), in1, n if pipe.has_filter else cap,
+                                            C.c_void_p(dbuf.GetDeviceMemory()), cap, flags, C.byref(res), None), acc.handle)
+        got = min(int(res.count), cap)
+        out = dbuf.Slice(0, got)
+        out._owner = dbuf                      # keeps the allocation alive as long as the view
+        return out
+
+    def _keys_of(self, values: UnifiedBuffer, selector: str | None) -> UnifiedBuffer:
+        if selector is None:
+            return values.Slice(0, values.Length)
+        return ComputeQueryable(values, self._acc, ((N.OP_SELECT, selector),), None, self._force_jit).ToBuffer()
+
+    def _order(self, key_selector: str | None, descending: bool) -> "ComputeQueryable":
+        acc = self.Accelerator
+        values = self.ToBuffer()
+        n = values.Length
+        if n <= 1:
+            return ComputeQueryable(values, acc, (), None, self._force_jit)
+        keys = self._keys_of(values, key_selector)
+        idx = acc.Memory.AllocateAsync(n, np.uint32)
+        N.check(N.lib().dcb_sort_indices(acc.handle, dcb_type(keys.dtype), C.c_void_p(keys.GetDeviceMemory()), n, 1 if descending else 0,
+                                         C.c_void_p(idx.GetDeviceMemory()), None), acc.handle)
+        out = acc.Memory.AllocateAsync(n, values.dtype)
+        N.check(N.lib().dcb_gather(acc.handle, values.dtype.itemsize, C.c_void_p(values.GetDeviceMemory()), C.c_void_p(idx.GetDeviceMemory()), n,
+                                   C.c_void_p(out.GetDeviceMemory()), None), acc.handle)
+        acc.Synchronize()
+        idx.Dispose(); keys.Dispose()
+        return ComputeQueryable(out, acc, (), None, self._force_jit)
+
+    def OrderBy(self, keySelector: str | None = None) -> "ComputeQueryable":
+        """Stable ascending sort by `keySelector` (the elements themselves if None): a multi-block radix sort on the device.
+        The reference's generator emits a single-block bitonic sort (CudaKernelGenerator.cs:613-751, OrderByKernelGenerator.cs:108);
+        its CPU path is Array.Sort(keys, values) (CpuKernelGenerator.cs:475-527). Ties keep source order, as Enumerable.OrderBy."""
+        return self._order(keySelector, False)
+
+    def OrderByDescending(self, keySelector: str | None = None) -> "ComputeQueryable":
+        return self._order(keySelector, True)
+
+    def GroupBy(self, keySelector: str | None = None) -> "Grouping":
+        """GroupBy followed by an aggregate (Count / Sum / Min / Max / Average), one result per key in order of first occurrence -
+        the order a Dictionary enumerates in, which is what the reference's CPU path produces (CpuKernelGenerator.cs:544-659;
+        GPU generator CudaKernelGenerator.cs:753-825, GroupByKernelGenerator.cs:152)."""
+        return Grouping(self, keySelector)
+
+    def _join(self, inner, outerKeySelector, innerKeySelector, kind: int):
+        acc = self.Accelerator
+        if inner is None:
+            raise errors.ArgumentNullException("inner")
+        inner_q = inner if isinstance(inner, ComputeQueryable) else ComputeQueryable(inner, acc, (), None, self._force_jit)
+        ov, iv = self.ToBuffer(), inner_q.ToBuffer()
+        ok, ik = self._keys_of(ov, outerKeySelector), self._keys_of(iv, innerKeySelector)
+        if ok.dtype != ik.dtype:
+            raise errors.ArgumentException(f"join keys have different types: {ok.dtype} and {ik.dtype}")
+        pairs = C.c_int64()
+        args = (acc.handle, dcb_type(ok.dtype), C.c_void_p(ok.GetDeviceMemory()), ov.Length, C.c_void_p(ik.GetDeviceMemory()), iv.Length, kind)
+        N.check(N.lib().dcb_join_indices(*args, 0, None, None, C.byref(pairs), None), acc.handle)
+        m = int(pairs.value)
+        oi = acc.Memory.AllocateAsync(max(m, 1), np.uint32)
+        ii = acc.Memory.AllocateAsync(max(m, 1), np.uint32)
+        if m:
+            N.check(N.lib().dcb_join_indices(*args, m, C.c_void_p(oi.GetDeviceMemory()), C.c_void_p(ii.GetDeviceMemory()), C.byref(pairs), None), acc.handle)
+        go = acc.Memory.AllocateAsync(max(m, 1), ov.dtype)
+        gi = acc.Memory.AllocateAsync(max(m, 1), iv.dtype)
+        if m:
+            N.check(N.lib().dcb_gather(acc.handle, ov.dtype.itemsize, C.c_void_p(ov.GetDeviceMemory()), C.c_void_p(oi.GetDeviceMemory()), m,
+                                       C.c_void_p(go.GetDeviceMemory()), None), acc.handle)
+            if kind == N.JOIN_INNER:
+                N.check(N.lib().dcb_gather(acc.handle, iv.dtype.itemsize, C.c_void_p(iv.GetDeviceMemory()), C.c_void_p(ii.GetDeviceMemory()), m,
+                                           C.c_void_p(gi.GetDeviceMemory()), None), acc.handle)
+        acc.Synchronize()
+        for b in (ok, ik, oi, ii):
+            b.Dispose()
+        return go.Slice(0, m), gi.Slice(0, m), go, gi
+
+    def Join(self, inner, outerKeySelector: str | None, innerKeySelector: str | None, resultSelector: str) -> "ComputeQueryable":
+        """Inner equi-join: resultSelector(outer, inner) for every pair with equal keys, ordered by outer element, then inner
+        element (the order of Enumerable.Join). The inner keys are sorted once (stable radix sort), every outer key finds its
+        run by binary search, and the pairs are written in order; the result selector is a fused Zip over the gathered pairs.
+        The reference's generator builds a fixed-size hash table (JoinKernelGenerator.cs:140-239, CudaKernelGenerator.cs:827-900)."""
+        if resultSelector is None:
+            raise errors.ArgumentNullException("resultSelector")
+        o, i, keep_o, keep_i = self._join(inner, outerKeySelector, innerKeySelector, N.JOIN_INNER)
+        q = ComputeQueryable(o, self.Accelerator, ((N.OP_ZIP, resultSelector),), i, self._force_jit)
+        q._keep = (keep_o, keep_i)
+        return q
+
+    def SemiJoin(self, inner, outerKeySelector: str | None = None, innerKeySelector: str | None = None) -> "ComputeQueryable":
+        """Outer elements that have at least one match among the inner keys, in source order (JoinType.Semi, JoinKernelGenerator.cs:71-74)."""
+        o, _i, keep_o, _ki = self._join(inner, outerKeySelector, innerKeySelector, N.JOIN_SEMI)
+        q = ComputeQueryable(o, self.Accelerator, (), None, self._force_jit)
+        q._keep = keep_o
+        return q
+
+    def AntiJoin(self, inner, outerKeySelector: str | None = None, innerKeySelector: str | None = None) -> "ComputeQueryable":
+        """Outer elements without a match (JoinType.Anti, JoinKernelGenerator.cs:75-77)."""
+        o, _i, keep_o, _ki = self._join(inner, outerKeySelector, innerKeySelector, N.JOIN_ANTI)
+        q = ComputeQueryable(o, self.Accelerator, (), None, self._force_jit)
+        q._keep = keep_o
+        return q
+
     # ------------------------------------------------------------------ terminals
     def ToArray(self) -> np.ndarray:
         if not self._ops:   # AsComputeQueryable().ToArray(): round trip of the source
@@ -437,6 +558,82 @@ class ComputeQueryable:
             raise errors.ArgumentNullException("predicate")
         head, body = _split_lambda(predicate)
         return self.Count(f"{head} => !({body})") == 0
+
+
+class Grouping:
+    """`source.GroupBy(keySelector)` waiting for its aggregate. Every aggregate returns one numpy array with an entry per
+    distinct key, in order of the key's first occurrence; `Keys()` gives the keys in the same order."""
+
+    def __init__(self, query: ComputeQueryable, key_selector: str | None):
+        self._q, self._sel = query, key_selector
+
+    def _run(self, agg: int, value_selector: str | None):
+        q = self._q
+        acc = q.Accelerator
+        values = q.ToBuffer()
+        n = values.Length
+        keys = q._keys_of(values, self._sel)
+        vals = q._keys_of(values, value_selector)
+        empty = (np.empty(0, keys.dtype), np.empty(0, np.int64), np.empty(0, np.float64), np.empty(0, np.int64), vals.dtype)
+        if n == 0:
+            return empty
+        cap = min(n, 1 << 20)
+        while True:
+            first = acc.Memory.AllocateAsync(cap, np.uint32)
+            counts = acc.Memory.AllocateAsync(cap, np.int64)
+            f64 = acc.Memory.AllocateAsync(cap, np.float64)
+            i64 = acc.Memory.AllocateAsync(cap, np.int64)
+            groups = C.c_int64()
+            st = N.lib().dcb_group_aggregate(acc.handle, dcb_type(keys.dtype), C.c_void_p(keys.GetDeviceMemory()), dcb_type(vals.dtype),
+                                             C.c_void_p(vals.GetDeviceMemory()), n, agg, cap, C.c_void_p(first.GetDeviceMemory()),
+                                             C.c_void_p(counts.GetDeviceMemory()), C.c_void_p(f64.GetDeviceMemory()),
+                                             C.c_void_p(i64.GetDeviceMemory()), C.byref(groups), None)
+            g = int(groups.value)
+            if st == 202 and g > cap:               # more groups than guessed: once more with room for all of them
+                for b in (first, counts, f64, i64):
+                    b.Dispose()
+                cap = g
+                continue
+            N.check(st, acc.handle)
+            break
+        acc.Synchronize()
+        gk = acc.Memory.AllocateAsync(max(g, 1), keys.dtype)
+        N.check(N.lib().dcb_gather(acc.handle, keys.dtype.itemsize, C.c_void_p(keys.GetDeviceMemory()), C.c_void_p(first.GetDeviceMemory()), g,
+                                   C.c_void_p(gk.GetDeviceMemory()), None), acc.handle)
+        out = (gk.CopyToAsync(count=g), counts.CopyToAsync(count=g), f64.CopyToAsync(count=g), i64.CopyToAsync(count=g), vals.dtype)
+        for b in (first, counts, f64, i64, gk, keys, vals):
+            b.Dispose()
+        return out
+
+    def Keys(self) -> np.ndarray:
+        return self._run(N.AGG_COUNT, None)[0]
+
+    def Count(self) -> np.ndarray:
+        return self._run(N.AGG_COUNT, None)[1].astype(np.int32)
+
+    def _typed(self, agg, selector):
+        _k, _c, f, i, dt = self._run(agg, selector)
+        if dt.kind == "f":
+            return f.astype(dt)
+        with np.errstate(over="ignore"):
+            return i.astype(dt)                      # integer sums wrap, as the unchecked C# accumulation does
+
+    def Sum(self, valueSelector: str | None = None) -> np.ndarray:
+        return self._typed(N.AGG_SUM, valueSelector)
+
+    def Min(self, valueSelector: str | None = None) -> np.ndarray:
+        return self._typed(N.AGG_MIN, valueSelector)
+
+    def Max(self, valueSelector: str | None = None) -> np.ndarray:
+        return self._typed(N.AGG_MAX, valueSelector)
+
+    def Average(self, valueSelector: str | None = None) -> np.ndarray:
+        return self._run(N.AGG_AVERAGE, valueSelector)[2]
+
+    def ToDictionary(self, aggregate: str = "Count", valueSelector: str | None = None) -> dict:
+        keys = self.Keys()
+        vals = getattr(self, aggregate)() if aggregate == "Count" else getattr(self, aggregate)(valueSelector)
+        return dict(zip(keys.tolist(), vals.tolist()))
 
 
 def _literal(value, dtype) -> str:

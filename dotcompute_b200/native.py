@@ -23,6 +23,8 @@ OP_SELECT, OP_WHERE, OP_ZIP = 1, 2, 3
 OP_TOARRAY, OP_SUM, OP_MIN, OP_MAX, OP_AVERAGE, OP_COUNT, OP_FIRST_INDEX, OP_LAST_INDEX = 16, 17, 18, 19, 20, 21, 22, 23
 PIPE_FORCE_JIT = 1
 RUN_TAKE = 1
+AGG_COUNT, AGG_SUM, AGG_MIN, AGG_MAX, AGG_AVERAGE = 0, 1, 2, 3, 4
+JOIN_INNER, JOIN_SEMI, JOIN_ANTI = 0, 2, 3
 RES_SAW_NAN, RES_TRUNCATED, RES_TIMEOUT, RES_OVERFLOW = 1, 2, 4, 8
 DEVICE_RESULT_BYTES = 128
 SLOT_FSUM, SLOT_COUNT_F, SLOT_ISUM_LO, SLOT_ISUM_HI, SLOT_COUNT = 0, 1, 2, 3, 4
@@ -104,6 +106,10 @@ PROTOTYPES = {
     "dcb_peer_connect_local": (_i32, [_vp, _i32, _i32, _pp]),
     "dcb_peer_exchange_async": (_i32, [_vp, _vp, _i32, _vp]),
     "dcb_peer_disconnect": (_i32, [_vp]),
+    "dcb_sort_indices": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp, _vp]),
+    "dcb_gather": (_i32, [_vp, _i32, _vp, _vp, _i64, _vp, _vp]),
+    "dcb_group_aggregate": (_i32, [_vp, _i32, _vp, _i32, _vp, _i64, _i32, _i64, _vp, _vp, _vp, _vp, C.POINTER(_i64), _vp]),
+    "dcb_join_indices": (_i32, [_vp, _i32, _vp, _i64, _vp, _i64, _i32, _i64, _vp, _vp, C.POINTER(_i64), _vp]),
     "dcb_compact_noalloc": (_i32, [_i32, C.POINTER(PipelineDesc), _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
     "dcb_kernel_compile": (_i32, [_vp, C.c_char_p, C.c_char_p, _pp]),
     "dcb_kernel_launch": (_i32, [_vp, C.POINTER(_u32), C.POINTER(_u32), _u32, _pp, _vp]),

@@ -360,6 +360,41 @@ dcb_status dcb_peer_connect_local(dcb_ctx* ctx, int32_t world, int32_t rank, voi
 dcb_status dcb_peer_exchange_async(dcb_ctx* ctx, void* d_record, int32_t out_type, void* stream);
 dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
 
+/* ------------------------------------------------------- OrderBy, GroupBy, Join (multi-block) */
+
+/* The three relational operators of the reference's generators, which emit single-block or direct-index kernels
+ * (src/Extensions/DotCompute.Linq/CodeGeneration/CudaKernelGenerator.cs:613-751 OrderBy, :753-825 GroupBy, :827-900 Join;
+ * OrderByKernelGenerator.cs:108, GroupByKernelGenerator.cs:152, JoinKernelGenerator.cs:140-239) with the CPU semantics of
+ * CpuKernelGenerator.cs:475-723. All three work on KEYS the caller has already computed with a fused Select pipeline (the key
+ * selector) and return INDICES into the source, which the caller gathers or feeds to another pipeline (the result selector).
+ * Sizes are limited to 2^32 - 1 elements (indices and counts are 32-bit). Scratch comes from the context's stream-ordered pool.
+ *
+ *   dcb_sort_indices     stable argsort of n keys of type key_type (DCB_T_*; floating keys order as .NET's comparer does: NaN
+ *                        first, -0 equal to +0); descending != 0 sorts descending, ties still in source order. A least-
+ *                        significant-digit radix sort, 8 bits a pass, over any number of blocks.
+ *   dcb_gather           dst[i] = src[indices[i]] for elements of 1, 2, 4 or 8 bytes.
+ *   dcb_group_aggregate  groups n (key, value) pairs by key; aggregate = DCB_AGG_*. One output per group, in order of first
+ *                        occurrence of the key (the order a Dictionary enumerates in, CpuKernelGenerator.cs:620-633):
+ *                        d_out_first[g] = index of the group's first element (its key is keys[that]), d_out_counts[g], and
+ *                        the aggregate as double in d_out_f64[g] (Sum / Min / Max / Average; integer values also exactly in
+ *                        d_out_i64[g] for Sum / Min / Max). Floating sums accumulate in fp64. *out_groups = number of groups;
+ *                        DCB_ERR_OUTPUT_TOO_SMALL if it exceeds out_cap (then call again with larger outputs).
+ *   dcb_join_indices     equi-join of outer and inner keys. DCB_JOIN_INNER: one (outer index, inner index) pair per match,
+ *                        ordered by outer index, then inner index (the order of Enumerable.Join); DCB_JOIN_SEMI / ANTI: the
+ *                        outer indices with at least one / with no match (d_inner_out may be NULL). With d_outer_out NULL
+ *                        only *out_pairs is computed (to size the outputs). */
+enum { DCB_AGG_COUNT = 0, DCB_AGG_SUM = 1, DCB_AGG_MIN = 2, DCB_AGG_MAX = 3, DCB_AGG_AVERAGE = 4 };
+enum { DCB_JOIN_INNER = 0, DCB_JOIN_SEMI = 2, DCB_JOIN_ANTI = 3 };   /* values of JoinKernelGenerator.JoinType (:67-77) */
+dcb_status dcb_sort_indices(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int64_t n, int32_t descending,
+                            uint32_t* d_indices, void* stream);
+dcb_status dcb_gather(dcb_ctx* ctx, int32_t elem_bytes, const void* d_src, const uint32_t* d_indices, int64_t n, void* d_dst, void* stream);
+dcb_status dcb_group_aggregate(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int32_t value_type, const void* d_values, int64_t n,
+                               int32_t aggregate, int64_t out_cap, uint32_t* d_out_first, int64_t* d_out_counts, double* d_out_f64,
+                               int64_t* d_out_i64, int64_t* out_groups, void* stream);
+dcb_status dcb_join_indices(dcb_ctx* ctx, int32_t key_type, const void* d_outer_keys, int64_t n_outer, const void* d_inner_keys,
+                            int64_t n_inner, int32_t join_kind, int64_t out_cap, uint32_t* d_outer_out, uint32_t* d_inner_out,
+                            int64_t* out_pairs, void* stream);
+
 /* ------------------------------------------------------------- no device allocation */
 
 /* Tiles the fixed scratch of dcb_compact_noalloc holds. A tile is 8192 elements for 4-byte inputs and outputs

@@ -78,6 +78,50 @@ class Enumerable:
             order = np.lexsort((np.arange(keys.size), -keys.astype(np.int64) if keys.dtype.itemsize < 8 else ~keys))
         return Enumerable(self.data[order])
 
+    def GroupAggregate(self, key, aggregate, value=None):
+        """GroupBy(key) followed by an aggregate, as the reference's CPU generator writes it (CpuKernelGenerator.cs:544-659): a
+        dictionary filled in one sequential pass and enumerated in insertion order. Returns (keys, aggregates). Sum adds in
+        the value type with wrap-around for integers; floating sums are returned in double (the comparison carries a tolerance)."""
+        keys = np.asarray(key(self.data)) if key is not None else self.data
+        vals = np.asarray(value(self.data)) if value is not None else self.data
+        groups = {}
+        for i in range(keys.size):
+            k = keys[i].item()
+            if isinstance(k, float) and k != k:
+                k = "nan"                                     # float.Equals(NaN, NaN) is true: one group
+            groups.setdefault(k, []).append(i)
+        out_keys, out = [], []
+        for k, idx in groups.items():
+            v = vals[idx]
+            out_keys.append(keys[idx[0]])
+            if aggregate == "Count":
+                out.append(len(idx))
+            elif aggregate == "Sum":
+                out.append(v.astype(np.float64).sum() if v.dtype.kind == "f" else int(v.astype(np.int64).sum()))
+            elif aggregate == "Min":
+                out.append(v.min())
+            elif aggregate == "Max":
+                out.append(v.max())
+            else:
+                out.append(v.astype(np.float64).sum() / len(idx))
+        return np.asarray(out_keys, dtype=keys.dtype), out
+
+    def Join(self, inner, outer_key, inner_key, result):
+        """Enumerable.Join: for every outer element in order, every inner element with an equal key in inner order."""
+        b = inner.data if isinstance(inner, Enumerable) else np.asarray(inner).reshape(-1)
+        ok = np.asarray(outer_key(self.data)) if outer_key is not None else self.data
+        ik = np.asarray(inner_key(b)) if inner_key is not None else b
+        lookup = {}
+        for j in range(ik.size):
+            lookup.setdefault(ik[j].item(), []).append(j)
+        oi, ii = [], []
+        for i in range(ok.size):
+            for j in lookup.get(ok[i].item(), ()):
+                oi.append(i)
+                ii.append(j)
+        oi, ii = np.asarray(oi, dtype=np.int64), np.asarray(ii, dtype=np.int64)
+        return Enumerable(np.asarray(result(self.data[oi], b[ii])))
+
     def First(self, pred=None):
         e = self.Where(pred) if pred else self
         if e.data.size == 0:
