@@ -187,6 +187,100 @@ def measure_config(acc, name, steps, warmup, log2n=None, check=True):
             "dtype": str(host[0].dtype)}
 
 
+def measure_relational(acc, steps=5):
+    """OrderBy, GroupBy(Sum) and Join through the C ABI on device-resident keys: K timed calls each (CUDA events), the result
+    of the last one against numpy's stable sort / a dictionary pass / a sequential join. Bytes are what the multi-block
+    algorithms must move: a radix pass reads the keys twice and moves (key, index) once."""
+    import torch
+    from dotcompute_b200 import native as N
+    out = {}
+    peak, _kind = measured_peak_gbs()
+    dev = "cuda"
+
+    def timed(fn):
+        fn(); torch.cuda.synchronize()
+        ts = []
+        for _ in range(steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    # OrderBy: 2^26 float32 keys, stable argsort + gather
+    n = 1 << 26
+    x = _rng(41).random(n, dtype=np.float32)
+    dx = torch.from_numpy(x).to(dev)
+    idx = torch.empty(n, dtype=torch.int32, device=dev)
+    srt = torch.empty_like(dx)
+
+    def sort_step():
+        N.check(N.lib().dcb_sort_indices(acc.handle, N.T_F32, C.c_void_p(dx.data_ptr()), n, 0, C.c_void_p(idx.data_ptr()), C.c_void_p(1)), acc.handle)
+        N.check(N.lib().dcb_gather(acc.handle, 4, C.c_void_p(dx.data_ptr()), C.c_void_p(idx.data_ptr()), n, C.c_void_p(srt.data_ptr()), C.c_void_p(1)), acc.handle)
+    ms = timed(sort_step)
+    got = srt.cpu().numpy()
+    bytes_per = 12 + 4 * (4 + 8 + 8) + 4 + 12          # prepare, four passes, copy of the indices, gather
+    out["orderby-f32-2p26"] = {"what": "OrderBy() over 2^26 float32: stable 4-pass radix argsort + gather", "n_elements": n, "ms": ms,
+                               "elements_per_s": n / (ms * 1e-3), "bytes_per_element": bytes_per,
+                               "achieved_gbs": n * bytes_per / (ms * 1e-3) / 1e9, "frac": n * bytes_per / (ms * 1e-3) / 1e9 / peak,
+                               "parity": bool(np.array_equal(got, np.sort(x, kind="stable")))}
+    del dx, idx, srt
+    # GroupBy: 2^26 int32 values, key = v % 1000, Sum per key
+    v = _rng(42).integers(0, 1_000_000, n, dtype=np.int32)
+    k = (v % 1000).astype(np.int32)
+    dv, dk = torch.from_numpy(v).to(dev), torch.from_numpy(k).to(dev)
+    cap = 4096
+    first = torch.empty(cap, dtype=torch.int32, device=dev)
+    cnt = torch.empty(cap, dtype=torch.int64, device=dev)
+    f64 = torch.empty(cap, dtype=torch.float64, device=dev)
+    i64 = torch.empty(cap, dtype=torch.int64, device=dev)
+    groups = C.c_int64()
+
+    def group_step():
+        N.check(N.lib().dcb_group_aggregate(acc.handle, N.T_I32, C.c_void_p(dk.data_ptr()), N.T_I32, C.c_void_p(dv.data_ptr()), n, N.AGG_SUM, cap,
+                                            C.c_void_p(first.data_ptr()), C.c_void_p(cnt.data_ptr()), C.c_void_p(f64.data_ptr()),
+                                            C.c_void_p(i64.data_ptr()), C.byref(groups), C.c_void_p(1)), acc.handle)
+    ms = timed(group_step)
+    g = int(groups.value)
+    order = np.unique(k, return_index=True)[1]
+    keys_first = k[np.sort(order)]
+    sums = np.bincount(k, weights=None, minlength=1000)                      # counts
+    want_sum = np.zeros(1000, dtype=np.int64)
+    np.add.at(want_sum, k, v.astype(np.int64))
+    ok = g == keys_first.size and np.array_equal(k[first.cpu().numpy()[:g].astype(np.int64)], keys_first) and \
+        np.array_equal(i64.cpu().numpy()[:g], want_sum[keys_first]) and np.array_equal(cnt.cpu().numpy()[:g], sums[keys_first])
+    bytes_per = 12 + 4 * 20 + 4 + 4 + 8 + 12                                 # sort of (key, index), head flags, scan, values through the index
+    out["groupby-sum-i32-2p26"] = {"what": "GroupBy(v % 1000).Sum() over 2^26 int32 (1000 groups, first-occurrence order)", "n_elements": n,
+                                   "ms": ms, "elements_per_s": n / (ms * 1e-3), "bytes_per_element": bytes_per,
+                                   "achieved_gbs": n * bytes_per / (ms * 1e-3) / 1e9, "frac": n * bytes_per / (ms * 1e-3) / 1e9 / peak,
+                                   "parity": bool(ok)}
+    del dv, dk
+    # Join: 2^24 outer keys against 2^20 inner keys (int64), inner join pairs in Enumerable.Join order
+    no, ni = 1 << 24, 1 << 20
+    ok_ = _rng(43).integers(0, 1 << 21, no, dtype=np.int64)
+    ik_ = _rng(44).integers(0, 1 << 21, ni, dtype=np.int64)
+    do, di = torch.from_numpy(ok_).to(dev), torch.from_numpy(ik_).to(dev)
+    pairs = C.c_int64()
+    N.check(N.lib().dcb_join_indices(acc.handle, N.T_I64, C.c_void_p(do.data_ptr()), no, C.c_void_p(di.data_ptr()), ni, N.JOIN_INNER, 0, None, None,
+                                     C.byref(pairs), C.c_void_p(1)), acc.handle)
+    m = int(pairs.value)
+    oo = torch.empty(max(m, 1), dtype=torch.int32, device=dev)
+    io = torch.empty(max(m, 1), dtype=torch.int32, device=dev)
+
+    def join_step():
+        N.check(N.lib().dcb_join_indices(acc.handle, N.T_I64, C.c_void_p(do.data_ptr()), no, C.c_void_p(di.data_ptr()), ni, N.JOIN_INNER, m,
+                                         C.c_void_p(oo.data_ptr()), C.c_void_p(io.data_ptr()), C.byref(pairs), C.c_void_p(1)), acc.handle)
+    ms = timed(join_step)
+    go, gi = oo.cpu().numpy().astype(np.int64), io.cpu().numpy().astype(np.int64)
+    srt_i = np.argsort(ik_, kind="stable")
+    lo, hi = np.searchsorted(ik_[srt_i], ok_, "left"), np.searchsorted(ik_[srt_i], ok_, "right")
+    want_o = np.repeat(np.arange(no), hi - lo)
+    ok = m == int((hi - lo).sum()) and np.array_equal(go, want_o) and bool(np.all(ok_[go] == ik_[gi])) and \
+        bool(np.all((np.diff(gi) > 0) | (np.diff(go) > 0)))                  # inner indices ascend inside one outer element
+    out["join-inner-i64-2p24x2p20"] = {"what": "Join of 2^24 outer and 2^20 inner int64 keys, pairs in Enumerable.Join order", "n_elements": no,
+                                       "pairs": m, "ms": ms, "elements_per_s": no / (ms * 1e-3), "parity": bool(ok)}
+    return out
+
+
 def run_config(args) -> int:
     """One of the secondary configurations on its own: one JSON line in the shape of the headline's."""
     from dotcompute_b200 import CudaAccelerator
@@ -843,6 +937,7 @@ def main() -> int:
                 cfgs[name] = {k: m[k] for k in ("what", "n_elements", "ms", "elements_per_s", "bytes_per_element", "selectivity",
                                                  "achieved_gbs", "frac", "parity", "precompiled_kernel", "l2")}
             line["configs"] = cfgs
+            line["relational"] = measure_relational(acc)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -72,6 +72,13 @@ extern "C" dcb_status dcb_compact_noalloc(int32_t device, const dcb_pipeline_des
     const dcb_builtin_entry* b = dcb_builtin_find(info.key.c_str());
     if (!b) return fail(DCB_ERR_NOT_SUPPORTED, "this query is not in the precompiled table; building it would allocate");
 
+    // The caller's current device is put back on every way out: with no context object, changing it behind the caller's
+    // back would redirect the caller's next CUDA call.
+    struct DeviceGuard {
+        int prev = -1;
+        DeviceGuard() { if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; (void)cudaGetLastError(); } }
+        ~DeviceGuard() { if (prev >= 0) (void)cudaSetDevice(prev); }
+    } restore_device;
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(DCB_ERR_NO_DEVICE, cudaGetErrorString(e)); }
     cudaStream_t s = (cudaStream_t)stream;   // NULL is the default stream here: there is no context object to own one

@@ -14,7 +14,9 @@
  *   - One dcb_ctx drives one GPU. Every entry point makes that GPU current itself, so
  *     it may be called from any thread (managed continuations hop threads; the
  *     reference calls cuCtxSetCurrent before each native call for the same reason,
- *     src/Backends/DotCompute.Backends.CUDA/Kernels/CudaKernelLauncher.cs:220).
+ *     src/Backends/DotCompute.Backends.CUDA/Kernels/CudaKernelLauncher.cs:220). A compiled
+ *     pipeline may be run from several threads and streams at once: the library
+ *     serialises what they share and keeps device scratch per (pipeline, stream).
  *   - Sizes and element counts are int64_t / size_t throughout. The reference uses
  *     int lengths (src/Core/DotCompute.Abstractions/Interfaces/IUnifiedMemoryBuffer.cs:20,
  *     src/Extensions/DotCompute.Linq/CodeGeneration/RuntimeExecutor.cs:275), which
@@ -397,8 +399,9 @@ dcb_status dcb_join_indices(dcb_ctx* ctx, int32_t key_type, const void* d_outer_
 
 /* ------------------------------------------------------------- no device allocation */
 
-/* Tiles the fixed scratch of dcb_compact_noalloc holds. A tile is 8192 elements for 4-byte inputs and outputs
- * (4096 for 8-byte ones), so float queries up to 2^29 elements fit. */
+/* Tiles the fixed scratch of dcb_compact_noalloc holds. With every pointer 16-byte aligned a tile is 8192 elements for
+ * 4-byte inputs and outputs (4096 for 8-byte ones), so float queries up to 2^29 elements fit; with an unaligned pointer
+ * the scalar kernel runs, whose tile is 2048 elements (2^27 elements per call). The refusal's text names the limit. */
 #define DCB_NOALLOC_MAX_TILES 65536
 
 /* Stable Where [-> Select] -> ToArray for callers that must not allocate device memory. (No counterpart in the
@@ -417,7 +420,8 @@ dcb_status dcb_join_indices(dcb_ctx* ctx, int32_t key_type, const void* d_outer_
  *     capture.
  * in0 / in1 / out / d_record are device pointers supplied by the caller; d_record receives DCB_DEVICE_RESULT_BYTES
  * (survivor count in slot DCB_SLOT_COUNT, DCB_RES_* bits in slot DCB_SLOT_FLAGS). The call only enqueues work on `stream`
- * (NULL = the default stream). There is no dcb_ctx: `device` is the CUDA device ordinal. */
+ * (NULL = the default stream). There is no dcb_ctx: `device` is the CUDA device ordinal; the call makes it current while
+ * it works and puts the caller's current device back before it returns. */
 dcb_status dcb_compact_noalloc(int32_t device, const dcb_pipeline_desc* desc, const void* in0, const void* in1,
                                int64_t n, void* out, int64_t out_cap, void* d_record, void* stream);
 
