@@ -79,6 +79,7 @@ struct dcb_ctx {
     int opt_blocks_per_sm = 0;             // DCB_OPT_BLOCKS_PER_SM (0 = what fits)
     int opt_withhold_first_count = 0;      // DCB_OPT_WITHHOLD_FIRST_COUNT
     int opt_cache_max = 100;               // DCB_OPT_CACHE_MAX_ENTRIES (the reference: new KernelCache(maxEntries: 100))
+    int opt_overlap_launches = 0;          // DCB_OPT_OVERLAP_LAUNCHES
     uint64_t cache_clock = 0;              // use counter behind the cache's least-recently-used order
     std::mutex host_mu;                    // serialises dcb_pipeline_run_host: the staging buffers belong to the context
     // Staging ring of the host path: kRingIn chunk buffers per input, kRingOut chunk buffers for the output, with the
@@ -545,6 +546,7 @@ extern "C" dcb_status dcb_set_option(dcb_ctx* ctx, int32_t option, int64_t value
         case DCB_OPT_CACHE_MAX_ENTRIES:
             NEED(ctx, value >= 1 && value <= (1 << 20), "DCB_OPT_CACHE_MAX_ENTRIES takes 1 to 2^20");
             ctx->opt_cache_max = (int)value; return DCB_OK;
+        case DCB_OPT_OVERLAP_LAUNCHES: ctx->opt_overlap_launches = value != 0; return DCB_OK;
         default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "unknown option %d", (int)option);
     }
 }
@@ -561,6 +563,7 @@ extern "C" dcb_status dcb_get_option(dcb_ctx* ctx, int32_t option, int64_t* out_
         case DCB_OPT_WITHHOLD_FIRST_COUNT: *out_value = ctx->opt_withhold_first_count; return DCB_OK;
         case DCB_OPT_CACHE_MAX_ENTRIES: *out_value = ctx->opt_cache_max; return DCB_OK;
         case DCB_OPT_CACHE_ENTRIES: *out_value = (int64_t)ctx->cache.size(); return DCB_OK;
+        case DCB_OPT_OVERLAP_LAUNCHES: *out_value = ctx->opt_overlap_launches; return DCB_OK;
         default: return set_err(ctx, DCB_ERR_INVALID_ARGUMENT, "unknown option %d", (int)option);
     }
 }
@@ -1008,6 +1011,19 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
         unsigned int* ticket = scp->words;
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&scp->partials, (void*)&ticket, (void*)&res};
         if (launches) *launches += 1;
+        if (ctx->opt_overlap_launches) {
+            // Programmatic dependent launch: this kernel may begin while the kernel before it on the stream is still running
+            // (it reads its input at once and touches scratch and record only after its grid-dependency wait).
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kBlock); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            CU(ctx, cudaLaunchKernelExC(&cfg, fn, args));
+            ctx->launches += 1;
+            return DCB_OK;
+        }
         return launch(ctx, fn, grid, args, s);
     }
 }

@@ -390,6 +390,13 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     __shared__ Partial s_part[BLOCK / 32];
     __shared__ bool s_last;
 
+    // Programmatic dependent launch (only when the host asked for it at launch; otherwise both instructions do nothing):
+    // the next kernel on the stream may start while this one runs, and this one may have started while its predecessor
+    // was still running. What such a pair shares - the partials, the ticket, the record - is touched only after the wait
+    // below, which returns once the predecessor has completed and its writes are visible; the input is read before it, so
+    // the host sets the launch attribute only when the caller has said the inputs are not written by the work just before.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     Acc<O, RED> acc; acc.init();
     // Whole tiles of BLOCK*UNROLL packs are dealt round-robin, the same number to every block, so that at any moment all
     // blocks read from one compact window that moves through the array (measured faster than giving each block its own
@@ -452,6 +459,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     }
 
     acc = block_reduce<O, RED, BLOCK>(acc, s_part);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
         Partial p; acc.to_partial(p);
         partial_store(partials + blockIdx.x, p);
@@ -843,6 +851,14 @@ __device__ __forceinline__ bool mbar_try_wait(u64* bar, u32 parity) {
     return ok != 0;
 }
 // Global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completing on `bar`.
+// The same with a suspend-time hint: the hardware may keep the thread asleep, off the issue slots, for up to `hint_ns`
+// or until the phase completes, whichever comes first.
+__device__ __forceinline__ bool mbar_try_wait_hint(u64* bar, u32 parity, u32 hint_ns) {
+    u32 ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_global, u32 bytes, u64* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_addr(dst_smem)), "l"(src_global), "r"(bytes), "r"(smem_addr(bar)) : "memory");
@@ -1128,16 +1144,16 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
 
     // Bounded wait for phase `parity` of one of the block's barriers: false when another warp of the block gave up or
     // the fixed time limit passed (one try may itself suspend the thread for a while).
-    // A waiting warp sleeps between tries: a warp that spins takes issue slots from the very warps it is waiting for.
-#ifndef DCB_STREAM_WAIT_SLEEP_NS
-#define DCB_STREAM_WAIT_SLEEP_NS 100
+    // A waiting warp is put to sleep by the barrier itself (a try with a suspend-time hint: it wakes when the phase
+    // completes or the hint runs out): a warp that spins takes issue slots from the very warps it is waiting for.
+#ifndef DCB_STREAM_WAIT_HINT_NS
+#define DCB_STREAM_WAIT_HINT_NS 2000
 #endif
     auto wait = [&](u64* bar, u32 parity, bool heed_dead) -> bool {
         if (mbar_try_wait(bar, parity)) return true;
         const i64 t0 = clock64();
         for (u32 i = 0; i < (1u << 30); ++i) {
-            if (DCB_STREAM_WAIT_SLEEP_NS > 0) __nanosleep(DCB_STREAM_WAIT_SLEEP_NS);
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait_hint(bar, parity, DCB_STREAM_WAIT_HINT_NS)) return true;
             if (heed_dead && *dead) return false;
             if ((i & 15u) == 15u && clock64() - t0 > DCB_STREAM_WAIT_CYCLES) return false;
         }

@@ -29,7 +29,7 @@ RES_SAW_NAN, RES_TRUNCATED, RES_TIMEOUT, RES_OVERFLOW = 1, 2, 4, 8
 DEVICE_RESULT_BYTES = 128
 SLOT_FSUM, SLOT_COUNT_F, SLOT_ISUM_LO, SLOT_ISUM_HI, SLOT_COUNT = 0, 1, 2, 3, 4
 SLOT_FMIN, SLOT_FMAX, SLOT_IMIN, SLOT_IMAX, SLOT_FLAGS, SLOT_OFFSET, SLOT_LOCAL_COUNT, SLOT_NSLOTS = 5, 6, 7, 8, 9, 10, 11, 16
-OPT_COMPACT_KERNEL, OPT_FORCE_SCALAR, OPT_BLOCKS_PER_SM, OPT_WITHHOLD_FIRST_COUNT, OPT_CACHE_MAX_ENTRIES, OPT_CACHE_ENTRIES = 1, 2, 3, 4, 5, 6
+OPT_COMPACT_KERNEL, OPT_FORCE_SCALAR, OPT_BLOCKS_PER_SM, OPT_WITHHOLD_FIRST_COUNT, OPT_CACHE_MAX_ENTRIES, OPT_CACHE_ENTRIES, OPT_OVERLAP_LAUNCHES = 1, 2, 3, 4, 5, 6, 7
 
 
 class Op(C.Structure):

@@ -216,7 +216,12 @@ enum {
                                          the survivor count of their first tile to themselves, so every bounded look-back
                                          wait for it runs out and the run ends with DCB_ERR_TIMEOUT (no fault, no trap)   */
     DCB_OPT_CACHE_MAX_ENTRIES = 5,    /* compiled pipelines kept per context (default 100, least recently used first out) */
-    DCB_OPT_CACHE_ENTRIES = 6         /* read-only: compiled pipelines in the cache now                                 */
+    DCB_OPT_CACHE_ENTRIES = 6,        /* read-only: compiled pipelines in the cache now                                 */
+    DCB_OPT_OVERLAP_LAUNCHES = 7      /* 1 = reductions are launched with programmatic stream serialisation: a query may start
+                                         reading its input while the kernel before it on the same stream is still finishing
+                                         (scratch and record are touched only after the grid-dependency wait). The caller
+                                         thereby states that a query's INPUT is not written by the work enqueued just before it
+                                         on that stream. Hides launch latency and ramp-up between back-to-back queries.   */
 };
 dcb_status dcb_set_option(dcb_ctx* ctx, int32_t option, int64_t value);
 dcb_status dcb_get_option(dcb_ctx* ctx, int32_t option, int64_t* out_value);

@@ -221,3 +221,36 @@ def test_host_arrays_larger_than_the_staging_ring(built_library):
         assert AsComputeQueryable(np.empty(0, F), acc).Where("x => x > 0.5f").ToArray().size == 0
     finally:
         acc.Dispose()
+
+
+def test_overlapped_launches_give_the_same_results(built_library):
+    """DCB_OPT_OVERLAP_LAUNCHES: back-to-back reductions on one stream, each allowed to start while the one before it is
+    still finishing (scratch and record are touched only after the grid-dependency wait). 60 queries of three kinds over
+    static inputs, every record equal to the one the same query leaves without the option."""
+    import torch
+    acc = CudaAccelerator(0)
+    try:
+        x = rng(95).random(9_000_001, dtype=F)
+        buf = acc.Memory.AllocateAndCopyAsync(x)
+        ops = ((N.OP_WHERE, "x => x > 0.5f"), (N.OP_SELECT, "x => x * x + 3f"))
+        pipes = [CompiledPipeline(acc, dcb_type(F), 0, ops + ((t, None),)) for t in (N.OP_SUM, N.OP_MAX, N.OP_COUNT)]
+        recs = torch.zeros((60, 16), dtype=torch.int64, device="cuda")
+
+        def run_all():
+            recs.zero_()
+            torch.cuda.synchronize()
+            for i in range(60):
+                p = pipes[i % 3]
+                N.check(N.lib().dcb_pipeline_run_async(p.handle, C.c_void_p(buf.GetDeviceMemory()), None, x.size - (i % 7), None, 0,
+                                                       C.c_void_p(recs[i].data_ptr()), None, None), acc.handle)
+            acc.Synchronize()
+            return recs.cpu().numpy()[:, :10].copy()
+
+        plain = run_all()
+        acc.SetOption(N.OPT_OVERLAP_LAUNCHES, 1)
+        assert acc.GetOption(N.OPT_OVERLAP_LAUNCHES) == 1
+        for _ in range(3):
+            assert np.array_equal(run_all(), plain)
+        buf.Dispose()
+    finally:
+        acc.Dispose()
