@@ -1071,8 +1071,9 @@ extern "C" dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, co
                 r->f64 = (out_type == DCB_T_F32) ? (double)round_f32(v) : v;   // one rounding, as (float)sum in the BCL
                 return DCB_OK;
             }
-            // integer Sum is checked in System.Linq: leaving the element type's range is an error
-            bool overflow = d->isum_hi != ((d->isum_lo < 0) ? -1 : 0);
+            // integer Sum is checked in System.Linq: a running sum that leaves the element type's range is an error
+            // (the Sum kernel flags it; Average adds in long, where only the total can leave the range)
+            bool overflow = d->isum_hi != ((d->isum_lo < 0) ? -1 : 0) || (!avg && (fl & dcb::FLAG_OVERFLOW) != 0);
             if (out_type == DCB_T_I32 && !avg) overflow = overflow || d->isum_lo > 2147483647LL || d->isum_lo < -2147483648LL;
             if (overflow) { r->flags |= DCB_RES_OVERFLOW; return set_err(ctx, DCB_ERR_OVERFLOW, "integer Sum overflowed %s", dcbt::csharp_name(out_type)); }
             if (avg) r->f64 = (double)d->isum_lo / (double)d->count;
@@ -1172,6 +1173,28 @@ void fold_records(const dcbt::ChainInfo& I, const dcb::DeviceResult* recs, int n
             out->imax = std::max<int64_t>(out->imax, recs[i].imax + (int64_t)i * chunk);
         }
         out->count_f = (double)out->count;
+        return;
+    }
+    if (I.checked_sum) {
+        // running-sum range over the chunks, in chunk order: (s, lo, hi) of a chunk is relative to the chunk's start
+        typedef __int128 wide;
+        auto w = [](int64_t lo, int64_t hi) { return (wide)(((unsigned __int128)(uint64_t)hi << 64) | (uint64_t)lo); };
+        wide s = 0, lo = 0, hi = 0;
+        uint64_t flags = 0;
+        for (int i = 0; i < n; ++i) {
+            const dcb::DeviceResult& r = recs[i];
+            const wide rs = w(r.isum_lo, r.isum_hi);
+            wide rlo = w(r.pad[0], r.pad[1]), rhi = w(r.pad[2], r.pad[3]);
+            if (!(r.flags & dcb::FLAG_PREFIX)) { rlo = rs < 0 ? rs : 0; rhi = rs > 0 ? rs : 0; }   // an empty chunk's record
+            lo = std::min(lo, s + rlo); hi = std::max(hi, s + rhi); s += rs;
+            flags |= r.flags;
+        }
+        const wide mn = I.out_type == DCB_T_I32 ? (wide)INT32_MIN : (wide)INT64_MIN, mx = I.out_type == DCB_T_I32 ? (wide)INT32_MAX : (wide)INT64_MAX;
+        out->isum_lo = (int64_t)(uint64_t)(unsigned __int128)s; out->isum_hi = (int64_t)(uint64_t)((unsigned __int128)s >> 64);
+        out->pad[0] = (int64_t)(uint64_t)(unsigned __int128)lo; out->pad[1] = (int64_t)(uint64_t)((unsigned __int128)lo >> 64);
+        out->pad[2] = (int64_t)(uint64_t)(unsigned __int128)hi; out->pad[3] = (int64_t)(uint64_t)((unsigned __int128)hi >> 64);
+        out->flags = (flags & ~(uint64_t)dcb::FLAG_OVERFLOW) | dcb::FLAG_PREFIX | ((lo < mn || hi > mx) ? (uint64_t)dcb::FLAG_OVERFLOW : 0);
+        out->count = 0; out->count_f = 0;
         return;
     }
     for (int i = 1; i < n; ++i) {
@@ -1457,6 +1480,7 @@ extern "C" dcb_status dcb_peer_exchange_async(dcb_ctx* ctx, void* d_record, int3
     unsigned long long tag = 0;
     if (out_type == DCB_T_F32 || out_type == DCB_T_F64) tag |= dcb::SLOT_IS_FP;
     if (out_type == DCB_T_U64) tag |= dcb::SLOT_IS_U64;
+    if (out_type == DCB_T_I32) tag |= dcb::SLOT_IS_I32;
     peer_exchange_kernel<<<1, 32, 0, pick(ctx, stream)>>>(ctx->peers, (dcb::DeviceResult*)d_record, tag);
     CU(ctx, cudaGetLastError());
     ctx->launches += 1;

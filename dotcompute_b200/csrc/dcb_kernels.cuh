@@ -50,7 +50,8 @@ __device__ __forceinline__ void memcpy_bits(U& dst, const T& src) {
 enum : int { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8, RED_FIRST = 16, RED_LAST = 32 };   // FIRST / LAST: smallest / largest index of a surviving element
 
 // Flag bits in the record (low bits match DCB_RES_* of the C ABI).
-enum : u32 { FLAG_SAW_NAN = 1u, FLAG_TRUNCATED = 2u, FLAG_TIMEOUT = 4u, FLAG_OVERFLOW = 8u, FLAG_SAW_NUMBER = 16u };
+enum : u32 { FLAG_SAW_NAN = 1u, FLAG_TRUNCATED = 2u, FLAG_TIMEOUT = 4u, FLAG_OVERFLOW = 8u, FLAG_SAW_NUMBER = 16u,
+             FLAG_PREFIX = 32u };   // PREFIX: slots 12..15 hold the smallest and the largest running sum (checked integer Sum)
 
 // The record a run leaves in device memory: 16 eight-byte slots (see DCB_SLOT_* in dcb200.h).
 struct __align__(16) DeviceResult {
@@ -66,7 +67,7 @@ struct __align__(16) DeviceResult {
     u64 flags;       // 9
     i64 offset;      // 10: after an exchange between GPUs: survivors (elements counted) on lower ranks; else 0
     i64 local_count; // 11: after an exchange: this GPU's own count (slot 4 then holds the total); else equal to slot 4
-    i64 pad[4];
+    i64 pad[4];      // 12..15: checked integer Sum: smallest running sum (low, high word), largest running sum (low, high word)
 };
 
 // Per-block partial of a reduction, also the shared-memory exchange format.
@@ -497,6 +498,287 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         res->flags = p.flags;
         res->offset = 0; res->local_count = p.count;
         *ticket = 0;   // ready for the next launch on this stream
+    }
+}
+
+// ------------------------------------------------------------------ checked integer Sum: the range of the running sum
+// Enumerable.Sum(int) and Sum(long) add in a checked context, element by element in source order: the call throws as soon
+// as a *running* sum leaves the element type's range, even if later elements would bring the total back. So the kernel
+// needs, beside the total, the smallest and the largest running sum. Per segment that is a triple (s, lo, hi) with lo and
+// hi relative to the segment's start and counting the empty prefix (lo <= 0 <= hi); two adjacent segments combine as
+// (s1 + s2, min(lo1, s1 + lo2), max(hi1, s1 + hi2)) - associative, not commutative, so everything below keeps source order.
+// Wide arithmetic: 64 bits for elements of up to 32 bits, 128 bits for 64-bit elements; neither can wrap for n < 2^63.
+struct Wide128 {
+    u64 lo; i64 hi;
+    __device__ __forceinline__ Wide128() {}
+    __device__ __forceinline__ explicit Wide128(i64 v) : lo((u64)v), hi(v < 0 ? -1 : 0) {}
+    __device__ __forceinline__ Wide128 operator+(const Wide128& o) const {
+        Wide128 r; r.lo = lo + o.lo; r.hi = hi + o.hi + (r.lo < lo ? 1 : 0); return r;
+    }
+    __device__ __forceinline__ bool operator<(const Wide128& o) const { return hi < o.hi || (hi == o.hi && lo < o.lo); }
+};
+template <typename O> struct prefix_wide { typedef i64 type; };
+template <> struct prefix_wide<long long> { typedef Wide128 type; };
+__device__ __forceinline__ i64 wide_shfl_xor(i64 v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+__device__ __forceinline__ Wide128 wide_shfl_xor(const Wide128& v, int m) {
+    Wide128 r; r.lo = __shfl_xor_sync(0xffffffffu, v.lo, m); r.hi = __shfl_xor_sync(0xffffffffu, v.hi, m); return r;
+}
+__device__ __forceinline__ u64 wide_low(i64 v) { return (u64)v; }
+__device__ __forceinline__ i64 wide_high(i64 v) { return v < 0 ? -1 : 0; }
+__device__ __forceinline__ u64 wide_low(const Wide128& v) { return v.lo; }
+__device__ __forceinline__ i64 wide_high(const Wide128& v) { return v.hi; }
+__device__ __forceinline__ void wide_set(i64& w, u64 lo, i64) { w = (i64)lo; }
+__device__ __forceinline__ void wide_set(Wide128& w, u64 lo, i64 hi) { w.lo = lo; w.hi = hi; }
+
+template <typename W>
+struct PrefixTriple {
+    W s, lo, hi;
+    __device__ __forceinline__ void zero() { s = W(0); lo = W(0); hi = W(0); }
+    __device__ __forceinline__ void push(i64 v) {            // one more element at the end
+        s = s + W(v);
+        if (s < lo) lo = s;
+        if (hi < s) hi = s;
+    }
+    __device__ __forceinline__ void append(const PrefixTriple& b) {   // `b` is the segment right after this one
+        const W l = s + b.lo, h = s + b.hi;
+        if (l < lo) lo = l;
+        if (hi < h) hi = h;
+        s = s + b.s;
+    }
+};
+// One lane's CNT consecutive values. When all of them are small enough for every running sum to fit the element type
+// itself, the arithmetic is done in that type (a third of the instructions); else in the wide type.
+template <typename O, int CNT>
+__device__ __forceinline__ void lane_prefix(const O (&v)[CNT], PrefixTriple<typename prefix_wide<O>::type>& t) {
+    typedef typename prefix_wide<O>::type W;
+    constexpr int LOG2 = CNT <= 1 ? 0 : CNT <= 2 ? 1 : CNT <= 4 ? 2 : CNT <= 8 ? 3 : CNT <= 16 ? 4 : CNT <= 32 ? 5 : CNT <= 64 ? 6 : 7;
+    static_assert(CNT <= 128, "too many elements per lane");
+    if constexpr (sizeof(O) == 4) {
+        u32 m = 0;
+#pragma unroll
+        for (int i = 0; i < CNT; ++i) m |= (u32)((int)v[i] ^ ((int)v[i] >> 31));      // magnitude bits of every value
+        if (m < (1u << (31 - LOG2))) {
+            int s = 0, lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < CNT; ++i) { s += (int)v[i]; lo = s < lo ? s : lo; hi = s > hi ? s : hi; }
+            t.s = W((i64)s); t.lo = W((i64)lo); t.hi = W((i64)hi);
+            return;
+        }
+    } else {
+        u64 m = 0;
+#pragma unroll
+        for (int i = 0; i < CNT; ++i) m |= (u64)((i64)v[i] ^ ((i64)v[i] >> 63));
+        if (m < (1ull << (63 - LOG2))) {
+            i64 s = 0, lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < CNT; ++i) { s += (i64)v[i]; lo = s < lo ? s : lo; hi = s > hi ? s : hi; }
+            t.s = W(s); t.lo = W(lo); t.hi = W(hi);
+            return;
+        }
+    }
+    t.zero();
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) t.push((i64)v[i]);
+}
+
+// The slot a block leaves for the fold: same 64 bytes as a Partial.
+struct __align__(16) PrefixPartial { u64 s_lo; i64 s_hi; u64 mn_lo; i64 mn_hi; u64 mx_lo; i64 mx_hi; u64 pad[2]; };
+static_assert(sizeof(PrefixPartial) == sizeof(Partial), "the checked Sum reuses the reduction's partial slots");
+
+// Warp-wide minimum / maximum of wide integers: the high words first (one redux), then the low words of the lanes that tie.
+__device__ __forceinline__ i64 warp_min_wide(i64 v) {
+    const int h = (int)(v >> 32), mh = __reduce_min_sync(0xffffffffu, h);
+    const u32 ml = __reduce_min_sync(0xffffffffu, h == mh ? (u32)v : 0xffffffffu);
+    return (i64)(((u64)(u32)mh << 32) | ml);
+}
+__device__ __forceinline__ i64 warp_max_wide(i64 v) {
+    const int h = (int)(v >> 32), mh = __reduce_max_sync(0xffffffffu, h);
+    const u32 ml = __reduce_max_sync(0xffffffffu, h == mh ? (u32)v : 0u);
+    return (i64)(((u64)(u32)mh << 32) | ml);
+}
+__device__ __forceinline__ u64 warp_min_u64(u64 v) {
+    const u32 h = (u32)(v >> 32), mh = __reduce_min_sync(0xffffffffu, h);
+    const u32 ml = __reduce_min_sync(0xffffffffu, h == mh ? (u32)v : 0xffffffffu);
+    return ((u64)mh << 32) | ml;
+}
+__device__ __forceinline__ u64 warp_max_u64(u64 v) {
+    const u32 h = (u32)(v >> 32), mh = __reduce_max_sync(0xffffffffu, h);
+    const u32 ml = __reduce_max_sync(0xffffffffu, h == mh ? (u32)v : 0u);
+    return ((u64)mh << 32) | ml;
+}
+__device__ __forceinline__ Wide128 warp_min_wide(const Wide128& v) {
+    Wide128 r; r.hi = warp_min_wide(v.hi); r.lo = warp_min_u64(v.hi == r.hi ? v.lo : ~0ull); return r;
+}
+__device__ __forceinline__ Wide128 warp_max_wide(const Wide128& v) {
+    Wide128 r; r.hi = warp_max_wide(v.hi); r.lo = warp_max_u64(v.hi == r.hi ? v.lo : 0ull); return r;
+}
+__device__ __forceinline__ i64 wide_shfl_up(i64 v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+__device__ __forceinline__ Wide128 wide_shfl_up(const Wide128& v, int d) {
+    Wide128 r; r.lo = __shfl_up_sync(0xffffffffu, v.lo, d); r.hi = __shfl_up_sync(0xffffffffu, v.hi, d); return r;
+}
+__device__ __forceinline__ i64 wide_shfl(i64 v, int src) { return __shfl_sync(0xffffffffu, v, src); }
+__device__ __forceinline__ Wide128 wide_shfl(const Wide128& v, int src) {
+    Wide128 r; r.lo = __shfl_sync(0xffffffffu, v.lo, src); r.hi = __shfl_sync(0xffffffffu, v.hi, src); return r;
+}
+
+// The lanes' segments appended in lane order; every lane gets the warp's triple. Instead of appending triples pairwise
+// (three wide values through every shuffle step), the totals alone are scanned; a lane's extremes, moved by the sum of
+// the lanes before it, are then absolute within the warp and an ordinary minimum / maximum finishes the job.
+template <typename W>
+__device__ __forceinline__ PrefixTriple<W> warp_prefix_append(const PrefixTriple<W>& t) {
+    const int lane = threadIdx.x & 31;
+    W incl = t.s;
+#pragma unroll
+    for (int d = 1; d <= 16; d <<= 1) {
+        const W up = wide_shfl_up(incl, d);
+        if (lane >= d) incl = incl + up;
+    }
+    W before = wide_shfl_up(incl, 1);
+    if (lane == 0) before = W(0);
+    PrefixTriple<W> r;
+    r.lo = warp_min_wide(before + t.lo);
+    r.hi = warp_max_wide(before + t.hi);
+    r.s = wide_shfl(incl, 31);
+    return r;
+}
+template <typename W>
+__device__ __forceinline__ void prefix_to_slot(PrefixPartial* dst, const PrefixTriple<W>& t) {
+    uint4 q0, q1, q2;
+    const u64 a = wide_low(t.s), c = wide_low(t.lo), e = wide_low(t.hi);
+    const i64 b = wide_high(t.s), d = wide_high(t.lo), f = wide_high(t.hi);
+    q0.x = (u32)a; q0.y = (u32)(a >> 32); q0.z = (u32)(u64)b; q0.w = (u32)((u64)b >> 32);
+    q1.x = (u32)c; q1.y = (u32)(c >> 32); q1.z = (u32)(u64)d; q1.w = (u32)((u64)d >> 32);
+    q2.x = (u32)e; q2.y = (u32)(e >> 32); q2.z = (u32)(u64)f; q2.w = (u32)((u64)f >> 32);
+    uint4* p = reinterpret_cast<uint4*>(dst);
+    __stcg(p, q0); __stcg(p + 1, q1); __stcg(p + 2, q2);
+}
+template <typename W>
+__device__ __forceinline__ void prefix_from_slot(PrefixTriple<W>& t, const PrefixPartial* src) {
+    const uint4* p = reinterpret_cast<const uint4*>(src);
+    const uint4 q0 = __ldcg(p), q1 = __ldcg(p + 1), q2 = __ldcg(p + 2);
+    wide_set(t.s, (u64)q0.x | ((u64)q0.y << 32), (i64)((u64)q0.z | ((u64)q0.w << 32)));
+    wide_set(t.lo, (u64)q1.x | ((u64)q1.y << 32), (i64)((u64)q1.z | ((u64)q1.w << 32)));
+    wide_set(t.hi, (u64)q2.x | ((u64)q2.y << 32), (i64)((u64)q2.z | ((u64)q2.w << 32)));
+}
+// Warp triples -> block triple, in warp order. Valid in warp 0.
+template <typename W, int BLOCK>
+__device__ __forceinline__ PrefixTriple<W> block_prefix_append(PrefixTriple<W> a, PrefixTriple<W>* smem /* BLOCK/32 */) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    a = warp_prefix_append(a);
+    if (lane == 0) smem[warp] = a;
+    __syncthreads();
+    PrefixTriple<W> b; b.zero();
+    if (warp == 0) {
+        if (lane < BLOCK / 32) b = smem[lane];
+        b = warp_prefix_append(b);
+    }
+    __syncthreads();
+    return b;
+}
+
+// Persistent grid, same launch and same scratch as reduce_body. Every *warp* owns one contiguous range of the input and
+// every lane UNROLL consecutive packs of each warp tile, so that a lane's elements, a warp's lanes, a block's warps and the
+// grid's blocks are each in source order; the last block appends the block triples in index order. The record carries the
+// exact total (slots 2, 3), the smallest and largest running sum (slots 12..15) and FLAG_OVERFLOW if either left O's range.
+template <class C, int BLOCK, int UNROLL, bool VEC>
+__device__ __forceinline__ void sum_checked_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
+                                                 i64 n, Partial* __restrict__ partials, unsigned int* __restrict__ ticket,
+                                                 DeviceResult* __restrict__ res) {
+    typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
+    typedef typename prefix_wide<O>::type W;
+    static_assert(sizeof(O) == 4 || sizeof(O) == 8, "checked Sum is defined for int and long");
+    constexpr int E = pack_elems<C, VEC>::value;
+    constexpr int WARPS = BLOCK / 32;
+    __shared__ PrefixTriple<W> s_tri[WARPS];
+    __shared__ bool s_last;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // same launch protocol as reduce_body
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 nitems = n / E;
+    const i64 total_warps = (i64)gridDim.x * WARPS, gw = (i64)blockIdx.x * WARPS + warp;
+    constexpr i64 WTILE = 32 * UNROLL;                                 // packs per warp tile
+    i64 per = (nitems + total_warps - 1) / total_warps;
+    per = (per + WTILE - 1) / WTILE * WTILE;
+    const i64 lo_pack = gw * per < nitems ? gw * per : nitems;
+    const i64 hi_pack = lo_pack + per < nitems ? lo_pack + per : nitems;
+
+    PrefixTriple<W> run; run.zero();
+    for (i64 base = lo_pack; base < hi_pack; base += WTILE) {
+        const i64 p0 = base + (i64)lane * UNROLL;
+        Pack<A, E> a[UNROLL]; Pack<B, E> b[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (p0 + u < hi_pack) {
+                a[u].load(in0 + (p0 + u) * E);
+                if constexpr (C::n_in == 2) b[u].load(in1 + (p0 + u) * E);
+            }
+        }
+        // An element the chain drops, or beyond the range, counts as 0: adding 0 changes neither the sum nor its range.
+        O vals[UNROLL * E];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int k = 0; k < E; ++k) {
+                O o = O(0); bool keep = false;
+                if (p0 + u < hi_pack) {
+                    if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
+                    else keep = C::apply(a[u].e[k], B(), o);
+                }
+                vals[u * E + k] = keep ? o : O(0);
+            }
+        }
+        PrefixTriple<W> t;
+        lane_prefix<O, UNROLL * E>(vals, t);
+        t = warp_prefix_append(t);
+        run.append(t);
+    }
+    if (gw == total_warps - 1) {   // the last n % E elements come after every pack: the last warp appends them
+        PrefixTriple<W> t; t.zero();
+        if (lane == 0) {
+            for (i64 i = nitems * E; i < n; ++i) {
+                O o; bool keep;
+                if constexpr (C::n_in == 2) keep = C::apply(in0[i], in1[i], o); else keep = C::apply(in0[i], B(), o);
+                if (keep) t.push((i64)o);
+            }
+        }
+        t = warp_prefix_append(t);
+        run.append(t);
+    }
+    // every lane of a warp holds the warp's triple; make lane 0's the one that counts and the others empty
+    if (lane != 0) run.zero();
+    PrefixTriple<W> blk = block_prefix_append<W, BLOCK>(run, s_tri);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    PrefixPartial* slots = reinterpret_cast<PrefixPartial*>(partials);
+    if (threadIdx.x == 0) {
+        prefix_to_slot(slots + blockIdx.x, blk);
+        __threadfence();
+        const unsigned int tk = atomicAdd(ticket, 1u);
+        s_last = (tk == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // Last block: thread k appends the slots of its own contiguous run, then the block appends the threads' triples in order.
+    const unsigned int per_thread = (gridDim.x + BLOCK - 1) / BLOCK;
+    PrefixTriple<W> tot; tot.zero();
+    for (unsigned int j = 0; j < per_thread; ++j) {
+        const unsigned int sl = threadIdx.x * per_thread + j;
+        if (sl < gridDim.x) { PrefixTriple<W> o; prefix_from_slot(o, slots + sl); tot.append(o); }
+    }
+    tot = block_prefix_append<W, BLOCK>(tot, s_tri);
+    if (threadIdx.x == 0) {
+        W mn, mx;
+        if constexpr (sizeof(O) == 4) { mn = W(-2147483647LL - 1LL); mx = W(2147483647LL); }
+        else { mn = W(-0x7fffffffffffffffLL - 1LL); mx = W(0x7fffffffffffffffLL); }
+        const bool overflow = (tot.lo < mn) || (mx < tot.hi);
+        res->fsum = 0.0; res->count_f = 0.0;
+        res->isum_lo = (i64)wide_low(tot.s); res->isum_hi = wide_high(tot.s);
+        res->count = 0; res->fmin = 0; res->fmax = 0; res->imin = 0; res->imax = 0;
+        res->flags = (u64)(FLAG_PREFIX | (overflow ? FLAG_OVERFLOW : 0u));
+        res->offset = 0; res->local_count = 0;
+        res->pad[0] = (i64)wide_low(tot.lo); res->pad[1] = wide_high(tot.lo);
+        res->pad[2] = (i64)wide_low(tot.hi); res->pad[3] = wide_high(tot.hi);
+        *ticket = 0;
     }
 }
 

@@ -19,7 +19,8 @@ enum : int { PEER_MAX = 8, PEER_RING = 4 };
 struct __align__(16) PeerSlot {   // 64 bytes: one rank's partial for one launch; valid when stamp == launch number
     double fsum; u64 isum_lo; i64 isum_hi; i64 count; i64 mn_bits; i64 mx_bits; u64 flags; u64 stamp;
 };
-enum : u64 { SLOT_IS_FP = 1ull << 32, SLOT_IS_U64 = 1ull << 33 };   // how to compare mn_bits / mx_bits
+enum : u64 { SLOT_IS_FP = 1ull << 32, SLOT_IS_U64 = 1ull << 33,     // how to compare mn_bits / mx_bits
+             SLOT_IS_I32 = 1ull << 34 };                             // a checked Sum's range is int's, not long's
 struct PeerState { u64 seq; u64 pad; };                              // device memory, one per context
 struct PeerTable {                // passed by value as a kernel parameter
     int world, rank;
@@ -52,6 +53,11 @@ __device__ __forceinline__ void peer_exchange_body(const PeerTable& pt, DeviceRe
         vd->fsum = rec->fsum; vd->isum_lo = (u64)rec->isum_lo; vd->isum_hi = rec->isum_hi; vd->count = rec->count;
         vd->mn_bits = fp ? __double_as_longlong(rec->fmin) : rec->imin;
         vd->mx_bits = fp ? __double_as_longlong(rec->fmax) : rec->imax;
+        if (rec->flags & (u64)FLAG_PREFIX) {
+            // a checked integer Sum: the fields a Sum leaves unused carry the range of the running sum (two words each)
+            vd->mn_bits = rec->pad[0]; vd->fsum = __longlong_as_double(rec->pad[1]);
+            vd->mx_bits = rec->pad[2]; vd->count = rec->pad[3];
+        }
         vd->flags = (rec->flags & 0xffffffffull) | tag;
         st_release_sys(&dst->stamp, seq);
         // collect: rank `lane`'s partial in my own area
@@ -73,6 +79,30 @@ __device__ __forceinline__ void peer_exchange_body(const PeerTable& pt, DeviceRe
     if (lane == 0) {
         if (failed) {                                  // a peer never showed up: say so, keep the local partial
             rec->flags = rec->flags | (u64)FLAG_TIMEOUT;
+        } else if (slots[0].flags & (u64)FLAG_PREFIX) {
+            // checked integer Sum: the ranks' (total, smallest, largest running sum) appended in rank order, exactly
+            Wide128 s(0), lo(0), hi(0);
+            u64 fl = 0;
+            for (int r = 0; r < pt.world; ++r) {
+                const PeerSlot& o = slots[r];
+                Wide128 os, olo, ohi;
+                os.lo = o.isum_lo; os.hi = o.isum_hi;
+                olo.lo = (u64)o.mn_bits; olo.hi = __double_as_longlong(o.fsum);
+                ohi.lo = (u64)o.mx_bits; ohi.hi = o.count;
+                const Wide128 l = s + olo, h = s + ohi;
+                if (l < lo) lo = l;
+                if (hi < h) hi = h;
+                s = s + os;
+                fl |= o.flags;
+            }
+            const bool is32 = (fl & SLOT_IS_I32) != 0;
+            const Wide128 mn(is32 ? -2147483647LL - 1LL : -0x7fffffffffffffffLL - 1LL), mx(is32 ? 2147483647LL : 0x7fffffffffffffffLL);
+            fl = (fl & 0xffffffffull & ~(u64)FLAG_OVERFLOW) | ((lo < mn || mx < hi) ? (u64)FLAG_OVERFLOW : 0ull);
+            rec->fsum = 0; rec->count_f = 0; rec->isum_lo = (i64)s.lo; rec->isum_hi = s.hi; rec->count = 0;
+            rec->fmin = 0; rec->fmax = 0; rec->imin = 0; rec->imax = 0;
+            rec->flags = fl;
+            rec->offset = 0; rec->local_count = 0;
+            rec->pad[0] = (i64)lo.lo; rec->pad[1] = lo.hi; rec->pad[2] = (i64)hi.lo; rec->pad[3] = hi.hi;
         } else {
             PeerSlot g = slots[0];
             const bool fp = (g.flags & SLOT_IS_FP) != 0, u64cmp = (g.flags & SLOT_IS_U64) != 0;

@@ -962,7 +962,7 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
                 *status = ST_NOT_SUPPORTED; return false;
             }
             info->red_mask = term.kind == OP_SUM ? RED_SUM : (RED_SUM | RED_COUNT);
-            if (term.kind == OP_SUM) { info->result_type = cur; key += "|Sum"; }
+            if (term.kind == OP_SUM) { info->result_type = cur; key += "|Sum"; info->checked_sum = (cur == T_I32 || cur == T_I64); }
             else { info->result_type = (cur == T_F32) ? T_F32 : T_F64; key += "|Average"; }
             break;
         default: *err = "the last operator must be ToArray, Sum, Min, Max, Average, Count, FirstIndex or LastIndex"; *status = ST_NOT_SUPPORTED; return false;
@@ -1061,11 +1061,14 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
         } else {
             // Keep the register count where 6 (one input) or 4 (Zip) blocks share an SM: measured as fast as 8 blocks, and
             // unlike a cap of 32 registers it leaves the once-per-launch tail (the fold of the block partials) free of spills.
-            const std::string rb = B + ", " + std::to_string(tuning.reduce_min_blocks > 0 ? tuning.reduce_min_blocks : (info.n_in == 2 ? 4 : 6));
+            // (the ordered integer Sum keeps a lane's run of outputs in registers: 4 blocks, 64 registers)
+            const std::string rb = B + ", " + std::to_string(tuning.reduce_min_blocks > 0 ? tuning.reduce_min_blocks : ((info.n_in == 2 || info.checked_sum) ? 4 : 6));
+            // Sum over int / long is checked element by element in source order: its own, ordered kernel (same launch).
+            const std::string body = info.checked_sum ? "dcb::sum_checked_body<" + C + ", " + B + ", " + u + ", " + vec + ">"
+                                                      : "dcb::reduce_body<" + C + ", " + std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">";
             s += "extern \"C\" __global__ void __launch_bounds__(" + rb + ") dcb_reduce_" + variants[v] + suffix +
                  "(const void* in0, const void* in1, long long n, void* partials, unsigned int* ticket, void* res) {\n"
-                 "    dcb::reduce_body<" + C + ", " + std::to_string(info.red_mask) + ", " + B + ", " + u + ", " + vec + ">(" + cast_in() +
-                 ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res);\n}\n";
+                 "    " + body + "(" + cast_in() + ", n, (dcb::Partial*)partials, ticket, (dcb::DeviceResult*)res);\n}\n";
         }
     }
     return s;

@@ -26,6 +26,8 @@ RUN_TAKE = 1
 AGG_COUNT, AGG_SUM, AGG_MIN, AGG_MAX, AGG_AVERAGE = 0, 1, 2, 3, 4
 JOIN_INNER, JOIN_SEMI, JOIN_ANTI = 0, 2, 3
 RES_SAW_NAN, RES_TRUNCATED, RES_TIMEOUT, RES_OVERFLOW = 1, 2, 4, 8
+RES_PREFIX_RANGE = 32
+SLOT_PREFIX_MIN_LO, SLOT_PREFIX_MIN_HI, SLOT_PREFIX_MAX_LO, SLOT_PREFIX_MAX_HI = 12, 13, 14, 15
 DEVICE_RESULT_BYTES = 128
 SLOT_FSUM, SLOT_COUNT_F, SLOT_ISUM_LO, SLOT_ISUM_HI, SLOT_COUNT = 0, 1, 2, 3, 4
 SLOT_FMIN, SLOT_FMAX, SLOT_IMIN, SLOT_IMAX, SLOT_FLAGS, SLOT_OFFSET, SLOT_LOCAL_COUNT, SLOT_NSLOTS = 5, 6, 7, 8, 9, 10, 11, 16

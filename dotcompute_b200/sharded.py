@@ -60,6 +60,30 @@ def fold_records(records: np.ndarray, out_type: int) -> np.ndarray:
     recs = np.asarray(records, dtype=np.int64).reshape(-1, N.SLOT_NSLOTS)
     out = recs[0].copy()
     f = out.view(np.float64)
+    if int(recs[0][N.SLOT_FLAGS]) & N.RES_PREFIX_RANGE:
+        # checked integer Sum: append the ranks' (total, smallest, largest running sum) in rank order
+        def wide(r, lo_slot):
+            return (int(r[lo_slot + 1]) << 64) + (int(r[lo_slot]) & (2**64 - 1))
+
+        def put(slot, v):
+            out[slot] = np.array(v & (2**64 - 1), dtype=np.uint64).view(np.int64)
+            out[slot + 1] = np.int64(v >> 64)
+
+        s = lo = hi = 0
+        flags = 0
+        for r in recs:
+            rs = wide(r, N.SLOT_ISUM_LO)
+            lo = min(lo, s + wide(r, N.SLOT_PREFIX_MIN_LO))
+            hi = max(hi, s + wide(r, N.SLOT_PREFIX_MAX_LO))
+            s += rs
+            flags |= int(r[N.SLOT_FLAGS])
+        bits = 31 if out_type == N.T_I32 else 63
+        over = lo < -(2**bits) or hi > 2**bits - 1
+        put(N.SLOT_ISUM_LO, s)
+        put(N.SLOT_PREFIX_MIN_LO, lo)
+        put(N.SLOT_PREFIX_MAX_LO, hi)
+        out[N.SLOT_FLAGS] = (flags & ~N.RES_OVERFLOW) | (N.RES_OVERFLOW if over else 0)
+        return out
     isum = (int(recs[0][N.SLOT_ISUM_HI]) << 64) + (int(recs[0][N.SLOT_ISUM_LO]) & (2**64 - 1))
     unsigned = out_type == N.T_U64
     for r in recs[1:]:
@@ -100,7 +124,7 @@ def combine_record(rec, terminal: int, out_type: int, group=None):
         if terminal == N.OP_AVERAGE:
             dist.all_reduce(rec[N.SLOT_COUNT: N.SLOT_COUNT + 1], op=dist.ReduceOp.SUM, group=group)
         return rec
-    if terminal in (N.OP_SUM, N.OP_AVERAGE) and out_type in _INT_SMALL:
+    if (terminal == N.OP_AVERAGE or out_type != N.T_I32) and terminal in (N.OP_SUM, N.OP_AVERAGE) and out_type in _INT_SMALL:
         # per-rank sums of <= 32-bit elements stay far inside int64, so a plain int64 SUM is exact
         dist.all_reduce(rec[N.SLOT_ISUM_LO: N.SLOT_COUNT + 1], op=dist.ReduceOp.SUM, group=group)
         rec[N.SLOT_ISUM_HI] = torch.where(rec[N.SLOT_ISUM_LO] < 0, -1, 0)
@@ -108,7 +132,8 @@ def combine_record(rec, terminal: int, out_type: int, group=None):
     if terminal in (N.OP_COUNT, N.OP_TOARRAY):
         dist.all_reduce(rec[N.SLOT_COUNT: N.SLOT_COUNT + 1], op=dist.ReduceOp.SUM, group=group)
         return rec
-    # Min / Max, and Sum over 64-bit integers: gather every rank's record and fold exactly in rank order.
+    # Min / Max, and Sum over int / long (checked: the running sum's range must be appended in rank order): gather every
+    # rank's record and fold exactly in rank order.
     world = dist.get_world_size(group)
     gathered = torch.empty((world, N.SLOT_NSLOTS), dtype=torch.int64, device=rec.device)
     dist.all_gather_into_tensor(gathered, rec.reshape(1, -1), group=group) if rec.is_cuda else \

@@ -153,7 +153,8 @@ enum {
     DCB_RES_SAW_NAN = 1u,
     DCB_RES_TRUNCATED = 2u,
     DCB_RES_TIMEOUT = 4u,
-    DCB_RES_OVERFLOW = 8u
+    DCB_RES_OVERFLOW = 8u,
+    DCB_RES_PREFIX_RANGE = 32u      /* record only: slots DCB_SLOT_PREFIX_MIN_LO.. hold the range of the running sum */
 };
 
 /* Raw per-run record the kernels write in device memory: 16 eight-byte slots. A sharded
@@ -172,6 +173,10 @@ enum {
     DCB_SLOT_OFFSET = 10,/* int64: after dcb_peer_exchange_async, the sum of the counts of all lower ranks, i.e. where this
                             GPU's compacted output starts in the global, rank-ordered result; 0 without an exchange */
     DCB_SLOT_LOCAL_COUNT = 11, /* int64: this GPU's own count (after an exchange DCB_SLOT_COUNT holds the global total) */
+    DCB_SLOT_PREFIX_MIN_LO = 12, /* Sum over int / long (checked like Enumerable.Sum: the call fails with DCB_ERR_OVERFLOW as  */
+    DCB_SLOT_PREFIX_MIN_HI = 13, /* soon as a running sum, taken in source order, leaves the element type's range): smallest and */
+    DCB_SLOT_PREFIX_MAX_LO = 14, /* largest running sum, empty prefix included, as 128-bit two's complement (low, high word).    */
+    DCB_SLOT_PREFIX_MAX_HI = 15, /* Records of adjacent ranges combine as (s1+s2, min(lo1, s1+lo2), max(hi1, s1+hi2)), in order. */
     DCB_SLOT_NSLOTS = 16
 };
 #define DCB_DEVICE_RESULT_BYTES 128

@@ -17,6 +17,9 @@ QUERIES = [
     ("map", np.float32, None, [(N.OP_SELECT, "x => MathF.Sqrt(x) * 2f + 1f"), (N.OP_TOARRAY, None)]),
     ("reduce-minmax-f64", np.float64, None, [(N.OP_WHERE, "x => x > 0.25"), (N.OP_MAX, None)]),
     ("reduce-sum-i32", np.int32, None, [(N.OP_SELECT, "x => x % 7"), (N.OP_SUM, None)]),
+    ("reduce-sum-i64-checked", np.int64, None, [(N.OP_WHERE, "x => x != 0L"), (N.OP_SUM, None)]),
+    ("reduce-sum-zip-i32-checked", np.int32, np.int32, [(N.OP_ZIP, "(a, b) => a * b"), (N.OP_SUM, None)]),
+    ("reduce-sum-u8-to-i32-checked", np.uint8, None, [(N.OP_SELECT, "x => (int)x * 3"), (N.OP_SUM, None)]),
     ("zip-sum", np.float32, np.float32, [(N.OP_ZIP, "(a, b) => a * b"), (N.OP_SUM, None)]),
     ("compact-f32", np.float32, None, [(N.OP_WHERE, "x => x > 0.5f"), (N.OP_SELECT, "x => x * x + 3f"), (N.OP_TOARRAY, None)]),
     ("compact-i64", np.int64, None, [(N.OP_WHERE, "k => (k & 0xF) == 3"), (N.OP_TOARRAY, None)]),
@@ -97,3 +100,11 @@ def test_translated_kernel_method_compiles(name):
     reg = translate_kernel_method(KERNEL_METHODS[name])
     res, log = compile_for_sm100a(reg.CudaSource)
     assert res == nvrtc.nvrtcResult.NVRTC_SUCCESS, reg.CudaSource + "\n" + log[:2000]
+
+
+def test_integer_sum_uses_the_ordered_kernel():
+    """Sum over int / long must track the running sum in source order; Sum over float, and Average, must not."""
+    assert "sum_checked_body" in generate_source(np.int32, [(N.OP_SUM, None)])
+    assert "sum_checked_body" in generate_source(np.int64, [(N.OP_SELECT, "x => x + 1L"), (N.OP_SUM, None)])
+    assert "sum_checked_body" not in generate_source(np.float32, [(N.OP_SUM, None)])
+    assert "sum_checked_body" not in generate_source(np.int32, [(N.OP_AVERAGE, None)])

@@ -137,3 +137,39 @@ def test_fold_records_is_exact_and_ordered():
     u[1][N.SLOT_IMAX] = 7
     out = fold_records(u, N.T_U64)
     assert out[N.SLOT_IMIN] == 7 and int(out[N.SLOT_IMAX]) & (2**64 - 1) == 2**63 + 5     # unsigned order
+
+
+def _prefix_record(k, bits):
+    """What the checked Sum kernel leaves for one shard: total, smallest and largest running sum (empty prefix included)."""
+    rec = np.zeros(16, dtype=np.int64)
+    pref = [0]
+    for v in k.tolist():
+        pref.append(pref[-1] + int(v))
+
+    def put(slot, v):
+        rec[slot] = np.array(v & (2**64 - 1), dtype=np.uint64).view(np.int64)
+        rec[slot + 1] = v >> 64
+    put(N.SLOT_ISUM_LO, pref[-1])
+    put(N.SLOT_PREFIX_MIN_LO, min(pref))
+    put(N.SLOT_PREFIX_MAX_LO, max(pref))
+    over = min(pref) < -(2**bits) or max(pref) > 2**bits - 1
+    rec[N.SLOT_FLAGS] = N.RES_PREFIX_RANGE | (N.RES_OVERFLOW if over else 0)
+    return rec
+
+
+@pytest.mark.parametrize("dtype,t,bits", [(np.int32, N.T_I32, 31), (np.int64, N.T_I64, 63)])
+def test_fold_records_appends_running_sum_ranges_in_rank_order(dtype, t, bits):
+    top = 2**bits - 1
+    shards_ok = [np.array([top - 10, -3], dtype=dtype), np.array([13, -top], dtype=dtype), np.array([5], dtype=dtype)]
+    out = fold_records(np.stack([_prefix_record(s, bits) for s in shards_ok]), t)
+    assert not int(out[N.SLOT_FLAGS]) & N.RES_OVERFLOW            # touches the maximum exactly, never above
+    assert finalize_record(out, N.OP_SUM, t).i64 == 5
+    assert (int(out[N.SLOT_PREFIX_MAX_HI]) << 64) + (int(out[N.SLOT_PREFIX_MAX_LO]) & (2**64 - 1)) == top
+    # the same shards in another order cross the limit in the middle although every shard alone, and the total, are inside
+    shards_bad = [shards_ok[0], np.array([14, -top - 1], dtype=dtype), shards_ok[2]]
+    assert all(not int(_prefix_record(s, bits)[N.SLOT_FLAGS]) & N.RES_OVERFLOW for s in shards_bad)
+    out = fold_records(np.stack([_prefix_record(s, bits) for s in shards_bad]), t)
+    assert int(out[N.SLOT_FLAGS]) & N.RES_OVERFLOW
+    with pytest.raises(Exception) as e:
+        finalize_record(out, N.OP_SUM, t)
+    assert type(e.value).__name__ == "OverflowException"
