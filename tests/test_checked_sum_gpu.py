@@ -188,3 +188,53 @@ def test_slices_that_start_anywhere(acc, dtype, skip):
         got = "overflow"
     assert got == expect
     buf.Dispose()
+
+
+@pytest.mark.parametrize("dtype,bits", [(np.int32, 31), (np.int64, 63)])
+def test_exchange_appends_ranges_in_rank_order(built_library, dtype, bits):
+    """The exchange kernel's fold for a checked Sum, on one GPU: a world of two in which the other rank's record is written
+    into this rank's exchange area by the host before the launch (nothing on the GPU waits for anything that is not there
+    yet). Rank 0 holds [top-10, -3]; the fabricated rank 1 once stays inside when appended and once crosses the limit,
+    although its own range and the global total are inside both times."""
+    import ctypes as C
+    from dotcompute_b200 import CudaAccelerator
+    top = 2**bits - 1
+
+    def record_of(values):
+        pref = [0]
+        for v in values:
+            pref.append(pref[-1] + v)
+        return pref[-1], min(pref), max(pref)
+
+    def words(v):
+        return [v & (2**64 - 1), (v >> 64) & (2**64 - 1)]
+
+    for other, crosses in (([13, -top], False), ([14, -top - 1 + 10], True)):
+        acc2 = CudaAccelerator(0)
+        try:
+            area, nbytes = C.c_void_p(), C.c_size_t()
+            N.check(N.lib().dcb_peer_area_ptr(acc2.handle, C.byref(area), C.byref(nbytes)), acc2.handle)
+            scratch = acc2.Memory.AllocateAsync(nbytes.value, np.uint8)
+            scratch.FillAsync(0)
+            areas = (C.c_void_p * 2)(area.value, scratch.GetDeviceMemory())
+            N.check(N.lib().dcb_peer_connect_local(acc2.handle, 2, 0, areas), acc2.handle)
+            s, lo, hi = record_of(other)
+            assert -(2**bits) <= lo and hi <= top
+            # PeerSlot = {fsum, isum_lo, isum_hi, count, mn_bits, mx_bits, flags, stamp}; a checked Sum carries the range in
+            # mn_bits / fsum (smallest, low / high word) and mx_bits / count (largest); first exchange: stamp 1, ring row 1
+            slot = np.array([words(lo)[1], words(s)[0], words(s)[1], words(hi)[1], words(lo)[0], words(hi)[0],
+                             N.RES_PREFIX_RANGE | ((1 << 34) if bits == 31 else 0), 1], dtype=np.uint64)
+            mine = acc2.Memory.WrapDevicePointer(area.value, nbytes.value // 8, np.uint64)
+            mine.CopyFromAsync(slot, offset=(1 * 8 + 1) * 8)
+            acc2.Synchronize()
+            x = np.array([top - 10, -3], dtype=dtype)
+            q = AsComputeQueryable(acc2.Memory.AllocateAndCopyAsync(x))
+            if crosses:
+                with pytest.raises(OverflowException):
+                    q.Sum()
+            else:
+                assert q.Sum() == top - 13 + s
+            N.check(N.lib().dcb_peer_disconnect(acc2.handle), acc2.handle)
+            scratch.Dispose()
+        finally:
+            acc2.Dispose()
