@@ -996,8 +996,22 @@ __device__ __forceinline__ void compact_copy_out(O* __restrict__ out, i64 out_ca
             const int done = head + nvec * VO;
             if (lane < warp_run - done) dst[done + lane] = stage[done + lane];
         } else {
-#pragma unroll 4
-            for (int i = lane; i < warp_run; i += 32) dst[i] = stage[i];
+            // Batches of eight per lane: all loads of a batch are issued before its first store, so a batch pays the
+            // shared-memory latency once (a rolled loop pays it on every element).
+            constexpr int BATCH = 8;
+            for (int i0 = 0; i0 < warp_run; i0 += 32 * BATCH) {
+                O v[BATCH];
+#pragma unroll
+                for (int j = 0; j < BATCH; ++j) {
+                    const int i = i0 + j * 32 + lane;
+                    if (i < warp_run) v[j] = stage[i];
+                }
+#pragma unroll
+                for (int j = 0; j < BATCH; ++j) {
+                    const int i = i0 + j * 32 + lane;
+                    if (i < warp_run) dst[i] = v[j];
+                }
+            }
         }
     } else {
         for (int i = lane; i < warp_run; i += 32) {
@@ -1652,7 +1666,9 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                     // Consecutive lanes move consecutive survivors: no bank conflicts on the way out of shared memory, whole
                     // 128-byte lines on the way into L2 (16-byte stores would read shared memory four lanes to a bank).
                     compact_copy_out<O, DCB_STREAM_VEC_OUT != 0>(out, out_cap, off, s_cnt[sj][w], lane, stage0);
+#ifndef DCB_STREAM_NO_PROXY_FENCE
                     fence_async_smem();                       // this warp's accesses to the slot come before the next copy into it
+#endif
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&s_empty[sj]);
                     if (w == 0) DCB_STAT_END(2, 3);

@@ -997,9 +997,13 @@ int pipe_bytes_per_elem(const ChainInfo& info) { return type_size(info.in0) + (i
 int stream_rows_for(const ChainInfo& info, int warps) {
     if (info.terminal != OP_TOARRAY || !info.has_filter) return 0;
     if (type_size(info.out_type) > type_size(info.in0)) return 0;
+    // Tiles of about 20 KB (all inputs together): five slots of two resident blocks fit an SM's shared memory, and the
+    // per-tile work (barriers, count descriptor, offsets) is spread over a quarter more elements than with 16 KB
+    // (measured 7 % faster on float, 17 % on long). A lane keeps rows * e values in registers: at most 40.
     const int e = 16 / type_size(info.in0);
-    const int rows = 16384 / (warps * 32 * e * pipe_bytes_per_elem(info));
-    return rows < 1 ? 1 : (rows > 8 ? 8 : rows);
+    const int cap = e <= 4 ? 10 : 8;
+    const int rows = 20480 / (warps * 32 * e * pipe_bytes_per_elem(info));
+    return rows < 1 ? 1 : (rows > cap ? cap : rows);
 }
 long long stream_tile_elems(const ChainInfo& info, int rows, int warps) { return (long long)warps * rows * 32 * (16 / type_size(info.in0)); }
 long long stream_smem_bytes(const ChainInfo& info, int rows, int warps, int nbuf) {

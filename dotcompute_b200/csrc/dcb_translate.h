@@ -74,8 +74,8 @@ struct Tuning {
     int stream_warps = 4;       // worker warps per block (the block has two more warps: offsets and loader)
     int stream_rows = 0;        // rows of 32 packs per worker and tile; 0 = automatic (stream_rows_for)
     int stream_lag = 3;         // rounds between ranking a tile and writing it (its offset is ready after two)
-    int stream_nbuf = 6;        // shared-memory slots per input: lag + 1 + tiles on their way in
-    int stream_depth = 4;       // 16-byte descriptor loads per lane of the offsets warp (128 * depth tiles per window)
+    int stream_nbuf = 5;        // shared-memory slots per input: lag + 1 + tiles on their way in
+    int stream_depth = 3;       // 16-byte descriptor loads per lane of the offsets warp (128 * depth tiles per window)
     int stream_ahead_mb = 12;   // distance of the L2 prefetch in front of the tile being drawn; 0 = none
     int stream_draw_ahead = 0;  // rounds the draw of a tile id may run ahead of ranking; 0 = as soon as a slot is free
     int stream_min_blocks = 2;  // second argument of __launch_bounds__; 0 = none
