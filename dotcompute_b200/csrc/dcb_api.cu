@@ -124,7 +124,7 @@ struct dcb_pipeline {
     int jit_rows = 0;                    // rows forced by a tuning experiment (0 = automatic)
     int compact_block = 256;             // threads per block of the compaction kernels
     const void* k_stream = nullptr;      // streamed compaction kernel (null: the query has none)
-    int stream_rows = 0, stream_warps = 0, stream_nbuf = 0, occ_stream = 1;
+    int stream_rows = 0, stream_warps = 0, stream_nbuf = 0, stream_copy_warps = 0, occ_stream = 1;
     std::mutex mu;                       // guards `scratch` and every enqueue that uses it
     std::map<cudaStream_t, Scratch> scratch;
     std::mutex run_mu;                   // serialises the blocking calls, which share d_result / h_record / ev0 / ev1
@@ -247,12 +247,14 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     tuning.stream_rows = env_int("DCB200_STREAM_ROWS", 0);
     tuning.stream_lag = env_int("DCB200_STREAM_LAG", tuning.stream_lag);
     tuning.stream_nbuf = env_int("DCB200_STREAM_NBUF", tuning.stream_nbuf);
+    tuning.stream_copy_warps = env_int("DCB200_STREAM_COPY_WARPS", tuning.stream_copy_warps);
     tuning.stream_depth = env_int("DCB200_STREAM_DEPTH", tuning.stream_depth);
     tuning.stream_ahead_mb = env_int("DCB200_STREAM_AHEAD_MB", tuning.stream_ahead_mb);
     tuning.stream_min_blocks = env_int("DCB200_STREAM_MINBLOCKS", tuning.stream_min_blocks);
     tuning.stream_draw_ahead = env_int("DCB200_STREAM_DRAW_AHEAD", tuning.stream_draw_ahead);
     p->stream_warps = tuning.stream_warps;
     p->stream_nbuf = tuning.stream_nbuf;
+    p->stream_copy_warps = tuning.stream_copy_warps;
     p->stream_rows = (tuning.stream && dcbt::stream_rows_for(p->info, tuning.stream_warps) > 0)
                          ? (tuning.stream_rows > 0 ? tuning.stream_rows : dcbt::stream_rows_for(p->info, tuning.stream_warps)) : 0;
     p->unroll = tuning.unroll;
@@ -317,7 +319,7 @@ dcb_status finish_pipeline(dcb_ctx* ctx, dcb_pipeline* p) {
     if (p->k_stream) {
         const int dyn = (int)dcbt::stream_smem_bytes(p->info, p->stream_rows, p->stream_warps, p->stream_nbuf);
         if (cudaFuncSetAttribute(p->k_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_stream, dcbt::stream_block_threads(p->stream_warps), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_stream = occ;
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, p->k_stream, dcbt::stream_block_threads(p->stream_warps, p->stream_copy_warps), (size_t)dyn) == cudaSuccess && occ > 0) p->occ_stream = occ;
         else { (void)cudaGetLastError(); p->k_stream = nullptr; }
     }
     CU(ctx, cudaMalloc(&p->d_result, DCB_DEVICE_RESULT_BYTES));
@@ -842,6 +844,7 @@ extern "C" dcb_status dcb_pipeline_compile(dcb_ctx* ctx, const dcb_pipeline_desc
         p->stream_rows = b->stream_rows;
         p->stream_warps = b->stream_warps;
         p->stream_nbuf = b->stream_nbuf;
+        p->stream_copy_warps = b->stream_copy_warps;
         p->source.clear();
     } else if ((st = load_jit(ctx, p)) != DCB_OK) {
         free_pipeline(p);
@@ -991,7 +994,7 @@ dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int
             void* pargs[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&out, (void*)&cap, (void*)&sc.cdesc, (void*)&epoch, (void*)&spin,
                              (void*)&num_tiles, (void*)&d_prev, (void*)&res, (void*)&abort_flag, (void*)&counters, (void*)&head, (void*)&kernel_flags};
             const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)ctx->sm_count * std::min(occ_cap, p->occ_stream));
-            CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps)), pargs,
+            CU(ctx, cudaLaunchKernel(p->k_stream, dim3(grid), dim3(dcbt::stream_block_threads(p->stream_warps, p->stream_copy_warps)), pargs,
                                      (size_t)dcbt::stream_smem_bytes(I, p->stream_rows, p->stream_warps, p->stream_nbuf), s));
             ctx->launches += 1;
             return DCB_OK;

@@ -13,6 +13,7 @@ struct dcb_builtin_entry {
     int stream_rows;        // rows per worker warp it was built with
     int stream_warps;       // worker warps per block
     int stream_nbuf;        // shared-memory slots per input
+    int stream_copy_warps;  // warps per block that only write tiles out
 };
 
 const dcb_builtin_entry* dcb_builtin_find(const char* key);

@@ -1314,11 +1314,14 @@ __device__ __forceinline__ int stream_rank_and_stage(const Pack<typename C::in0_
         }
         incl[w] = v;
     }
+    u32 tot[WORDS];
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) tot[w] = __shfl_sync(0xffffffffu, incl[w], 31);
     int row_start = 0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
         const int w = r / PER_WORD, sh = (r % PER_WORD) * FIELD;
-        const u32 tot_word = __shfl_sync(0xffffffffu, incl[w], 31);
+        const u32 tot_word = tot[w];
         const int before = (int)(((incl[w] - packed[w]) >> sh) & FMASK);
         u32 addr = stage_addr + (u32)(row_start + before) * (u32)sizeof(O);
 #pragma unroll
@@ -1404,7 +1407,7 @@ __device__ __forceinline__ void l2_prefetch_bulk(const void* src_global, u32 byt
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
 }
 
-template <class C, int WARPS, int ROWS, int LAG, int NBUF, int DEPTH, int AHEAD_BYTES, int DRAW_AHEAD>
+template <class C, int WARPS, int ROWS, int LAG, int NBUF, int DEPTH, int AHEAD_BYTES, int DRAW_AHEAD, int COPY_WARPS>
 __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __restrict__ in0, const typename C::in1_t* __restrict__ in1,
                                                     i64 n, typename C::out_t* __restrict__ out, i64 out_cap,
                                                     u64* __restrict__ desc, u32 epoch, u32 spin_limit, i64 num_tiles,
@@ -1415,6 +1418,7 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
     static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
     static_assert(LAG >= 2 && NBUF >= LAG + 2 && NBUF <= 16, "an offset is ready two rounds after its tile was ranked; NBUF = LAG + 1 + tiles on their way in");
     static_assert(WARPS >= 1 && WARPS <= 30 && DEPTH >= 1 && DEPTH <= 8, "one offsets lane per worker warp; DEPTH * 128 tiles per window");
+    static_assert(COPY_WARPS >= 0 && COPY_WARPS <= WARPS, "copy warps share the worker warps' runs among them");
     static_assert(WARPS * ROWS * 32 * (16 / (int)sizeof(typename C::in0_t)) < (1 << 19), "a tile's count must fit the descriptor");
     constexpr int E = 16 / (int)sizeof(A);
     constexpr int WARP_ELEMS = ROWS * 32 * E;
@@ -1459,7 +1463,7 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int st = 0; st < NBUF; ++st) {
-            mbar_init(&s_full[st], 1u); mbar_init(&s_ranked[st], (u32)WARPS); mbar_init(&s_offs[st], 1u); mbar_init(&s_empty[st], (u32)WARPS);
+            mbar_init(&s_full[st], 1u); mbar_init(&s_ranked[st], (u32)WARPS); mbar_init(&s_offs[st], 1u); mbar_init(&s_empty[st], (u32)(COPY_WARPS > 0 ? COPY_WARPS : WARPS));
         }
         s_dead = 0;
         fence_async_smem();                                   // the barriers exist before a copy can complete on them
@@ -1491,7 +1495,8 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                     const i64 rr = r - DRAW_AHEAD;
                     if (!wait(&s_ranked[(int)(rr % NBUF)], (u32)((rr / NBUF) & 1), true)) { *dead = 1; break; }
                 }
-                // The id is asked for before the wait for the slot: the counter's round trip overlaps that wait.
+                // The id is asked for before the wait for the slot: the counter's round trip overlaps that wait. (Asking one
+                // round earlier still changed nothing: the counter is not what a round waits for.)
                 i64 t = num_tiles;
                 if (!((run_flags & STREAM_TAKE) && *(volatile unsigned int*)(abort_flag + 2) == epoch)) {   // Take(k) already satisfied?
                     t = (i64)atomicAdd(counters, 1u);
@@ -1605,12 +1610,43 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                 if (++st == NBUF) { st = 0; ph ^= 1u; }
             }
         }
+    } else if (COPY_WARPS > 0 && warp_id >= 2 + WARPS) {
+        // ---------------------------------------------------------------- copy warps (COPY_WARPS > 0)
+        // Writing a tile out is mostly waiting - for shared memory, then for room in the store queue - and ranking is
+        // mostly arithmetic; in one warp the two only take turns. Here they are different warps' work: these warps move
+        // the runs the workers staged, the workers go straight on to the next tile.
+        const int c = warp_id - 2 - WARPS;
+        int sj = 0; u32 pj = 0;
+        for (;;) {
+            // The round's tile id: its `full` phase completed LAG rounds ago and cannot complete again before these warps
+            // give the slot back.
+            if (!wait(&s_full[sj], pj, true)) { *dead = 1; break; }
+            if (s_tile[sj] >= num_tiles) break;
+            { DCB_STAT_BEGIN;
+              if (!wait(&s_offs[sj], pj, true)) { *dead = 1; break; }
+              if (c == 0) DCB_STAT_END(4, 2); }
+            DCB_STAT_BEGIN;
+            bool gave_up = false;
+#pragma unroll 1
+            for (int w = c; w < WARPS; w += COPY_WARPS) {
+                const i64 off = s_off[sj][w];
+                if (off < 0) { gave_up = true; break; }
+                const O* stage0 = reinterpret_cast<const O*>(reinterpret_cast<const A*>(s_dyn + (size_t)sj * BYTES_A) + w * WARP_ELEMS);
+                compact_copy_out<O, DCB_STREAM_VEC_OUT != 0>(out, out_cap, off, s_cnt[sj][w], lane, stage0);
+            }
+            if (gave_up) { *dead = 1; break; }
+            fence_async_smem();                               // this warp's reads of the slot come before the next copy into it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[sj]);
+            if (c == 0) DCB_STAT_END(4, 3);
+            if (++sj == NBUF) { sj = 0; pj ^= 1u; }
+        }
     } else {
         // ---------------------------------------------------------------- workers
         const int w = warp_id - 2;
         i64 nvalid = (i64)1 << 62;                            // rounds in which this block has a tile
         int st = 0, sj = 0; u32 ph = 0, pj = 0;               // slot and phase of round k, and of round k - LAG
-        for (i64 k = 0; k < nvalid + LAG; ++k) {
+        for (i64 k = 0; k < nvalid + (COPY_WARPS > 0 ? 0 : LAG); ++k) {
             if (k < nvalid) {
                 { DCB_STAT_BEGIN;
                   if (!wait(&s_full[st], ph, true)) { *dead = 1; break; }
@@ -1650,11 +1686,12 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                     if (lane == 0) s_cnt[st][w] = run;
                     if (w == 0) DCB_STAT_END(2, 1);
                 }
+                if (COPY_WARPS > 0) fence_async_smem();       // the staged run was written here and is read, and the slot given back, elsewhere
                 __syncwarp();                                 // the staged run and its count are written
                 if (lane == 0) mbar_arrive(&s_ranked[st]);    // also for the round without a tile: it ends the offsets warp
                 if (++st == NBUF) { st = 0; ph ^= 1u; }
             }
-            if (k >= LAG) {
+            if (COPY_WARPS == 0 && k >= LAG) {
                 if (k - LAG < nvalid) {                       // write the tile ranked LAG rounds ago, give its slot back
                     { DCB_STAT_BEGIN;
                       if (!wait(&s_offs[sj], pj, true)) { *dead = 1; break; }
@@ -1679,7 +1716,7 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
     }
 
 #ifdef DCB_STREAM_STATS
-    if (lane == 0 && (warp_id == 0 ? DCB_STREAM_STATS == 1 : (warp_id == 1 ? DCB_STREAM_STATS == 3 : (warp_id == 2 && DCB_STREAM_STATS == 2))))
+    if (lane == 0 && (warp_id == 0 ? DCB_STREAM_STATS == 1 : (warp_id == 1 ? DCB_STREAM_STATS == 3 : (warp_id == 2 ? DCB_STREAM_STATS == 2 : (warp_id == 2 + WARPS && DCB_STREAM_STATS == 4)))))
         for (int i = 0; i < 4; ++i) atomicAdd((u64*)&res->pad[i], (u64)stat[i]);
 #endif
     __syncthreads();

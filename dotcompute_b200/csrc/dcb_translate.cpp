@@ -1009,7 +1009,7 @@ long long stream_tile_elems(const ChainInfo& info, int rows, int warps) { return
 long long stream_smem_bytes(const ChainInfo& info, int rows, int warps, int nbuf) {
     return (long long)nbuf * stream_tile_elems(info, rows, warps) * pipe_bytes_per_elem(info);
 }
-int stream_block_threads(int warps) { return (warps + 2) * 32; }
+int stream_block_threads(int warps, int copy_warps) { return (warps + 2 + copy_warps) * 32; }
 
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
                           const Tuning& tuning, bool with_prelude) {
@@ -1051,7 +1051,7 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                  "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag);\n}\n";
             if (v == 0 && tuning.stream && stream_rows_for(info, tuning.stream_warps) > 0) {
                 const int srow = tuning.stream_rows > 0 ? tuning.stream_rows : stream_rows_for(info, tuning.stream_warps);
-                const std::string ST = std::to_string(stream_block_threads(tuning.stream_warps));
+                const std::string ST = std::to_string(stream_block_threads(tuning.stream_warps, tuning.stream_copy_warps));
                 const std::string sbounds = tuning.stream_min_blocks > 0 ? ST + ", " + std::to_string(tuning.stream_min_blocks) : ST;
                 s += "extern \"C\" __global__ void __launch_bounds__(" + sbounds + ") dcb_compact_stream" + suffix +
                      "(const void* in0, const void* in1, long long n, void* out, long long out_cap, unsigned long long* desc, "
@@ -1059,7 +1059,7 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
                      "unsigned int* counters, unsigned int head, unsigned int run_flags) {\n"
                      "    dcb::compact_stream_body<" + C + ", " + std::to_string(tuning.stream_warps) + ", " + std::to_string(srow) + ", " +
                      std::to_string(tuning.stream_lag) + ", " + std::to_string(tuning.stream_nbuf) + ", " + std::to_string(tuning.stream_depth) + ", " +
-                     std::to_string(tuning.stream_ahead_mb) + " << 20, " + std::to_string(tuning.stream_draw_ahead) + ">(" + cast_in() + ", n, (" + C +
+                     std::to_string(tuning.stream_ahead_mb) + " << 20, " + std::to_string(tuning.stream_draw_ahead) + ", " + std::to_string(tuning.stream_copy_warps) + ">(" + cast_in() + ", n, (" + C +
                      "::out_t*)out, out_cap, desc, epoch, spin_limit, num_tiles, (const dcb::DeviceResult*)prev, (dcb::DeviceResult*)res, abort_flag, counters, head, run_flags);\n}\n";
             }
         } else {

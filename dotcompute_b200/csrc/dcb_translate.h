@@ -74,6 +74,7 @@ struct Tuning {
     int stream_warps = 4;       // worker warps per block (the block has two more warps: offsets and loader)
     int stream_rows = 0;        // rows of 32 packs per worker and tile; 0 = automatic (stream_rows_for)
     int stream_lag = 3;         // rounds between ranking a tile and writing it (its offset is ready after two)
+    int stream_copy_warps = 2;  // warps that only write ranked tiles out (0: every worker writes its own run after ranking the next tile)
     int stream_nbuf = 5;        // shared-memory slots per input: lag + 1 + tiles on their way in
     int stream_depth = 3;       // 16-byte descriptor loads per lane of the offsets warp (128 * depth tiles per window)
     int stream_ahead_mb = 12;   // distance of the L2 prefetch in front of the tile being drawn; 0 = none
@@ -87,7 +88,7 @@ struct Tuning {
 int stream_rows_for(const ChainInfo& info, int warps);
 long long stream_tile_elems(const ChainInfo& info, int rows, int warps);
 long long stream_smem_bytes(const ChainInfo& info, int rows, int warps, int nbuf);
-int stream_block_threads(int warps);
+int stream_block_threads(int warps, int copy_warps);
 std::string build_program(const ChainInfo& info, const std::string& suffix, const std::string& kernels_header,
                           const Tuning& tuning, bool with_prelude);
 

@@ -124,7 +124,7 @@ def test_streamed_compaction_kernel_is_generated_where_it_applies():
     for queries whose output element is no wider than the first input's; every compaction query keeps the
     one-tile-per-block kernels (vector and scalar) as the route for everything else."""
     src = generate_source(np.int64, [(N.OP_WHERE, "k => (k & 0xF) == 3"), (N.OP_TOARRAY, None)])
-    assert "dcb::compact_stream_body<dcb_chain, 4, 10, 3, 5, 3, " in src and "__launch_bounds__(192, 2) dcb_compact_stream(" in src
+    assert "dcb::compact_stream_body<dcb_chain, 4, 10, 3, 5, 3, " in src and "__launch_bounds__(256, 2) dcb_compact_stream(" in src
     assert "dcb_compact_vec(" in src and "dcb_compact_scalar(" in src
     src = generate_source(np.float32, [(N.OP_ZIP, "(x, y) => x * y"), (N.OP_WHERE, "v => v > 0f"), (N.OP_TOARRAY, None)], np.float32)
     assert "dcb::compact_stream_body<dcb_chain, 4, 5, 3, 5, 3, " in src          # two inputs: half the rows, same bytes per slot

@@ -32,9 +32,10 @@ class MBar:
 
 
 class Sim:
-    def __init__(self, num_tiles, grid, resident, warps, lag, nbuf, seed):
+    def __init__(self, num_tiles, grid, resident, warps, lag, nbuf, seed, copy_warps=0):
         self.rng = random.Random(seed)
         self.num_tiles, self.grid, self.resident, self.W, self.lag, self.nbuf = num_tiles, grid, resident, warps, lag, nbuf
+        self.CW = copy_warps                    # 0: every worker writes its own run; else that many warps only write
         self.counts = [[self.rng.randrange(0, 9) for _ in range(warps)] for _ in range(num_tiles)]
         self.desc = [None] * num_tiles          # published tile totals
         self.counter = 0
@@ -49,12 +50,13 @@ class Sim:
         blk.full = [MBar(1) for _ in range(nb)]
         blk.ranked = [MBar(W) for _ in range(nb)]
         blk.offs = [MBar(1) for _ in range(nb)]
-        blk.empty = [MBar(W) for _ in range(nb)]
+        blk.empty = [MBar(self.CW or W) for _ in range(nb)]
         blk.tile = [None] * nb
         blk.cnt = [[None] * W for _ in range(nb)]
         blk.off = [[None] * W for _ in range(nb)]
         blk.busy = [False] * nb                 # slot holds a tile that has not been written out by every worker
         blk.agents = [self.loader(blk), self.offsets(blk)] + [self.worker(blk, w) for w in range(W)]
+        blk.agents += [self.copier(blk, c) for c in range(self.CW)]
         return blk
 
     def loader(self, blk):
@@ -116,7 +118,7 @@ class Sim:
         st = sj = ph = pj = 0
         nvalid = 1 << 62
         k = 0
-        while k < nvalid + self.lag:
+        while k < nvalid + (0 if self.CW else self.lag):
             if k < nvalid:
                 while not blk.full[st].test(ph):
                     yield
@@ -130,7 +132,7 @@ class Sim:
                 if st == self.nbuf:
                     st, ph = 0, ph ^ 1
                 yield
-            if k >= self.lag:
+            if not self.CW and k >= self.lag:
                 if k - self.lag < nvalid:
                     while not blk.offs[sj].test(pj):
                         yield
@@ -144,6 +146,30 @@ class Sim:
                 if sj == self.nbuf:
                     sj, pj = 0, pj ^ 1
             k += 1
+            yield
+
+    def copier(self, blk, c):
+        """A warp that only writes: the round's tile id comes from the slot's `full` phase (long complete), then the
+        offsets; it writes the runs of workers c, c + CW, ... and gives the slot back."""
+        sj = pj = 0
+        while True:
+            while not blk.full[sj].test(pj):
+                yield
+            tile = blk.tile[sj]
+            if tile >= self.num_tiles:
+                return
+            while not blk.offs[sj].test(pj):
+                yield
+            assert blk.tile[sj] == tile, "the slot was reloaded while a copy warp still had to write it"
+            for w in range(c, self.W, self.CW):
+                assert (tile, w) not in self.written
+                self.written[(tile, w)] = blk.off[sj][w]
+            blk.empty[sj].arrive()
+            if blk.empty[sj].pending == blk.empty[sj].count:
+                blk.busy[sj] = False
+            sj += 1
+            if sj == self.nbuf:
+                sj, pj = 0, pj ^ 1
             yield
 
     # ---- scheduler
@@ -200,3 +226,15 @@ def test_stream_protocol_many_random_shapes():
         sim = Sim(r.randrange(1, 90), grid, r.randrange(1, grid + 1), warps=r.randrange(1, 5), lag=lag, nbuf=nbuf, seed=r.randrange(1 << 30))
         assert sim.run()
         sim.check()
+
+
+@pytest.mark.parametrize("warps,copy_warps", [(4, 2), (4, 1), (3, 3), (5, 2)])
+@pytest.mark.parametrize("grid,resident", [(1, 1), (6, 2), (7, 1), (12, 5)])
+def test_stream_protocol_with_copy_warps(warps, copy_warps, grid, resident):
+    """The same with the writing done by warps of their own (the kernel's default shape: 4 workers, 2 copy warps)."""
+    for seed in range(6):
+        num_tiles = [1, 3, 17, 64][seed % 4] + seed
+        for lag, nbuf in ((2, 4), (3, 5), (3, 7)):
+            sim = Sim(num_tiles, grid, resident, warps=warps, lag=lag, nbuf=nbuf, seed=seed * 104729 + warps, copy_warps=copy_warps)
+            assert sim.run(), "the schedule stopped with work left"
+            sim.check()
