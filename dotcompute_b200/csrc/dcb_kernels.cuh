@@ -1416,7 +1416,8 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                                                     u32 run_flags) {
     typedef typename C::in0_t A; typedef typename C::in1_t B; typedef typename C::out_t O;
     static_assert(sizeof(O) <= sizeof(A), "in-place staging needs an output element no larger than the input element");
-    static_assert(LAG >= 2 && NBUF >= LAG + 2 && NBUF <= 16, "an offset is ready two rounds after its tile was ranked; NBUF = LAG + 1 + tiles on their way in");
+    static_assert(COPY_WARPS > 0 || (LAG >= 2 && NBUF >= LAG + 2), "workers that also write: an offset is ready two rounds after its tile was ranked; NBUF = LAG + 1 + tiles on their way in");
+    static_assert(NBUF >= 3 && NBUF <= 16, "one slot on its way in, one being ranked, one waiting to be written");
     static_assert(WARPS >= 1 && WARPS <= 30 && DEPTH >= 1 && DEPTH <= 8, "one offsets lane per worker warp; DEPTH * 128 tiles per window");
     static_assert(COPY_WARPS >= 0 && COPY_WARPS <= WARPS, "copy warps share the worker warps' runs among them");
     static_assert(WARPS * ROWS * 32 * (16 / (int)sizeof(typename C::in0_t)) < (1 << 19), "a tile's count must fit the descriptor");
