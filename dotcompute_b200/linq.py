@@ -373,10 +373,17 @@ class ComputeQueryable:
         if n <= 1:
             return ComputeQueryable(values, acc, (), None, self._force_jit)
         keys = self._keys_of(values, key_selector)
+        out = acc.Memory.AllocateAsync(n, values.dtype)
+        if values.dtype.itemsize == 4:
+            # 4-byte elements travel beside their keys through the sort: no gather afterwards
+            N.check(N.lib().dcb_sort_by_key(acc.handle, dcb_type(keys.dtype), C.c_void_p(keys.GetDeviceMemory()), n, 1 if descending else 0, 4,
+                                            C.c_void_p(values.GetDeviceMemory()), C.c_void_p(out.GetDeviceMemory()), None), acc.handle)
+            acc.Synchronize()
+            keys.Dispose()
+            return ComputeQueryable(out, acc, (), None, self._force_jit)
         idx = acc.Memory.AllocateAsync(n, np.uint32)
         N.check(N.lib().dcb_sort_indices(acc.handle, dcb_type(keys.dtype), C.c_void_p(keys.GetDeviceMemory()), n, 1 if descending else 0,
                                          C.c_void_p(idx.GetDeviceMemory()), None), acc.handle)
-        out = acc.Memory.AllocateAsync(n, values.dtype)
         N.check(N.lib().dcb_gather(acc.handle, values.dtype.itemsize, C.c_void_p(values.GetDeviceMemory()), C.c_void_p(idx.GetDeviceMemory()), n,
                                    C.c_void_p(out.GetDeviceMemory()), None), acc.handle)
         acc.Synchronize()
