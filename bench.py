@@ -277,6 +277,18 @@ def measure_relational(acc, steps=5):
         bool(np.all((np.diff(gi) > 0) | (np.diff(go) > 0)))                  # inner indices ascend inside one outer element
     out["join-inner-i64-2p24x2p20"] = {"what": "Join of 2^24 outer and 2^20 inner int64 keys, pairs in Enumerable.Join order", "n_elements": no,
                                        "pairs": m, "ms": ms, "elements_per_s": no / (ms * 1e-3), "parity": bool(ok)}
+    del do, di, oo, io
+    # Scan: running sum of 2^26 float32 (fp64 accumulation, each output rounded once)
+    x = _rng(45).random(n, dtype=np.float32)
+    dx = torch.from_numpy(x).to(dev)
+    ds = torch.empty_like(dx)
+    ms = timed(lambda: N.check(N.lib().dcb_prefix_sum(acc.handle, N.T_F32, C.c_void_p(dx.data_ptr()), n, 1, C.c_void_p(ds.data_ptr()), C.c_void_p(1)), acc.handle))
+    want = np.cumsum(x.astype(np.float64))
+    err = float(np.max(np.abs(ds.cpu().numpy().astype(np.float64) - want)))
+    out["scan-f32-2p26"] = {"what": "Scan(): inclusive running sum of 2^26 float32 (tile totals, scan of totals, tiles)", "n_elements": n, "ms": ms,
+                            "elements_per_s": n / (ms * 1e-3), "bytes_per_element": 12, "achieved_gbs": n * 12 / (ms * 1e-3) / 1e9,
+                            "frac": n * 12 / (ms * 1e-3) / 1e9 / peak, "max_abs_error": err,
+                            "parity": bool(err <= 1e-5 * float(np.abs(x).astype(np.float64).sum()))}
     return out
 
 

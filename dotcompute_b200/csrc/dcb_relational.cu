@@ -289,6 +289,144 @@ dcb_status exclusive_scan(const u32* d_in, u32* d_out, i64 n, u32* d_totals, u32
 }
 size_t scan_totals_count(i64 n) { return (size_t)((n + kScanTile - 1) / kScanTile) + 1; }
 
+// ---------------------------------------------------------------------------------------------- prefix sum of a column
+// out[i] = in[0] + ... + in[i] (inclusive) or ... + in[i-1] (exclusive), over any number of blocks: tile totals, one scan of
+// the totals, then every tile scans itself starting from the sum before it - 12 bytes per 4-byte element. Integers add in
+// their own width and wrap (what the reference's generated kernel does, CudaKernelGenerator.cs:499-576, which stops at one
+// block of 256); floats add in fp64 and every output is rounded once, so the result does not depend on the grid.
+template <typename T> struct ScanAcc;
+template <> struct ScanAcc<int> { typedef u32 acc_t; static __device__ __forceinline__ u32 in(int v) { return (u32)v; } static __device__ __forceinline__ int out(u32 a) { return (int)a; } };
+template <> struct ScanAcc<i64> { typedef u64 acc_t; static __device__ __forceinline__ u64 in(i64 v) { return (u64)v; } static __device__ __forceinline__ i64 out(u64 a) { return (i64)a; } };
+template <> struct ScanAcc<float> { typedef double acc_t; static __device__ __forceinline__ double in(float v) { return (double)v; } static __device__ __forceinline__ float out(double a) { return (float)a; } };
+template <> struct ScanAcc<double> { typedef double acc_t; static __device__ __forceinline__ double in(double v) { return v; } static __device__ __forceinline__ double out(double a) { return a; } };
+
+template <typename A> __device__ __forceinline__ A shfl_up_acc(A v, int d);
+template <> __device__ __forceinline__ u32 shfl_up_acc<u32>(u32 v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+template <> __device__ __forceinline__ u64 shfl_up_acc<u64>(u64 v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+template <> __device__ __forceinline__ double shfl_up_acc<double>(double v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+
+// Sum of the block's values in thread order; every thread gets (sum of the threads before it, block total).
+template <typename A>
+__device__ __forceinline__ void block_exclusive(A mine, A* s_warp /* kWarps */, A& before, A& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    A incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const A t = shfl_up_acc<A>(incl, d); if (lane >= d) incl = incl + t; }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    A off = A(0); total = A(0);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) { if (w < warp) off = off + s_warp[w]; total = total + s_warp[w]; }
+    before = off + incl - mine;
+    __syncthreads();
+}
+// A thread's kItems consecutive elements, with 16-byte accesses when the tile lies inside the array and the column starts
+// at a 16-byte boundary (a thread's run then does too), element by element otherwise.
+template <typename T>
+__device__ __forceinline__ void load_run(const T* __restrict__ in, i64 base, i64 n, bool vec, T (&v)[kItems]) {
+    constexpr int VE = 16 / (int)sizeof(T);
+    if (vec) {
+        const uint4* p = reinterpret_cast<const uint4*>(in + base);
+#pragma unroll
+        for (int q = 0; q < kItems / VE; ++q) {
+            const uint4 w = __ldcs(p + q);
+            *reinterpret_cast<uint4*>(&v[q * VE]) = w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) v[i] = base + i < n ? in[base + i] : T(0);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store_run(T* __restrict__ out, i64 base, i64 n, bool vec, const T (&v)[kItems]) {
+    constexpr int VE = 16 / (int)sizeof(T);
+    if (vec) {
+        uint4* p = reinterpret_cast<uint4*>(out + base);
+#pragma unroll
+        for (int q = 0; q < kItems / VE; ++q) __stcs(p + q, *reinterpret_cast<const uint4*>(&v[q * VE]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) if (base + i < n) out[base + i] = v[i];
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads) prefix_tile_totals(const T* __restrict__ in, i64 n, typename ScanAcc<T>::acc_t* __restrict__ totals) {
+    typedef typename ScanAcc<T>::acc_t A;
+    __shared__ A s_warp[kWarps];
+    const i64 base = (i64)blockIdx.x * kTile + (i64)threadIdx.x * kItems;
+    const bool vec = (i64)(blockIdx.x + 1) * kTile <= n && (reinterpret_cast<unsigned long long>(in) & 15ull) == 0;
+    __align__(16) T x[kItems];
+    load_run<T>(in, base, n, vec, x);
+    A sum = A(0);
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) sum = sum + ScanAcc<T>::in(x[i]);   // same order as prefix_tiles: same bits
+    A before, total;
+    block_exclusive<A>(sum, s_warp, before, total);
+    if (threadIdx.x == 0) totals[blockIdx.x] = total;
+}
+template <typename A>
+__global__ void __launch_bounds__(1024) prefix_scan_totals(A* __restrict__ totals, u32 count) {
+    // one block: exclusive scan of the tile totals in tile order, 1024 at a time with a running carry
+    __shared__ A s_warp[32];
+    __shared__ A s_carry;
+    if (threadIdx.x == 0) s_carry = A(0);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (u32 base = 0; base < count; base += 1024) {
+        const u32 i = base + threadIdx.x;
+        const A v = i < count ? totals[i] : A(0);
+        A incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { const A t = shfl_up_acc<A>(incl, d); if (lane >= d) incl = incl + t; }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        A off = A(0), all = A(0);
+        for (int w = 0; w < 32; ++w) { if (w < warp) off = off + s_warp[w]; all = all + s_warp[w]; }
+        const A carry = s_carry;
+        if (i < count) totals[i] = carry + off + incl - v;
+        __syncthreads();
+        if (threadIdx.x == 0) s_carry = carry + all;
+        __syncthreads();
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads) prefix_tiles(const T* __restrict__ in, i64 n, const typename ScanAcc<T>::acc_t* __restrict__ totals_excl,
+                                                        int inclusive, T* __restrict__ out) {
+    typedef typename ScanAcc<T>::acc_t A;
+    __shared__ A s_warp[kWarps];
+    const i64 base = (i64)blockIdx.x * kTile + (i64)threadIdx.x * kItems;
+    const bool vec = (i64)(blockIdx.x + 1) * kTile <= n && ((reinterpret_cast<unsigned long long>(in) | reinterpret_cast<unsigned long long>(out)) & 15ull) == 0;
+    __align__(16) T x[kItems];
+    load_run<T>(in, base, n, vec, x);
+    A sum = A(0);
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) sum = sum + ScanAcc<T>::in(x[i]);
+    A before, total;
+    block_exclusive<A>(sum, s_warp, before, total);
+    A run = totals_excl[blockIdx.x] + before;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const A next = run + ScanAcc<T>::in(x[i]);
+        x[i] = ScanAcc<T>::out(inclusive ? next : run);
+        run = next;
+    }
+    store_run<T>(out, base, n, vec, x);
+}
+template <typename T>
+dcb_status prefix_sum_typed(const void* d_in, i64 n, int inclusive, void* d_out, cudaStream_t s) {
+    typedef typename ScanAcc<T>::acc_t A;
+    const u32 tiles = (u32)((n + kTile - 1) / kTile);
+    A* totals = nullptr;
+    RCU(cudaMallocAsync((void**)&totals, (size_t)tiles * sizeof(A), s));
+    prefix_tile_totals<T><<<tiles, kThreads, 0, s>>>((const T*)d_in, n, totals);
+    prefix_scan_totals<A><<<1, 1024, 0, s>>>(totals, tiles);
+    prefix_tiles<T><<<tiles, kThreads, 0, s>>>((const T*)d_in, n, totals, inclusive, (T*)d_out);
+    const cudaError_t e = cudaGetLastError();
+    cudaFreeAsync(totals, s);
+    if (e != cudaSuccess) { dcb_set_thread_error(cudaGetErrorString(e)); return DCB_ERR_CUDA; }
+    return DCB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------- the sort itself
 struct SortScratch {
     void* keys[2] = {nullptr, nullptr};
@@ -572,6 +710,27 @@ extern "C" dcb_status dcb_sort_by_key(dcb_ctx* ctx, int32_t key_type, const void
     st = sort_keys(sc, key_type, d_keys, n, descending, &buf, (const u32*)d_values, (u32*)d_sorted_values);
     sc.release();
     return st;
+}
+
+extern "C" dcb_status dcb_prefix_sum(dcb_ctx* ctx, int32_t elem_type, const void* d_in, int64_t n, int32_t inclusive, void* d_out, void* stream) {
+    if (!ctx) return bad("ctx is null");
+    if (n < 0) return bad("n is negative");
+    if (!(elem_type == DCB_T_I32 || elem_type == DCB_T_I64 || elem_type == DCB_T_F32 || elem_type == DCB_T_F64)) {
+        dcb_set_thread_error("prefix sums are defined for int, long, float and double (project with Select first)");
+        return DCB_ERR_NOT_SUPPORTED;
+    }
+    if (n == 0) return DCB_OK;
+    if (!d_in || !d_out) return bad("null pointer");
+    if (n > (int64_t)kTile * 0x7fffffffll) return bad("n is too large");
+    if (dcb_ctx_make_current(ctx)) return DCB_ERR_CUDA;
+    cudaStream_t s = (cudaStream_t)dcb_ctx_pick_stream(ctx, stream);
+    dcb_ctx_count_launches(ctx, 3);
+    switch (elem_type) {
+        case DCB_T_I32: return prefix_sum_typed<int>(d_in, n, inclusive, d_out, s);
+        case DCB_T_I64: return prefix_sum_typed<i64>(d_in, n, inclusive, d_out, s);
+        case DCB_T_F32: return prefix_sum_typed<float>(d_in, n, inclusive, d_out, s);
+        default: return prefix_sum_typed<double>(d_in, n, inclusive, d_out, s);
+    }
 }
 
 extern "C" dcb_status dcb_gather(dcb_ctx* ctx, int32_t elem_bytes, const void* d_src, const uint32_t* d_indices, int64_t n, void* d_dst, void* stream) {

@@ -390,6 +390,23 @@ class ComputeQueryable:
         idx.Dispose(); keys.Dispose()
         return ComputeQueryable(out, acc, (), None, self._force_jit)
 
+    def Scan(self, inclusive: bool = True) -> "ComputeQueryable":
+        """Running sum of the sequence (after its fused Select / Where): element i is the sum of elements 0..i (or 0..i-1 with
+        inclusive=False). The reference's visitor has the operation type (ExpressionTreeVisitor.cs:248-249) and a generator
+        for one block of 256 elements (CudaKernelGenerator.cs:499-576); this one takes any length. int / long add in their
+        own width and wrap, as that kernel's arithmetic does; float / double add in fp64, each output rounded once."""
+        acc = self.Accelerator
+        values = self.ToBuffer()
+        n = values.Length
+        if values.dtype not in (np.dtype(np.int32), np.dtype(np.int64), np.dtype(np.float32), np.dtype(np.float64)):
+            raise errors.NotSupportedException("Scan is defined for int, long, float and double (project with Select first)")
+        out = acc.Memory.AllocateAsync(max(n, 1), values.dtype).Slice(0, n) if n == 0 else acc.Memory.AllocateAsync(n, values.dtype)
+        if n:
+            N.check(N.lib().dcb_prefix_sum(acc.handle, dcb_type(values.dtype), C.c_void_p(values.GetDeviceMemory()), n, 1 if inclusive else 0,
+                                           C.c_void_p(out.GetDeviceMemory()), None), acc.handle)
+            acc.Synchronize()
+        return ComputeQueryable(out, acc, (), None, self._force_jit)
+
     def OrderBy(self, keySelector: str | None = None) -> "ComputeQueryable":
         """Stable ascending sort by `keySelector` (the elements themselves if None): a multi-block radix sort on the device.
         The reference's generator emits a single-block bitonic sort (CudaKernelGenerator.cs:613-751, OrderByKernelGenerator.cs:108);

@@ -110,6 +110,7 @@ PROTOTYPES = {
     "dcb_peer_disconnect": (_i32, [_vp]),
     "dcb_sort_indices": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp, _vp]),
     "dcb_sort_by_key": (_i32, [_vp, _i32, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "dcb_prefix_sum": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp, _vp]),
     "dcb_gather": (_i32, [_vp, _i32, _vp, _vp, _i64, _vp, _vp]),
     "dcb_group_aggregate": (_i32, [_vp, _i32, _vp, _i32, _vp, _i64, _i32, _i64, _vp, _vp, _vp, _vp, C.POINTER(_i64), _vp]),
     "dcb_join_indices": (_i32, [_vp, _i32, _vp, _i64, _vp, _i64, _i32, _i64, _vp, _vp, C.POINTER(_i64), _vp]),

@@ -389,6 +389,10 @@ dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
  *                        32-byte sector per element from all over the source: a quarter of OrderBy's time). value_bytes must
  *                        be 4; DCB_ERR_NOT_SUPPORTED otherwise (use dcb_sort_indices + dcb_gather). d_values may be d_keys.
  *   dcb_gather           dst[i] = src[indices[i]] for elements of 1, 2, 4 or 8 bytes.
+ *   dcb_prefix_sum       d_out[i] = d_in[0] + ... + d_in[i] (inclusive != 0) or ... + d_in[i-1] (exclusive) for int, long, float
+ *                        or double columns of any length (the reference's scan kernel, CudaKernelGenerator.cs:499-576,
+ *                        covers one block of 256). Integers add in their own width and wrap, as that kernel does; floats
+ *                        add in fp64 and each output is rounded once. d_out may be d_in.
  *   dcb_group_aggregate  groups n (key, value) pairs by key; aggregate = DCB_AGG_*. One output per group, in order of first
  *                        occurrence of the key (the order a Dictionary enumerates in, CpuKernelGenerator.cs:620-633):
  *                        d_out_first[g] = index of the group's first element (its key is keys[that]), d_out_counts[g], and
@@ -405,6 +409,7 @@ dcb_status dcb_sort_indices(dcb_ctx* ctx, int32_t key_type, const void* d_keys, 
                             uint32_t* d_indices, void* stream);
 dcb_status dcb_sort_by_key(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int64_t n, int32_t descending,
                            int32_t value_bytes, const void* d_values, void* d_sorted_values, void* stream);
+dcb_status dcb_prefix_sum(dcb_ctx* ctx, int32_t elem_type, const void* d_in, int64_t n, int32_t inclusive, void* d_out, void* stream);
 dcb_status dcb_gather(dcb_ctx* ctx, int32_t elem_bytes, const void* d_src, const uint32_t* d_indices, int64_t n, void* d_dst, void* stream);
 dcb_status dcb_group_aggregate(dcb_ctx* ctx, int32_t key_type, const void* d_keys, int32_t value_type, const void* d_values, int64_t n,
                                int32_t aggregate, int64_t out_cap, uint32_t* d_out_first, int64_t* d_out_counts, double* d_out_f64,

@@ -151,6 +151,23 @@ class Enumerable:
     def All(self, pred):
         return self.Where(pred).data.size == self.data.size
 
+    def Scan(self, inclusive=True):
+        """Running sum. Integers add in their own width and wrap (the arithmetic of the reference's generated scan kernel,
+        CudaKernelGenerator.cs:499-576); floats are summed sequentially in fp64 and rounded per element."""
+        d = self.data
+        if d.dtype in (np.int32, np.int64):
+            u = d.view(np.uint32 if d.dtype == np.int32 else np.uint64)
+            c = np.cumsum(u, dtype=u.dtype)
+            if not inclusive:
+                c = np.concatenate([np.zeros(1, u.dtype), c[:-1]]) if c.size else c
+            return Enumerable(c.view(d.dtype))
+        if d.dtype in (np.float32, np.float64):
+            c = np.cumsum(d.astype(np.float64))
+            if not inclusive:
+                c = np.concatenate([np.zeros(1), c[:-1]]) if c.size else c
+            return Enumerable(c.astype(d.dtype))
+        raise TypeError(f"Scan is not defined for {d.dtype}")
+
     def Sum(self):
         d = self.data
         if d.dtype in (np.float32, np.float64):

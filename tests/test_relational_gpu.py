@@ -105,3 +105,57 @@ def test_sort_is_a_permutation_at_scale(acc):
     assert got.view(np.uint32).astype(np.uint64).sum() == x.view(np.uint32).astype(np.uint64).sum()
     assert np.bitwise_xor.reduce(got.view(np.uint32)) == np.bitwise_xor.reduce(x.view(np.uint32))
     assert got[0] == x.min() and got[-1] == x.max()
+
+
+def test_sort_by_key_carries_values_of_another_type(acc):
+    """dcb_sort_by_key through the C ABI: float values ordered by separate integer keys with many ties (stable), both
+    directions; values wider than 4 bytes and an output that aliases the input are refused."""
+    import ctypes as C
+    from dotcompute_b200 import native as N
+    r = rng(91)
+    for n in (1, 4096, 4097, 777_777):
+        keys = r.integers(-50, 50, n, dtype=np.int64)
+        vals = r.standard_normal(n).astype(F)
+        dk, dv = acc.Memory.AllocateAndCopyAsync(keys), acc.Memory.AllocateAndCopyAsync(vals)
+        out = acc.Memory.AllocateAsync(n, F)
+        for desc in (0, 1):
+            N.check(N.lib().dcb_sort_by_key(acc.handle, N.T_I64, C.c_void_p(dk.GetDeviceMemory()), n, desc, 4,
+                                            C.c_void_p(dv.GetDeviceMemory()), C.c_void_p(out.GetDeviceMemory()), None), acc.handle)
+            acc.Synchronize()
+            order = np.argsort(-keys if desc else keys, kind="stable")
+            assert np.array_equal(out.CopyToAsync().view(np.uint32), vals[order].view(np.uint32))
+        assert N.lib().dcb_sort_by_key(acc.handle, N.T_I64, C.c_void_p(dk.GetDeviceMemory()), n, 0, 8,
+                                       C.c_void_p(dk.GetDeviceMemory()), C.c_void_p(out.GetDeviceMemory()), None) == 302   # DCB_ERR_NOT_SUPPORTED
+        assert N.lib().dcb_sort_by_key(acc.handle, N.T_I64, C.c_void_p(dk.GetDeviceMemory()), n, 0, 4,
+                                       C.c_void_p(dv.GetDeviceMemory()), C.c_void_p(dv.GetDeviceMemory()), None) == 301   # DCB_ERR_INVALID_ARGUMENT
+        dk.Dispose(); dv.Dispose(); out.Dispose()
+
+
+@pytest.mark.parametrize("n", [0, 1, 255, 4096, 4097, 1_000_003, (1 << 24) + 5])
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
+def test_scan_running_sum(acc, n, dtype):
+    """Running sums over one element to thousands of tiles: integers bit-exact (they wrap in their own width), floats
+    within 1e-5 * sum|x| of the sequential fp64 running sum (and normally equal to it after the rounding)."""
+    r = rng(n * 3 + 1)
+    if np.dtype(dtype).kind == "i":
+        info = np.iinfo(dtype)
+        x = r.integers(info.min // 2, info.max // 2, n, dtype=dtype)      # wraps many times over
+    else:
+        x = (r.standard_normal(n) * 10).astype(dtype)
+    for inclusive in (True, False):
+        got = AsComputeQueryable(x, acc).Scan(inclusive).ToArray()
+        want = Enumerable(x).Scan(inclusive).ToArray()
+        assert got.dtype == x.dtype and got.shape == want.shape
+        if np.dtype(dtype).kind == "i":
+            assert np.array_equal(got, want)
+        elif n:
+            tol = (1e-5 if dtype == np.float32 else 1e-12) * float(np.abs(x.astype(np.float64)).sum())
+            assert float(np.max(np.abs(got.astype(np.float64) - want.astype(np.float64)))) <= tol
+    if n:   # composes with the fused operators on both sides
+        got = AsComputeQueryable(x, acc).Where("v => v > 0").Select("v => v + v").Scan().Take(100).ToArray()
+        pos = x[x > 0]
+        want = Enumerable(pos + pos).Scan().ToArray()[:100]
+        if np.dtype(dtype).kind == "i":
+            assert np.array_equal(got, want)
+        else:
+            assert np.allclose(got, want, rtol=1e-5, atol=1e-3)
