@@ -171,12 +171,13 @@ struct Acc {
     u32 cnt32;     // per-thread running count; folded into `count` by finish()
     T mn, mx;
     i64 ifirst, ilast;   // RED_FIRST / RED_LAST: index of the first / last element that passed the chain
+    i64 zfirst;          // floating Min / Max: 2 * index + sign bit of the earliest zero seen (see zero_sign below)
     u32 flags;
 
     __device__ __forceinline__ void finish() { count += (i64)cnt32; cnt32 = 0; }
     __device__ __forceinline__ void init() {
         fsum = 0.0; isum_lo = 0; isum_hi = 0; count = 0; cnt32 = 0; flags = 0;
-        ifirst = 0x7fffffffffffffffLL; ilast = -1;
+        ifirst = 0x7fffffffffffffffLL; ilast = -1; zfirst = 0x7fffffffffffffffLL;
         if constexpr (same_t<T, float>::value) { mn = __int_as_float(0x7f800000); mx = __int_as_float(0xff800000); }
         else if constexpr (same_t<T, double>::value) { mn = __longlong_as_double(0x7ff0000000000000LL); mx = __longlong_as_double(0xfff0000000000000LL); }
         else if constexpr (same_t<T, bool>::value) { mn = true; mx = false; }
@@ -216,6 +217,31 @@ struct Acc {
         }
         if constexpr ((RED & (RED_COUNT | RED_MIN | RED_MAX | RED_FIRST | RED_LAST)) != 0) cnt32 += 1u;   // Sum alone needs no count
     }
+    // Enumerable.Min / Max replace their candidate only on a strict comparison, so among -0 and +0 (equal to each other)
+    // the one that comes first in the sequence is returned. note_zero remembers which that is; callers test a whole pack
+    // for zeros with one branch and call it only then (a branch per element costs a quarter of the kernel's time).
+    static constexpr bool TRACK_ZERO = is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0;
+    __device__ __forceinline__ void note_zero(T v, i64 idx) {
+        if (v == T(0)) {
+            const i64 z = idx * 2 + (signbit_of(v) ? 1 : 0);
+            zfirst = z < zfirst ? z : zfirst;
+        }
+    }
+    static __device__ __forceinline__ bool signbit_of(T v) {
+        if constexpr (same_t<T, float>::value) return (__float_as_uint(v) >> 31) != 0u;
+        else if constexpr (same_t<T, double>::value) return ((u64)__double_as_longlong(v) >> 63) != 0ull;
+        else return false;
+    }
+    // The sign a zero result of Min / Max carries: that of the earliest zero in the sequence.
+    __device__ __forceinline__ void zero_sign() {
+        if constexpr (is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0) {
+            if (zfirst != 0x7fffffffffffffffLL) {
+                const T z = (zfirst & 1) ? -T(0) : T(0);
+                if constexpr ((RED & RED_MIN) != 0) { if (mn == T(0)) mn = z; }
+                if constexpr ((RED & RED_MAX) != 0) { if (mx == T(0)) mx = z; }
+            }
+        }
+    }
     // Fixed-shape combine: `this` is the left (lower-index) operand.
     __device__ __forceinline__ void merge(const Acc& o) {
         if constexpr ((RED & RED_SUM) != 0) {
@@ -230,12 +256,14 @@ struct Acc {
         if constexpr ((RED & RED_MAX) != 0) mx = o.mx > mx ? o.mx : mx;
         if constexpr ((RED & RED_FIRST) != 0) ifirst = o.ifirst < ifirst ? o.ifirst : ifirst;
         if constexpr ((RED & RED_LAST) != 0) ilast = o.ilast > ilast ? o.ilast : ilast;
+        if constexpr (is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0) zfirst = o.zfirst < zfirst ? o.zfirst : zfirst;
         flags |= o.flags;
         count += o.count + (i64)o.cnt32;
     }
     __device__ __forceinline__ Acc shuffled(int lane_mask) const {
         Acc r;
-        r.fsum = 0.0; r.isum_lo = 0; r.isum_hi = 0; r.mn = mn; r.mx = mx; r.cnt32 = 0; r.ifirst = ifirst; r.ilast = ilast;
+        r.fsum = 0.0; r.isum_lo = 0; r.isum_hi = 0; r.mn = mn; r.mx = mx; r.cnt32 = 0; r.ifirst = ifirst; r.ilast = ilast; r.zfirst = zfirst;
+        if constexpr (is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0) r.zfirst = __shfl_xor_sync(0xffffffffu, zfirst, lane_mask);
         if constexpr ((RED & RED_FIRST) != 0) r.ifirst = __shfl_xor_sync(0xffffffffu, ifirst, lane_mask);
         if constexpr ((RED & RED_LAST) != 0) r.ilast = __shfl_xor_sync(0xffffffffu, ilast, lane_mask);
         if constexpr ((RED & RED_SUM) != 0) {
@@ -265,6 +293,7 @@ struct Acc {
     __device__ __forceinline__ void to_partial(Partial& p) const {
         p.fsum = fsum; p.isum_lo = isum_lo; p.isum_hi = isum_hi; p.count = count + (i64)cnt32; p.flags = flags;
         p.pad0 = 0; p.pad1 = 0;
+        if constexpr (is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0) p.pad1 = zfirst;
         if constexpr ((RED & (RED_FIRST | RED_LAST)) != 0) { p.mn_bits = ifirst; p.mx_bits = ilast; }   // index reductions use the Min / Max slots
         else if constexpr (is_fp<T>::value) { p.mn_bits = __double_as_longlong((double)mn); p.mx_bits = __double_as_longlong((double)mx); }
         else { p.mn_bits = (i64)mn; p.mx_bits = (i64)mx; }
@@ -286,11 +315,12 @@ struct Acc {
             const i64 b = __ldcg(&p->mx_bits);
             if constexpr (is_fp<T>::value) mx = (T)__longlong_as_double(b); else mx = (T)b;
         }
-        if constexpr ((RED & (RED_MIN | RED_MAX)) != 0 && is_fp<T>::value) flags = __ldcg(&p->flags);
+        if constexpr ((RED & (RED_MIN | RED_MAX)) != 0 && is_fp<T>::value) { flags = __ldcg(&p->flags); zfirst = __ldcg(&p->pad1); }
     }
     __device__ __forceinline__ void from_partial(const Partial& p) {
         fsum = p.fsum; isum_lo = p.isum_lo; isum_hi = p.isum_hi; count = p.count; cnt32 = 0; flags = p.flags;
-        ifirst = 0x7fffffffffffffffLL; ilast = -1;
+        ifirst = 0x7fffffffffffffffLL; ilast = -1; zfirst = 0x7fffffffffffffffLL;
+        if constexpr (is_fp<T>::value && (RED & (RED_MIN | RED_MAX)) != 0) zfirst = p.pad1;
         if constexpr ((RED & (RED_FIRST | RED_LAST)) != 0) { ifirst = p.mn_bits; ilast = p.mx_bits; mn = T(); mx = T(); }
         else if constexpr (is_fp<T>::value) { mn = (T)__longlong_as_double(p.mn_bits); mx = (T)__longlong_as_double(p.mx_bits); }
         else { mn = (T)p.mn_bits; mx = (T)p.mx_bits; }
@@ -415,12 +445,19 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
+            O ov[E]; bool kv[E]; bool zero = false;
 #pragma unroll
             for (int k = 0; k < E; ++k) {
-                O o; bool keep;
-                if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
-                else keep = C::apply(a[u].e[k], B(), o);
-                if (keep) acc.add(o, (base + (i64)u * BLOCK) * E + k);
+                if constexpr (C::n_in == 2) kv[k] = C::apply(a[u].e[k], b[u].e[k], ov[k]);
+                else kv[k] = C::apply(a[u].e[k], B(), ov[k]);
+                if (kv[k]) acc.add(ov[k], (base + (i64)u * BLOCK) * E + k);
+                if constexpr (Acc<O, RED>::TRACK_ZERO) zero = zero || (kv[k] && ov[k] == O(0));
+            }
+            if constexpr (Acc<O, RED>::TRACK_ZERO) {
+                if (zero) {
+#pragma unroll
+                    for (int k = 0; k < E; ++k) if (kv[k]) acc.note_zero(ov[k], (base + (i64)u * BLOCK) * E + k);
+                }
             }
         }
     }
@@ -447,7 +484,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
                     O o; bool keep;
                     if constexpr (C::n_in == 2) keep = C::apply(a[u].e[k], b[u].e[k], o);
                     else keep = C::apply(a[u].e[k], B(), o);
-                    if (keep) acc.add(o, it * E + k);
+                    if (keep) { acc.add(o, it * E + k); if constexpr (Acc<O, RED>::TRACK_ZERO) acc.note_zero(o, it * E + k); }
                 }
             }
         }
@@ -456,7 +493,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     for (i64 i = nitems * E + gtid; i < n; i += gsize) {   // the last n % E elements
         O o; bool keep;
         if constexpr (C::n_in == 2) keep = C::apply(in0[i], in1[i], o); else keep = C::apply(in0[i], B(), o);
-        if (keep) acc.add(o, i);
+        if (keep) { acc.add(o, i); if constexpr (Acc<O, RED>::TRACK_ZERO) acc.note_zero(o, i); }
     }
 
     acc = block_reduce<O, RED, BLOCK>(acc, s_part);
@@ -488,6 +525,7 @@ __device__ __forceinline__ void reduce_body(const typename C::in0_t* __restrict_
     }
     tot = block_reduce<O, RED, BLOCK>(tot, s_part);
     if (threadIdx.x == 0) {
+        tot.zero_sign();
         Partial p; tot.to_partial(p);
         res->fsum = p.fsum; res->count_f = (double)p.count;
         res->isum_lo = (i64)p.isum_lo; res->isum_hi = (sizeof(O) == 8) ? p.isum_hi : ((i64)p.isum_lo < 0 ? -1 : 0);

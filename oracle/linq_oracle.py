@@ -203,7 +203,9 @@ class Enumerable:
         if d.size == 0:
             raise InvalidOperationError("Sequence contains no elements")
         if d.dtype.kind == "f":
-            return d.dtype.type(np.nan) if np.isnan(d).any() else d.min()
+            if np.isnan(d).any():
+                return d.dtype.type(np.nan)
+            return _first_of_equals(d, d.min())
         return d.min()
 
     def Max(self):
@@ -211,8 +213,18 @@ class Enumerable:
         if d.size == 0:
             raise InvalidOperationError("Sequence contains no elements")
         if d.dtype.kind == "f":
-            return d.dtype.type(np.nan) if np.isnan(d).all() else np.nanmax(d)
+            if np.isnan(d).all():
+                return d.dtype.type(np.nan)
+            return _first_of_equals(d, np.nanmax(d))
         return d.max()
+
+
+def _first_of_equals(d, m):
+    """Enumerable.Min / Max replace their candidate only on a strict comparison (`x < value`, `value < x`), so of several
+    elements that compare equal to the result the earliest one is returned. Only -0 and +0 can tell: same value, other bits."""
+    if m == 0:
+        return d[np.flatnonzero(d == 0)[0]]
+    return m
 
 
 def scalar_enumerable_where_select(data, pred, sel):

@@ -446,3 +446,31 @@ def test_take_after_where_stops_early(acc):
     assert np.array_equal(AsComputeQueryable(x, acc).Where("x => x > 0.5f").Take(50_000).ToArray(), want[:50_000])   # host source: uploads stop
     assert AsComputeQueryable(buf, acc).Where("x => x > 2f").Take(10).ToArray().size == 0
     buf.Dispose()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_min_max_of_signed_zeros_return_the_earliest(acc, dtype):
+    """Enumerable.Min / Max keep their candidate unless the next element is strictly smaller / larger, so among -0 and +0
+    the earliest in the sequence is returned; the GPU reduction, which has no sequence order of its own, must remember it."""
+    cases = [[0.0, -0.0], [-0.0, 0.0], [3.0, 0.0, -0.0, 5.0], [3.0, -0.0, 0.0, 5.0], [-2.0, 0.0, -0.0], [-2.0, -0.0, 0.0]]
+    for c in cases:
+        x = np.array(c, dtype=dtype)
+        for name in ("Min", "Max"):
+            want = getattr(Enumerable(x), name)()
+            got = getattr(AsComputeQueryable(x, acc), name)()
+            assert got == want and np.signbit(got) == np.signbit(want), (c, name, got, want)
+    r = rng(77)
+    n = 3_000_001
+    x = np.abs(r.standard_normal(n)).astype(dtype) + dtype(1)        # all above zero, then zeros planted far apart
+    for first, second, a, b in ((-0.0, 0.0, 1_234_567, 2_999_999), (0.0, -0.0, 17, 2_000_000), (-0.0, 0.0, 2_900_000, 2_900_001)):
+        y = x.copy(); y[a] = first; y[b] = second
+        want = Enumerable(y).Min()
+        for src in (y, acc.Memory.AllocateAndCopyAsync(y)):
+            got = AsComputeQueryable(src, acc).Min()
+            assert got == 0 and np.signbit(got) == np.signbit(want) == np.signbit(dtype(first))
+        z = -y                                                        # all below zero: the zeros are the maximum
+        want = Enumerable(z).Max()
+        got = AsComputeQueryable(z, acc).Max()
+        assert got == 0 and np.signbit(got) == np.signbit(want)
+        got = AsComputeQueryable(y, acc).Where("v => v < 0.5").Min()  # only the zeros survive the filter
+        assert got == 0 and np.signbit(got) == np.signbit(dtype(first))
