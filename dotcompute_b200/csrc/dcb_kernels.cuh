@@ -1394,23 +1394,38 @@ __device__ __forceinline__ void cdesc_issue(const u32* __restrict__ cdesc, i64 l
 // Sum of the counts of tiles [lo, hi) by one whole warp; `d` holds the loads cdesc_issue made for (lo, hi). Counts that
 // were not there yet are asked for again, all together, with a bounded number of polls; a range longer than one window
 // is finished window by window. Returns the sum in every lane, or sets `failed`.
+// The offsets warp is one warp working through dependent instructions, and what it does per tile sets the length of every
+// round of its block (measured: 1900 cycles a round whatever the tile size, 1100 of them in here with the loads long
+// back). So the common case is kept short: a 16-byte group that lies inside the range is tested with four XORs against
+// the expected top bits and summed raw, the warp-wide results come from one redux each.
 template <int D4>
 __device__ __forceinline__ i64 cdesc_finish(const u32* __restrict__ cdesc, i64 lo, i64 hi, int lane, u32 epoch, u32 spin_limit,
                                             const unsigned int* abort_flag, volatile int* dead, u32 (&d)[D4][4], bool& failed) {
     i64 total = 0;
+    const u32 tag = (((epoch & 0xfffu) << 1) | 1u) << 19;      // the top 13 bits of a descriptor written by this launch
     for (;;) {
         const i64 base = lo & ~(i64)3;
         const int first = (int)(lo - base);
         const int span = (int)(hi - base < (i64)D4 * 128 ? hi - base : (i64)D4 * 128);
+        u32 warp_sum = 0;
         for (u32 polls = 0;;) {
-            bool stale = false;
+            u32 bad = 0, sum = 0;
 #pragma unroll
             for (int u = 0; u < D4; ++u) {
                 const int rel = (u * 32 + lane) * 4;
+                if (rel >= first && rel + 4 <= span) {        // the whole group matters: the usual case
+                    bad |= ((d[u][0] ^ tag) | (d[u][1] ^ tag) | (d[u][2] ^ tag) | (d[u][3] ^ tag)) >> 19;
+                    sum += d[u][0] + d[u][1] + d[u][2] + d[u][3] - 4u * tag;   // the counts, if all four carry the tag
+                } else if (rel < span && rel + 4 > first) {   // a group on the range's edge
 #pragma unroll
-                for (int e = 0; e < 4; ++e) stale = stale || (rel + e >= first && rel + e < span && !cdesc_written(d[u][e], epoch));
+                    for (int e = 0; e < 4; ++e) {
+                        if (rel + e >= first && rel + e < span) { bad |= (d[u][e] ^ tag) >> 19; sum += d[u][e] & 0x7ffffu; }
+                    }
+                }
             }
-            if (!__any_sync(0xffffffffu, stale)) break;
+            const u32 warp_bad = __reduce_or_sync(0xffffffffu, bad);   // the two reductions are independent: issued back to back
+            warp_sum = __reduce_add_sync(0xffffffffu, sum);           // at most D4 * 128 counts below 2^19 each
+            if (warp_bad == 0u) break;
             if (++polls > spin_limit || *dead || ((polls & 15u) == 0u && *(volatile unsigned int*)abort_flag == epoch)) { failed = true; break; }
             __nanosleep(polls > 4096 ? 4 * DCB_POLL_SLEEP_NS : DCB_POLL_SLEEP_NS);
 #pragma unroll
@@ -1423,16 +1438,7 @@ __device__ __forceinline__ i64 cdesc_finish(const u32* __restrict__ cdesc, i64 l
             }
         }
         if (failed) break;
-        int sum = 0;                                          // at most D4 * 128 counts below 2^19 each
-#pragma unroll
-        for (int u = 0; u < D4; ++u) {
-            const int rel = (u * 32 + lane) * 4;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) sum += (rel + e >= first && rel + e < span) ? (int)(d[u][e] & 0x7ffffu) : 0;
-        }
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
-        total += sum;
+        total += (i64)warp_sum;
         lo = base + (i64)D4 * 128;
         if (lo >= hi) break;
         cdesc_issue<D4>(cdesc, lo, hi, lane, d);              // the rare long range: the next window, waited for in place
@@ -1592,11 +1598,11 @@ __device__ __forceinline__ void compact_stream_body(const typename C::in0_t* __r
                 cnt = lane < WARPS ? s_cnt[st][lane] : 0;
                 incl = cnt;
 #pragma unroll
-                for (int dd = 1; dd < 32; dd <<= 1) {
+                for (int dd = 1; dd < WARPS; dd <<= 1) {      // only the first WARPS lanes hold anything
                     const int t = __shfl_up_sync(0xffffffffu, incl, dd);
                     if (lane >= dd) incl += t;
                 }
-                total = __shfl_sync(0xffffffffu, incl, 31);
+                total = __shfl_sync(0xffffffffu, incl, WARPS - 1);
                 if (lane == 0 && !(tile == 0 && *(volatile unsigned int*)(abort_flag + 1) == epoch))
                     cdesc_store(cdesc + tile, cdesc_make(epoch, (u32)total));
             }
