@@ -428,11 +428,25 @@ dcb_status prefix_sum_typed(const void* d_in, i64 n, int inclusive, void* d_out,
 }
 
 // ---------------------------------------------------------------------------------------------- the sort itself
+// Which bits differ among the keys: OR of key ^ first key. A pass whose digit is the same in every key would move nothing
+// and is skipped (keys below 1000 need two passes of four, `v % 7` one).
+template <typename K>
+__global__ void __launch_bounds__(kThreads) key_bits_differ(const K* __restrict__ keys, i64 n, u64* __restrict__ out) {
+    const K k0 = keys[0];
+    K acc = 0;
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) acc |= keys[i] ^ k0;
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) acc |= (K)__shfl_xor_sync(0xffffffffu, acc, m);
+    if ((threadIdx.x & 31) == 0 && acc != 0) atomicOr(out, (u64)acc);
+}
+
 struct SortScratch {
     void* keys[2] = {nullptr, nullptr};
     u32* idx[2] = {nullptr, nullptr};
     u32* hist = nullptr;
     u32* totals = nullptr;
+    u64* differ = nullptr;
     cudaStream_t s = nullptr;
     dcb_status alloc(i64 n, int key_bytes, cudaStream_t stream) {
         s = stream;
@@ -444,28 +458,46 @@ struct SortScratch {
         }
         RCU(cudaMallocAsync((void**)&hist, m * 4, s));
         RCU(cudaMallocAsync((void**)&totals, scan_totals_count((i64)m) * 4, s));
+        RCU(cudaMallocAsync((void**)&differ, 16, s));
         return DCB_OK;
     }
     void release() {
         for (int i = 0; i < 2; ++i) { if (keys[i]) cudaFreeAsync(keys[i], s); if (idx[i]) cudaFreeAsync(idx[i], s); keys[i] = nullptr; idx[i] = nullptr; }
         if (hist) cudaFreeAsync(hist, s);
         if (totals) cudaFreeAsync(totals, s);
-        hist = totals = nullptr;
+        if (differ) cudaFreeAsync(differ, s);
+        hist = totals = nullptr; differ = nullptr;
     }
 };
 
 // Sorts sc.keys[0] / sc.idx[0] (n pairs of sortable bits and payload); returns which of the two buffers holds the result.
-// `final_idx` (optional): where the last pass writes the payloads instead of the scratch buffer.
+// `final_idx` (optional): where the last pass writes the payloads instead of the scratch buffer. Passes whose digit is
+// the same in every key are skipped; finding that out costs one read of the keys and one synchronisation of the stream
+// (not done while the stream is being captured into a graph).
 template <typename K>
-dcb_status radix_sort(SortScratch& sc, i64 n, int* result_buf, u32* final_idx = nullptr) {
+dcb_status radix_sort(SortScratch& sc, i64 n, int* result_buf, u32* final_idx = nullptr, const u64* known_differ = nullptr) {
     const u32 tiles = (u32)((n + kTile - 1) / kTile);
     int cur = 0;
     if (scatter_smem_bytes<K>() + 11 * 1024 > 48 * 1024) {   // static + dynamic shared memory beyond the default 48 KB: opt in (cheap, per device)
         RCU(cudaFuncSetAttribute(radix_scatter<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)scatter_smem_bytes<K>()));
     }
     if (n > 0) {
-        for (int shift = 0; shift < (int)sizeof(K) * 8; shift += 8) {
-            const bool last = shift + 8 >= (int)sizeof(K) * 8;
+        u64 differ = ~0ull;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(sc.s, &cap) != cudaSuccess) { (void)cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+        if (known_differ) differ = *known_differ;
+        else if (cap == cudaStreamCaptureStatusNone && n > 1) {
+            RCU(cudaMemsetAsync(sc.differ, 0, 8, sc.s));
+            key_bits_differ<K><<<(int)std::min<i64>((n + kThreads - 1) / kThreads, 148 * 8), kThreads, 0, sc.s>>>((const K*)sc.keys[0], n, sc.differ);
+            RCU(cudaMemcpyAsync(&differ, sc.differ, 8, cudaMemcpyDeviceToHost, sc.s));
+            RCU(cudaStreamSynchronize(sc.s));
+        }
+        int shifts[8], passes = 0;
+        for (int shift = 0; shift < (int)sizeof(K) * 8; shift += 8)
+            if ((differ >> shift) & 0xffull) shifts[passes++] = shift;
+        for (int p = 0; p < passes; ++p) {
+            const int shift = shifts[p];
+            const bool last = p + 1 == passes;
             radix_tile_hist<K><<<(tiles + kHistTiles - 1) / kHistTiles, kThreads, 0, sc.s>>>((const K*)sc.keys[cur], n, shift, tiles, sc.hist);
             dcb_status st = exclusive_scan(sc.hist, sc.hist, (i64)256 * tiles, sc.totals, nullptr, sc.s);
             if (st) return st;
@@ -473,6 +505,7 @@ dcb_status radix_sort(SortScratch& sc, i64 n, int* result_buf, u32* final_idx = 
                                                                                  (K*)sc.keys[cur ^ 1], (last && final_idx) ? final_idx : sc.idx[cur ^ 1]);
             cur ^= 1;
         }
+        if (passes == 0 && final_idx) RCU(cudaMemcpyAsync(final_idx, sc.idx[0], (size_t)n * 4, cudaMemcpyDeviceToDevice, sc.s));   // all keys equal: source order
         RCU(cudaGetLastError());
     }
     *result_buf = cur;
@@ -518,6 +551,18 @@ dcb_status sort_keys(SortScratch& sc, int key_type, const void* d_keys, i64 n, i
     dcb_status st = prepare_any(key_type, d_keys, n, descending, sc.keys[0], sc.idx[0], payload, sc.s);
     if (st) return st;
     return key_bytes_of(key_type) == 8 ? radix_sort<u64>(sc, n, buf, final_idx) : radix_sort<u32>(sc, n, buf, final_idx);
+}
+// The bits that differ among the prepared keys in sc.keys[0] (synchronises the stream).
+dcb_status keys_differ(SortScratch& sc, int key_bytes, i64 n, u64* differ) {
+    *differ = 0;
+    if (n <= 1) return DCB_OK;
+    RCU(cudaMemsetAsync(sc.differ, 0, 8, sc.s));
+    const int grid = (int)std::min<i64>((n + kThreads - 1) / kThreads, 148 * 8);
+    if (key_bytes == 8) key_bits_differ<u64><<<grid, kThreads, 0, sc.s>>>((const u64*)sc.keys[0], n, sc.differ);
+    else key_bits_differ<u32><<<grid, kThreads, 0, sc.s>>>((const u32*)sc.keys[0], n, sc.differ);
+    RCU(cudaMemcpyAsync(differ, sc.differ, 8, cudaMemcpyDeviceToHost, sc.s));
+    RCU(cudaStreamSynchronize(sc.s));
+    return DCB_OK;
 }
 
 // ---------------------------------------------------------------------------------------------- gather
@@ -626,6 +671,112 @@ __global__ void __launch_bounds__(kThreads) group_emit(const u32* __restrict__ o
         out_counts[j] = (i64)counts[g];
         if (fp) out_f[j] = agg == AGG_AVERAGE ? facc[g] / (double)counts[g] : facc[g];
         else { out_i[j] = iacc[g]; out_f[j] = agg == AGG_AVERAGE ? (double)iacc[g] / (double)counts[g] : (double)iacc[g]; }
+    }
+}
+
+// Keys that differ in their low bits only (at most 16 of them) need no sort: the low bits index a table directly. Each
+// block adds into a table of its own in shared memory when that fits (Count / Sum / Average over at most 2048 slots) and
+// flushes it once; otherwise straight into the table in global memory. A group's first index is a minimum that, after
+// the group's first few elements, only has to be looked at.
+constexpr int kDenseSmemSlots = 2048;
+template <typename K, typename V, bool FP>
+__global__ void __launch_bounds__(kThreads) group_dense(const K* __restrict__ bits, const V* __restrict__ values, i64 n, int agg, u32 mask, int in_smem,
+                                                        u32* __restrict__ first, u32* __restrict__ counts, double* __restrict__ facc, i64* __restrict__ iacc) {
+    __shared__ u32 s_cnt[kDenseSmemSlots];
+    __shared__ u32 s_first[kDenseSmemSlots];
+    __shared__ u64 s_acc[kDenseSmemSlots];                    // double or 64-bit integer sums
+    const u32 slots = mask + 1u;
+    if (in_smem) {
+        for (u32 i = threadIdx.x; i < slots; i += kThreads) { s_cnt[i] = 0; s_first[i] = 0xffffffffu; s_acc[i] = 0; }
+        __syncthreads();
+    }
+    const i64 stride = (i64)gridDim.x * blockDim.x;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const u32 g = (u32)bits[i] & mask;
+        double fv = 0; i64 iv = 0;
+        if (agg != AGG_COUNT) { if (FP) fv = ValueOf<V>::f(values, (u32)i); else iv = ValueOf<V>::i(values, (u32)i); }
+        if (in_smem) {
+            atomicAdd(&s_cnt[g], 1u);
+            if ((u32)i < s_first[g]) atomicMin(&s_first[g], (u32)i);
+            if (agg != AGG_COUNT) { if (FP) atomicAdd(reinterpret_cast<double*>(&s_acc[g]), fv); else atomicAdd(&s_acc[g], (u64)iv); }
+        } else {
+            atomicAdd(&counts[g], 1u);
+            if ((u32)i < *(volatile u32*)&first[g]) atomicMin(&first[g], (u32)i);
+            if (agg == AGG_SUM || agg == AGG_AVERAGE) { if (FP) atomicAdd(&facc[g], fv); else atomicAdd((u64*)&iacc[g], (u64)iv); }
+            else if (agg == AGG_MIN) { if (FP) atomic_min_f64(&facc[g], fv); else atomicMin(&iacc[g], iv); }
+            else if (agg == AGG_MAX) { if (FP) atomic_max_f64(&facc[g], fv); else atomicMax(&iacc[g], iv); }
+        }
+    }
+    if (in_smem) {
+        __syncthreads();
+        for (u32 g = threadIdx.x; g < slots; g += kThreads) {
+            const u32 c = s_cnt[g];
+            if (c == 0) continue;
+            atomicAdd(&counts[g], c);
+            atomicMin(&first[g], s_first[g]);
+            if (agg != AGG_COUNT) { if (FP) atomicAdd(&facc[g], __longlong_as_double((i64)s_acc[g])); else atomicAdd((u64*)&iacc[g], s_acc[g]); }
+        }
+    }
+}
+__global__ void __launch_bounds__(kThreads) dense_init(u32 slots, int agg, u32* first, u32* counts, double* facc, i64* iacc) {
+    for (u32 g = blockIdx.x * blockDim.x + threadIdx.x; g < slots; g += gridDim.x * blockDim.x) {
+        first[g] = 0xffffffffu; counts[g] = 0;
+        if (agg == AGG_MIN) { facc[g] = __longlong_as_double(0x7ff8000000000000LL); iacc[g] = 0x7fffffffffffffffLL; }
+        else if (agg == AGG_MAX) { facc[g] = __longlong_as_double(0x7ff8000000000000LL); iacc[g] = -0x7fffffffffffffffLL - 1; }
+        else { facc[g] = 0.0; iacc[g] = 0; }
+    }
+}
+// One block: the table's used slots, packed to the front of the same arrays (slot order; the caller sorts by first index).
+__global__ void __launch_bounds__(1024) dense_pack(u32 slots, u32* first, u32* counts, double* facc, i64* iacc, u32* __restrict__ groups_out) {
+    __shared__ u32 s_warp[32];
+    __shared__ u32 s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (u32 base = 0; base < slots; base += 1024) {
+        const u32 g = base + threadIdx.x;
+        const u32 c = g < slots ? counts[g] : 0u;
+        const u32 fi = g < slots ? first[g] : 0u;
+        const double fa = g < slots ? facc[g] : 0.0;
+        const i64 ia = g < slots ? iacc[g] : 0;
+        const u32 used = c ? 1u : 0u;
+        u32 incl = used;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { const u32 t = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += t; }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();                                     // every slot of this chunk has been read
+        u32 off = 0, all = 0;
+        for (int w = 0; w < 32; ++w) { if (w < warp) off += s_warp[w]; all += s_warp[w]; }
+        const u32 pos = s_carry + off + incl - used;         // pos <= g: packing to the front never overtakes the reads
+        if (used) { first[pos] = fi; counts[pos] = c; facc[pos] = fa; iacc[pos] = ia; }
+        __syncthreads();
+        if (threadIdx.x == 0) s_carry += all;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *groups_out = s_carry;
+}
+template <typename K, typename V, bool FP>
+static void launch_group_dense(const void* bits, const void* values, i64 n, int agg, u32 mask, u32* first, u32* counts, double* facc, i64* iacc, cudaStream_t s) {
+    const int in_smem = (mask + 1u <= (u32)kDenseSmemSlots && (agg == AGG_COUNT || agg == AGG_SUM || agg == AGG_AVERAGE)) ? 1 : 0;
+    const int grid = (int)std::min<i64>((n + kThreads - 1) / kThreads, 148 * 4);
+    group_dense<K, V, FP><<<grid, kThreads, 0, s>>>((const K*)bits, (const V*)values, n, agg, mask, in_smem, first, counts, facc, iacc);
+}
+template <typename K>
+static bool launch_group_dense_typed(int value_type, const void* d_keys_for_count, const void* bits, const void* values, i64 n, int agg, u32 mask,
+                                     u32* first, u32* counts, double* facc, i64* iacc, cudaStream_t s) {
+    switch (value_type) {
+        case DCB_T_F32: launch_group_dense<K, float, true>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_F64: launch_group_dense<K, double, true>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_I8: launch_group_dense<K, signed char, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_U8: case DCB_T_BOOL: launch_group_dense<K, unsigned char, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_I16: launch_group_dense<K, short, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_U16: launch_group_dense<K, unsigned short, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_I32: launch_group_dense<K, int, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_U32: launch_group_dense<K, u32, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        case DCB_T_I64: case DCB_T_U64: launch_group_dense<K, i64, false>(bits, values, n, agg, mask, first, counts, facc, iacc, s); return true;
+        default:
+            if (agg == AGG_COUNT) { launch_group_dense<K, u32, false>(bits, d_keys_for_count, n, agg, mask, first, counts, facc, iacc, s); return true; }
+            return false;
     }
 }
 
@@ -789,8 +940,42 @@ extern "C" dcb_status dcb_group_aggregate(dcb_ctx* ctx, int32_t key_type, const 
     };
     if (st) { cleanup(); return st; }
     int buf = 0;
-    if ((st = sort_keys(sc, key_type, d_keys, n, 0, &buf))) { cleanup(); return st; }
-    cudaError_t e = cudaMallocAsync((void**)&heads, (size_t)n * 4, s);
+    if ((st = prepare_any(key_type, d_keys, n, 0, sc.keys[0], sc.idx[0], nullptr, s))) { cleanup(); return st; }
+    u64 differ = 0;
+    if ((st = keys_differ(sc, kb, n, &differ))) { cleanup(); return st; }
+    cudaError_t e = cudaSuccess;
+    if (differ < 65536ull) {
+        // Dense keys: no sort. The table is indexed by the keys' low bits, packed, and emitted in order of first occurrence.
+        u32 slots = 1; while ((u64)slots <= differ) slots <<= 1;
+        const u32 mask = slots - 1u;
+        e = cudaMallocAsync((void**)&first_idx, (size_t)slots * 4, s);
+        if (e == cudaSuccess) e = cudaMallocAsync((void**)&counts, (size_t)slots * 4, s);
+        if (e == cudaSuccess) e = cudaMallocAsync((void**)&facc, (size_t)slots * 8, s);
+        if (e == cudaSuccess) e = cudaMallocAsync((void**)&iacc, (size_t)slots * 8, s);
+        if (e == cudaSuccess) e = cudaMallocAsync((void**)&d_total, 16, s);
+        if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_OUT_OF_MEMORY; }
+        dense_init<<<launch_grid(slots), kThreads, 0, s>>>(slots, aggregate, first_idx, counts, facc, iacc);
+        const bool ok = kb == 8 ? launch_group_dense_typed<u64>(value_type, d_keys, sc.keys[0], d_values, n, aggregate, mask, first_idx, counts, facc, iacc, s)
+                                : launch_group_dense_typed<u32>(value_type, d_keys, sc.keys[0], d_values, n, aggregate, mask, first_idx, counts, facc, iacc, s);
+        if (!ok) { cleanup(); return bad("unsupported value type"); }
+        dense_pack<<<1, 1024, 0, s>>>(slots, first_idx, counts, facc, iacc, d_total);
+        u32 groups = 0;
+        e = cudaMemcpyAsync(&groups, d_total, 4, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) { cleanup(); (void)cudaGetLastError(); return DCB_ERR_CUDA; }
+        *out_groups = groups;
+        if ((int64_t)groups > out_cap) { cleanup(); dcb_set_thread_error("more groups than the outputs hold"); return DCB_ERR_OUTPUT_TOO_SMALL; }
+        if ((st = sg.alloc(groups, 4, s))) { cleanup(); return st; }
+        int gb = 0;
+        if ((st = sort_keys(sg, DCB_T_U32, first_idx, groups, 0, &gb))) { cleanup(); return st; }
+        group_emit<<<launch_grid(groups), kThreads, 0, s>>>(sg.idx[gb], first_idx, counts, facc, iacc, groups, aggregate, fp, d_out_first, (i64*)d_out_counts, d_out_f64, (i64*)d_out_i64);
+        e = cudaGetLastError();
+        cleanup();
+        return e == cudaSuccess ? DCB_OK : DCB_ERR_CUDA;
+    }
+    st = kb == 8 ? radix_sort<u64>(sc, n, &buf, nullptr, &differ) : radix_sort<u32>(sc, n, &buf, nullptr, &differ);
+    if (st) { cleanup(); return st; }
+    e = cudaMallocAsync((void**)&heads, (size_t)n * 4, s);
     if (e == cudaSuccess) e = cudaMallocAsync((void**)&excl, (size_t)n * 4, s);
     if (e == cudaSuccess) e = cudaMallocAsync((void**)&totals, scan_totals_count(n) * 4, s);
     if (e == cudaSuccess) e = cudaMallocAsync((void**)&d_total, 16, s);

@@ -383,7 +383,9 @@ dcb_status dcb_peer_disconnect(dcb_ctx* ctx);
  *
  *   dcb_sort_indices     stable argsort of n keys of type key_type (DCB_T_*; floating keys order as .NET's comparer does: NaN
  *                        first, -0 equal to +0); descending != 0 sorts descending, ties still in source order. A least-
- *                        significant-digit radix sort, 8 bits a pass, over any number of blocks.
+ *                        significant-digit radix sort, 8 bits a pass, over any number of blocks. Passes whose digit is the
+ *                        same in every key are skipped (keys below 1000: two passes of four); to know them the call reads
+ *                        the keys once and synchronises the stream once (not while the stream is being captured).
  *   dcb_sort_by_key      the same sort with the elements travelling beside their keys instead of their positions:
  *                        d_sorted_values = d_values in stable key order, with no gather afterwards (a gather reads one
  *                        32-byte sector per element from all over the source: a quarter of OrderBy's time). value_bytes must

@@ -53,11 +53,14 @@ def test_orderby_key_selector_is_stable_and_composes(acc):
 
 
 @pytest.mark.parametrize("n,groups", [(1, 1), (1000, 7), (4097, 4097), (500_000, 1000), (2_000_003, 13)])
-def test_groupby_aggregates(acc, n, groups):
+@pytest.mark.parametrize("spread", [1, 100_003])
+def test_groupby_aggregates(acc, n, groups, spread):
+    """spread = 1: keys 0..groups-1 differ in their low bits only and index a table directly; spread = 100003 scatters them
+    over the whole int range, which takes the sort-based path. Same groups, same order of first occurrence either way."""
     r = rng(n + groups)
     x = r.integers(0, 1_000_000, n, dtype=np.int32)
-    key_py = lambda v: v % groups                                    # noqa: E731
-    key_cs = f"v => v % {groups}"
+    key_py = lambda v: (v % groups) * np.int32(spread)               # noqa: E731
+    key_cs = f"v => (v % {groups}) * {spread}"
     g = AsComputeQueryable(x, acc).GroupBy(key_cs)
     e = Enumerable(x)
     wk, wc = e.GroupAggregate(key_py, "Count")
@@ -159,3 +162,20 @@ def test_scan_running_sum(acc, n, dtype):
             assert np.array_equal(got, want)
         else:
             assert np.allclose(got, want, rtol=1e-5, atol=1e-3)
+
+
+def test_sort_skips_passes_but_not_order(acc):
+    """Keys that share whole digits (all equal; equal but for one byte in the middle; 64-bit keys that differ in the top
+    byte only): the passes that would move nothing are skipped, the result is the same stable order."""
+    n = 300_001
+    r = rng(12)
+    x = r.integers(0, 1_000_000, n, dtype=np.int32)
+    assert np.array_equal(AsComputeQueryable(x, acc).OrderBy("v => 0").ToArray(), x)                       # no pass at all
+    assert np.array_equal(AsComputeQueryable(x, acc).OrderByDescending("v => 5").ToArray(), x)
+    mid = ((x & 0xFF) << 8) | 0x40000001                                                                  # only bits 8..15 differ
+    assert np.array_equal(AsComputeQueryable(x, acc).OrderBy("v => ((v & 0xFF) << 8) | 0x40000001").ToArray(), x[np.argsort(mid, kind="stable")])
+    k64 = (r.integers(0, 7, n, dtype=np.int64) << 56) + 12345
+    got = AsComputeQueryable(k64, acc).OrderBy().ToArray()
+    assert np.array_equal(got, np.sort(k64, kind="stable"))
+    f = np.full(n, 2.5, dtype=F); f[::1000] = np.nan
+    assert np.array_equal(AsComputeQueryable(f, acc).OrderBy().ToArray().view(np.uint32), Enumerable(f).OrderBy().ToArray().view(np.uint32))
