@@ -124,6 +124,7 @@ struct dcb_pipeline {
     int jit_rows = 0;                    // rows forced by a tuning experiment (0 = automatic)
     int compact_block = 256;             // threads per block of the compaction kernels
     const void* k_stream = nullptr;      // streamed compaction kernel (null: the query has none)
+    unsigned int* fault_word = nullptr;  // device word the lambdas' checked integer divisions set (null: the query has none)
     int stream_rows = 0, stream_warps = 0, stream_nbuf = 0, stream_copy_warps = 0, occ_stream = 1;
     std::mutex mu;                       // guards `scratch` and every enqueue that uses it
     std::map<cudaStream_t, Scratch> scratch;
@@ -297,6 +298,11 @@ dcb_status load_jit(dcb_ctx* ctx, dcb_pipeline* p) {
     CU(ctx, cudaLibraryGetKernel(&ks, p->lib, (std::string(stem) + "scalar").c_str()));
     p->k_vec = (const void*)kv;
     p->k_scalar = (const void*)ks;
+    if (p->info.checked_div) {
+        void* w = nullptr; size_t bytes = 0;
+        CU(ctx, cudaLibraryGetGlobal(&w, &bytes, p->lib, "dcb_fault_word"));
+        p->fault_word = (unsigned int*)w;
+    }
     if (p->stream_rows > 0) {
         cudaKernel_t kst = nullptr;
         CU(ctx, cudaLibraryGetKernel(&kst, p->lib, "dcb_compact_stream"));
@@ -404,6 +410,7 @@ extern "C" const char* dcb_status_name(dcb_status s) {
         case DCB_ERR_CUDA: return "DCB_ERR_CUDA";
         case DCB_ERR_EMPTY_SEQUENCE: return "DCB_ERR_EMPTY_SEQUENCE";
         case DCB_ERR_OVERFLOW: return "DCB_ERR_OVERFLOW";
+        case DCB_ERR_DIVIDE_BY_ZERO: return "DCB_ERR_DIVIDE_BY_ZERO";
         default: return "DCB_ERR_UNKNOWN";
     }
 }
@@ -909,8 +916,36 @@ dcb_status launch(dcb_ctx* ctx, const void* fn, unsigned grid, void** args, cuda
     return DCB_OK;
 }
 
+__global__ void fold_fault_kernel(unsigned int* word, dcb::DeviceResult* rec) {
+    // behind the query's kernel on the same stream: what the lambdas' integer divisions noted goes into the record's flags
+    const unsigned int f = *word;
+    if (f) {
+        rec->flags = rec->flags | ((f & 1u) ? (unsigned long long)dcb::FLAG_DIV0 : 0ull) | ((f & 2u) ? (unsigned long long)dcb::FLAG_DIV_OVERFLOW : 0ull);
+        *word = 0;
+    }
+}
+
+dcb_status run_async_launch(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
+                            void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, uint32_t run_flags);
+
 dcb_status run_async_impl(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
                           void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, uint32_t run_flags = 0) {
+    dcb_status st = run_async_launch(p, in0, in1, n, out, out_cap, d_result, d_prev, s, launches, run_flags);
+    if (st != DCB_OK || !p->fault_word || n == 0) return st;
+    // A map writes no record of its own: its faults are read from the word itself by the blocking calls, and reach a
+    // caller's record only if one was given.
+    const bool plain_map = p->info.terminal == DCB_OP_TOARRAY && !p->info.has_filter;
+    if (plain_map && !d_result) return st;
+    dcb::DeviceResult* res = d_result ? (dcb::DeviceResult*)d_result : p->d_result;
+    fold_fault_kernel<<<1, 1, 0, s>>>(p->fault_word, res);
+    CU(p->ctx, cudaGetLastError());
+    if (launches) *launches += 1;
+    p->ctx->launches += 1;
+    return DCB_OK;
+}
+
+dcb_status run_async_launch(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out, int64_t out_cap,
+                            void* d_result, const void* d_prev, cudaStream_t s, uint32_t* launches, uint32_t run_flags) {
     dcb_ctx* ctx = p->ctx;
     const dcbt::ChainInfo& I = p->info;
     NEED(ctx, n >= 0, "element count is negative");
@@ -1052,6 +1087,8 @@ extern "C" dcb_status dcb_record_finalize(int32_t terminal, int32_t out_type, co
         return set_err(ctx, DCB_ERR_TIMEOUT, terminal == DCB_OP_TOARRAY ? "a look-back wait in the compaction kernel ran out"
                                                                         : "a peer's partial did not arrive in time");
     }
+    if (fl & dcb::FLAG_DIV0) { r->flags |= DCB_RES_DIVIDE_BY_ZERO; return set_err(ctx, DCB_ERR_DIVIDE_BY_ZERO, "attempted to divide by zero in a lambda"); }
+    if (fl & dcb::FLAG_DIV_OVERFLOW) { r->flags |= DCB_RES_DIVIDE_OVERFLOW; return set_err(ctx, DCB_ERR_OVERFLOW, "MinValue / -1 in a lambda"); }
     switch (terminal) {
         case DCB_OP_TOARRAY:
             if (fl & dcb::FLAG_TRUNCATED) { r->flags |= DCB_RES_TRUNCATED; return set_err(ctx, DCB_ERR_OUTPUT_TOO_SMALL, "%lld elements survive, the output holds fewer", (long long)d->count); }
@@ -1130,6 +1167,20 @@ static dcb_status finish_take(dcb_status st, int64_t cap, dcb_result* result) {
     return st;
 }
 
+namespace {
+// A map's integer-division faults, read from the module's word after the stream has been synchronised.
+dcb_status map_faults(dcb_pipeline* p, cudaStream_t s) {
+    dcb_ctx* ctx = p->ctx;
+    unsigned int f = 0;
+    CU(ctx, cudaMemcpyAsync(&f, p->fault_word, 4, cudaMemcpyDeviceToHost, s));
+    CU(ctx, cudaStreamSynchronize(s));
+    if (!f) return DCB_OK;
+    CU(ctx, cudaMemsetAsync(p->fault_word, 0, 4, s));
+    if (f & 1u) return set_err(ctx, DCB_ERR_DIVIDE_BY_ZERO, "attempted to divide by zero in a lambda");
+    return set_err(ctx, DCB_ERR_OVERFLOW, "MinValue / -1 in a lambda");
+}
+}  // namespace
+
 extern "C" dcb_status dcb_pipeline_run_ex(dcb_pipeline* p, const void* in0, const void* in1, int64_t n, void* out,
                                           int64_t out_cap, uint32_t flags, dcb_result* result, void* stream) {
     if (!p) return set_err(nullptr, DCB_ERR_INVALID_ARGUMENT, "pipeline is null");
@@ -1156,7 +1207,10 @@ extern "C" dcb_status dcb_pipeline_run_ex(dcb_pipeline* p, const void* in0, cons
     float ms = 0;
     CU(ctx, cudaEventElapsedTime(&ms, p->ev0, p->ev1));
     result->launches = launches; result->kernel_ms = ms; result->total_ms = ms;
-    if (plain_map) { result->count = n; return DCB_OK; }
+    if (plain_map) {
+        result->count = n;
+        return p->fault_word ? map_faults(p, s) : DCB_OK;
+    }
     st = dcb_result_finalize(p, p->h_record, result);
     return take ? finish_take(st, out_cap, result) : st;
 }
@@ -1371,7 +1425,7 @@ extern "C" dcb_status dcb_pipeline_run_host_ex(dcb_pipeline* p, const void* host
     if (compaction) {
         if (last_chunk == n_chunks - 1) ce = drain_compacted(n_chunks - 1);
         total.count = survivors; total.count_f = (double)survivors; total.local_count = survivors;
-        total.flags = flags_seen & (uint64_t)dcb::FLAG_TIMEOUT;
+        total.flags = flags_seen & (uint64_t)(dcb::FLAG_TIMEOUT | dcb::FLAG_DIV0 | dcb::FLAG_DIV_OVERFLOW);
         if (survivors > host_out_cap) total.flags |= dcb::FLAG_TRUNCATED;
     } else if (!plain_map) {
         ce = cudaMemcpyAsync(h_recs, d_recs, sizeof(dcb::DeviceResult) * (size_t)n_chunks, cudaMemcpyDeviceToHost, ks);
@@ -1388,7 +1442,7 @@ extern "C" dcb_status dcb_pipeline_run_host_ex(dcb_pipeline* p, const void* host
     float ms = 0;
     cudaEventElapsedTime(&ms, t0, t1);
     result->launches = launches; result->total_ms = ms; result->kernel_ms = 0;
-    if (plain_map) { result->count = n; return DCB_OK; }
+    if (plain_map) { result->count = n; return p->fault_word ? map_faults(p, ks) : DCB_OK; }
     st = dcb_result_finalize(p, &total, result);
     return take ? finish_take(st, host_out_cap, result) : st;
 }

@@ -51,7 +51,8 @@ enum : int { RED_SUM = 1, RED_MIN = 2, RED_MAX = 4, RED_COUNT = 8, RED_FIRST = 1
 
 // Flag bits in the record (low bits match DCB_RES_* of the C ABI).
 enum : u32 { FLAG_SAW_NAN = 1u, FLAG_TRUNCATED = 2u, FLAG_TIMEOUT = 4u, FLAG_OVERFLOW = 8u, FLAG_SAW_NUMBER = 16u,
-             FLAG_PREFIX = 32u };   // PREFIX: slots 12..15 hold the smallest and the largest running sum (checked integer Sum)
+             FLAG_PREFIX = 32u,     // PREFIX: slots 12..15 hold the smallest and the largest running sum (checked integer Sum)
+             FLAG_DIV0 = 64u, FLAG_DIV_OVERFLOW = 128u };   // an integer / or % of a lambda: zero divisor, MinValue / -1
 
 // The record a run leaves in device memory: 16 eight-byte slots (see DCB_SLOT_* in dcb200.h).
 struct __align__(16) DeviceResult {

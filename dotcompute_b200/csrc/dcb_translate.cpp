@@ -331,6 +331,11 @@ class Parser {
             // C# integer arithmetic wraps (unchecked context); do it in the unsigned type so C++ agrees.
             std::string ut = cuda_name(unsigned_of(t));
             r->code = std::string("((") + cuda_name(t) + ")((" + ut + ")(" + ca + ") " + op + " (" + ut + ")(" + cb + ")))";
+        } else if ((op == "/" || op == "%") && is_integral(t) && !kernel_mode && !(b.const_int && b.cval != 0)) {
+            // C# throws DivideByZeroException on a zero divisor and OverflowException on MinValue / -1: the helpers note
+            // either in the module's fault word (the host turns it into the error) and return 0.
+            // (`keep`: an element an earlier Where has dropped is never divided in C#, so it cannot fault here either)
+            r->code = std::string(op == "/" ? "dcb_idiv<" : "dcb_irem<") + cuda_name(t) + ">(" + ca + ", " + cb + ", keep)";
         } else {
             r->code = "(" + ca + " " + op + " " + cb + ")";
         }
@@ -975,10 +980,13 @@ bool build_chain(int t0, int t1, const std::vector<OpSpec>& ops, ChainInfo* info
     s += std::string("    static constexpr int n_in = ") + (info->n_in == 2 ? "2" : "1") + ";\n";
     s += std::string("    static constexpr bool has_filter = ") + (info->has_filter ? "true" : "false") + ";\n";
     s += "    static __device__ __forceinline__ bool apply(const in0_t& p0, const in1_t& p1, out_t& out) {\n";
+    const bool divides = body.find("dcb_idiv<") != std::string::npos || body.find("dcb_irem<") != std::string::npos;
     if (info->has_filter) s += "        bool keep = true;\n";
+    else if (divides) s += "        const bool keep = true;\n";       // the checked divisions ask whether the element is still live
     s += body;
     s += "        out = " + cur_var + std::string(";\n        return ") + (info->has_filter ? "keep" : "true") + ";\n    }\n};\n";
     info->chain_src = s;
+    info->checked_div = s.find("dcb_idiv<") != std::string::npos || s.find("dcb_irem<") != std::string::npos;
     info->key = key;
     *status = 0;
     return true;
@@ -1025,7 +1033,16 @@ std::string build_program(const ChainInfo& info, const std::string& suffix, cons
              "    return signbit(a) ? a : b;\n}\n"
              "template <typename T> __device__ __forceinline__ T dcb_net_max(T a, T b) {\n"
              "    if (a != b) return (a == a) ? (b < a ? a : b) : a;\n"
-             "    return signbit(b) ? a : b;\n}\n#endif\n\n";
+             "    return signbit(b) ? a : b;\n}\n"
+             "// Integer division as C# defines it: a zero divisor and MinValue / -1 are errors. Bit 0 / bit 1 of the fault word.\n"
+             "__device__ unsigned int dcb_fault_word = 0;\n"
+             "template <typename T> __device__ __forceinline__ bool dcb_div_fault(T a, T b, bool live) {\n"
+             "    if (b == T(0)) { if (live) atomicOr(&dcb_fault_word, 1u); return true; }\n"
+             "    if (T(-1) < T(0) && b == T(-1) && a == T(1ull << (sizeof(T) * 8 - 1))) { if (live) atomicOr(&dcb_fault_word, 2u); return true; }\n"
+             "    return false;\n}\n"
+             "template <typename T> __device__ __forceinline__ T dcb_idiv(T a, T b, bool live) { return dcb_div_fault(a, b, live) ? T(0) : T(a / b); }\n"
+             "template <typename T> __device__ __forceinline__ T dcb_irem(T a, T b, bool live) { return dcb_div_fault(a, b, live) ? T(0) : T(a % b); }\n"
+             "#endif\n\n";
     }
     s += replace_all(info.chain_src, "@", suffix);
     const std::string C = "dcb_chain" + suffix;

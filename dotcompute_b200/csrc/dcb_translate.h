@@ -50,6 +50,7 @@ struct ChainInfo {
     int terminal = 0;                 // DCB_OP_*
     int result_type = T_NONE;         // scalar type a reduction returns
     int red_mask = 0;                 // RED_* bits the kernel needs
+    bool checked_div = false;         // a lambda divides integers by something that may be zero: the module has a fault word
     bool checked_sum = false;         // Sum over int / long: the kernel tracks the range of the running sum (checked arithmetic)
     bool has_filter = false;
     bool is_identity = false;         // no Select/Where/Zip at all

@@ -50,6 +50,10 @@ class OverflowException(DotComputeException, ArithmeticError):
     pass
 
 
+class DivideByZeroException(DotComputeException, ZeroDivisionError):
+    """An integer / or % inside a lambda met a zero divisor (System.DivideByZeroException)."""
+
+
 class ObjectDisposedException(InvalidOperationException):
     pass
 
@@ -83,6 +87,7 @@ _BY_STATUS = {
     304: ObjectDisposedException,
     501: InvalidOperationException,
     502: OverflowException,
+    503: DivideByZeroException,
 }
 
 

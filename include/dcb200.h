@@ -58,7 +58,8 @@ enum {
     DCB_ERR_NO_DEVICE = 401,        /* fatal: no usable CUDA device / driver */
     DCB_ERR_CUDA = 402,             /* fatal: a CUDA call failed; text in dcb_last_error */
     DCB_ERR_EMPTY_SEQUENCE = 501,   /* Min/Max/Average of zero elements (InvalidOperationException in System.Linq) */
-    DCB_ERR_OVERFLOW = 502          /* checked integer Sum left its type's range (OverflowException) */
+    DCB_ERR_OVERFLOW = 502,         /* checked integer Sum left its type's range, or int.MinValue / -1 in a lambda (OverflowException) */
+    DCB_ERR_DIVIDE_BY_ZERO = 503    /* an integer / or % in a lambda met a zero divisor (DivideByZeroException) */
 };
 
 enum { DCB_CLASS_NONE = 0, DCB_CLASS_TRANSIENT = 1, DCB_CLASS_RESOURCE = 2,
@@ -154,7 +155,9 @@ enum {
     DCB_RES_TRUNCATED = 2u,
     DCB_RES_TIMEOUT = 4u,
     DCB_RES_OVERFLOW = 8u,
-    DCB_RES_PREFIX_RANGE = 32u      /* record only: slots DCB_SLOT_PREFIX_MIN_LO.. hold the range of the running sum */
+    DCB_RES_PREFIX_RANGE = 32u,     /* record only: slots DCB_SLOT_PREFIX_MIN_LO.. hold the range of the running sum */
+    DCB_RES_DIVIDE_BY_ZERO = 64u,   /* an integer division or remainder in a lambda had a zero divisor */
+    DCB_RES_DIVIDE_OVERFLOW = 128u  /* ... or was MinValue / -1 */
 };
 
 /* Raw per-run record the kernels write in device memory: 16 eight-byte slots. A sharded

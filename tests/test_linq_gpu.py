@@ -474,3 +474,48 @@ def test_min_max_of_signed_zeros_return_the_earliest(acc, dtype):
         assert got == 0 and np.signbit(got) == np.signbit(want)
         got = AsComputeQueryable(y, acc).Where("v => v < 0.5").Min()  # only the zeros survive the filter
         assert got == 0 and np.signbit(got) == np.signbit(dtype(first))
+
+
+def test_integer_division_faults_are_exceptions(acc):
+    """C#: x / 0 and x % 0 on integers throw DivideByZeroException, int.MinValue / -1 throws OverflowException; the reference
+    runs these lambdas through System.Linq, where that is what happens. Here the lambdas note the fault on the device and
+    the call that runs them fails - for maps, filters and reductions, from host arrays and device buffers - and the same
+    compiled query works again afterwards on clean data."""
+    from dotcompute_b200 import DivideByZeroException, OverflowException
+    n = 200_001
+    x = rng(5).integers(1, 50, n, dtype=np.int32)
+    clean = AsComputeQueryable(x, acc).Select("v => 1000 / v").ToArray()
+    assert np.array_equal(clean, (1000 // x).astype(np.int32))
+    bad = x.copy(); bad[123_456] = 0
+    for src in (bad, acc.Memory.AllocateAndCopyAsync(bad)):
+        with pytest.raises(DivideByZeroException):
+            AsComputeQueryable(src, acc).Select("v => 1000 / v").ToArray()
+        with pytest.raises(DivideByZeroException):
+            AsComputeQueryable(src, acc).Select("v => 1000 % v").Sum()
+        with pytest.raises(DivideByZeroException):
+            AsComputeQueryable(src, acc).Where("v => 1000 / v > 30").ToArray()
+        with pytest.raises(DivideByZeroException):
+            AsComputeQueryable(src, acc).Where("v => 1000 / v > 30").Count()
+        # a filter in front that removes the zero: nothing is divided by it, nothing is thrown (Where runs before Select)
+        got = AsComputeQueryable(src, acc).Where("v => v != 0").Select("v => 1000 / v").Sum("v => (long)v")
+        assert got == int((1000 // bad[bad != 0]).sum())
+    assert np.array_equal(AsComputeQueryable(x, acc).Select("v => 1000 / v").ToArray(), clean)            # same cached query, clean again
+    assert AsComputeQueryable(x, acc).Where("v => 1000 / v > 30").Count() == int((1000 // x > 30).sum())
+    # Zip: the divisor is the second sequence
+    a = rng(6).integers(-1000, 1000, n, dtype=np.int32)
+    b = rng(7).integers(1, 9, n, dtype=np.int32)
+    assert np.array_equal(AsComputeQueryable(a, acc).Zip(b, "(p, q) => p / q + p % q").ToArray(),
+                          (np.trunc(a / b).astype(np.int32) + np.fmod(a, b).astype(np.int32)))
+    b0 = b.copy(); b0[-1] = 0
+    with pytest.raises(DivideByZeroException):
+        AsComputeQueryable(a, acc).Zip(b0, "(p, q) => p / q").ToArray()
+    # int.MinValue / -1
+    m = np.array([5, -2147483648, 7], dtype=np.int32)
+    d = np.array([1, -1, 1], dtype=np.int32)
+    with pytest.raises(OverflowException):
+        AsComputeQueryable(m, acc).Zip(d, "(p, q) => p / q").ToArray()
+    assert np.array_equal(AsComputeQueryable(m, acc).Zip(np.array([1, 1, 1], dtype=np.int32), "(p, q) => p / q").ToArray(), m)
+    # long
+    k = np.array([10, 0, 3], dtype=np.int64)
+    with pytest.raises(DivideByZeroException):
+        AsComputeQueryable(k, acc).Select("v => 100L / v").Max()

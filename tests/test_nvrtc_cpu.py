@@ -108,3 +108,19 @@ def test_integer_sum_uses_the_ordered_kernel():
     assert "sum_checked_body" in generate_source(np.int64, [(N.OP_SELECT, "x => x + 1L"), (N.OP_SUM, None)])
     assert "sum_checked_body" not in generate_source(np.float32, [(N.OP_SUM, None)])
     assert "sum_checked_body" not in generate_source(np.int32, [(N.OP_AVERAGE, None)])
+
+
+def test_integer_division_is_checked_only_where_the_divisor_can_be_zero():
+    """C# throws on x / 0 and on int.MinValue / -1: a division whose divisor is not a non-zero constant goes through the
+    helper that records either; constant divisors and floating division stay plain; such a program still compiles."""
+    assert "dcb_idiv<int>" in generate_source(np.int32, [(N.OP_SELECT, "x => 100 / x"), (N.OP_TOARRAY, None)])
+    assert "dcb_irem<long long>" in generate_source(np.int64, [(N.OP_WHERE, "k => k % (k >> 3) == 0L"), (N.OP_COUNT, None)])
+    assert "dcb_idiv<" not in generate_source(np.int32, [(N.OP_SELECT, "x => x / 7 + x % 3"), (N.OP_TOARRAY, None)])
+    assert "dcb_idiv<" not in generate_source(np.float32, [(N.OP_SELECT, "x => 1f / x"), (N.OP_TOARRAY, None)])
+    with open(HEADER) as f:
+        header = f.read()
+    for ops, second in (([(N.OP_ZIP, "(a, b) => a / b + a % b"), (N.OP_WHERE, "v => v != 0"), (N.OP_SUM, None)], np.int32),
+                        ([(N.OP_SELECT, "x => 100 / x"), (N.OP_TOARRAY, None)], None)):          # with and without a filter
+        src = generate_source(np.int32, ops, second)
+        res, log = compile_for_sm100a(src.replace('#include "dcb_kernels.cuh"', header))
+        assert res == nvrtc.nvrtcResult.NVRTC_SUCCESS, log[:2000]
