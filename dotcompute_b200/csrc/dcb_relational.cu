@@ -781,26 +781,45 @@ static bool launch_group_dense_typed(int value_type, const void* d_keys_for_coun
 }
 
 // ---------------------------------------------------------------------------------------------- join
-template <typename K>
-__device__ __forceinline__ u32 lower_bound(const K* __restrict__ a, u32 n, K key) {
-    u32 lo = 0, hi = n;
-    while (lo < hi) { const u32 mid = lo + ((hi - lo) >> 1); if (a[mid] < key) lo = mid + 1; else hi = mid; }
-    return lo;
-}
-template <typename K>
-__device__ __forceinline__ u32 upper_bound(const K* __restrict__ a, u32 n, K key) {
-    u32 lo = 0, hi = n;
-    while (lo < hi) { const u32 mid = lo + ((hi - lo) >> 1); if (a[mid] <= key) lo = mid + 1; else hi = mid; }
-    return lo;
-}
 enum { JOIN_INNER = 0, JOIN_SEMI = 2, JOIN_ANTI = 3 };
+// Every outer element looks its key up in the sorted inner keys. The first ten steps of each search run over 1024 pivots
+// kept in shared memory (every 1/1024th of the array), the rest in the slice between two pivots; the end of the run of
+// equal keys is found by doubling steps from its start, not by a second search over the whole array.
+constexpr int kJoinPivots = 1024;
 template <typename K>
 __global__ void __launch_bounds__(kThreads) join_count(const K* __restrict__ outer_bits, i64 n_outer, const K* __restrict__ inner_sorted, u32 n_inner,
                                                        int kind, u32* __restrict__ lo_out, u32* __restrict__ cnt_out) {
+    __shared__ K s_piv[kJoinPivots];
+    const bool use_piv = n_inner >= 4u * kJoinPivots;
+    if (use_piv) {
+        for (int j = threadIdx.x; j < kJoinPivots; j += kThreads) s_piv[j] = inner_sorted[(u32)(((u64)j * n_inner) >> 10)];
+        __syncthreads();
+    }
     const i64 stride = (i64)gridDim.x * blockDim.x;
     for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n_outer; i += stride) {
         const K key = outer_bits[i];
-        const u32 lo = lower_bound(inner_sorted, n_inner, key), hi = upper_bound(inner_sorted, n_inner, key);
+        u32 a = 0, b = n_inner;                               // the first element >= key lies in [a, b]
+        if (use_piv) {
+            u32 c = 0, h = kJoinPivots;                       // c = number of pivots below the key
+            while (c < h) { const u32 mid = (c + h) >> 1; if (s_piv[mid] < key) c = mid + 1; else h = mid; }
+            a = c == 0 ? 0u : (u32)(((u64)(c - 1) * n_inner) >> 10) + 1u;
+            b = c == (u32)kJoinPivots ? n_inner : (u32)(((u64)c * n_inner) >> 10);
+        }
+        while (a < b) { const u32 mid = a + ((b - a) >> 1); if (inner_sorted[mid] < key) a = mid + 1; else b = mid; }
+        const u32 lo = a;
+        // end of the run of keys equal to `key`: doubling steps, then a search inside the last step
+        u32 hi = lo;
+        if (lo < n_inner && inner_sorted[lo] == key) {
+            u32 step = 1, last = lo;                          // inner_sorted[last] == key
+            for (;;) {
+                const u32 probe = last + step;
+                if (probe >= n_inner || inner_sorted[probe] != key) { hi = probe < n_inner ? probe : n_inner; break; }
+                last = probe; step <<= 1;
+            }
+            u32 x = last + 1, y = hi;                         // first index in (last, hi] whose key differs
+            while (x < y) { const u32 mid = x + ((y - x) >> 1); if (inner_sorted[mid] == key) x = mid + 1; else y = mid; }
+            hi = x;
+        }
         lo_out[i] = lo;
         const u32 m = hi - lo;
         cnt_out[i] = kind == JOIN_INNER ? m : (kind == JOIN_SEMI ? (m ? 1u : 0u) : (m ? 0u : 1u));
