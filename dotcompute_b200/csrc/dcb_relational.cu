@@ -158,13 +158,26 @@ __global__ void __launch_bounds__(kThreads, 3) radix_scatter(const K* __restrict
         key[i] = e < n ? keys_in[e] : (K)0;
         pay[i] = e < n ? idx_in[e] : 0u;
     }
-    // (Issuing the sixteen counter updates as shared-memory atomics whose results are used later, instead of waiting for
-    // shared memory in every round, measured slower: 767 us a pass against 636 us, at 117 registers instead of 87.)
+    // The lanes that hold the same digit: one ballot per bit (nine of them: bin 256 is the ninth bit). match.any walks
+    // through the distinct values of the warp one by one, about thirty of them for random digits.
+    auto peers_of = [&](u32 d) -> u32 {
+        u32 peers = 0xffffffffu;
+#pragma unroll
+        for (int bit = 0; bit < 9; ++bit) {
+            const bool on = ((d >> bit) & 1u) != 0u;
+            const u32 m = __ballot_sync(0xffffffffu, on);
+            peers &= on ? m : ~m;
+        }
+        return peers;
+    };
+    // (Shared-memory atomics whose results are used only after all sixteen are in flight, instead of a read and a write of
+    // the counter per item, measured slower twice: 767 against 636 us a pass with match.any, 3.7 against 3.0 ms a sort with
+    // the ballots.)
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const i64 e = run + i * 32 + lane;
         const u32 d = e < n ? ((u32)(key[i] >> shift) & 255u) : 256u;
-        const u32 peers = __match_any_sync(0xffffffffu, d);
+        const u32 peers = peers_of(d);
         const u32 before = s_cnt[warp][d];
         __syncwarp();
         if ((peers & lt) == 0u) s_cnt[warp][d] = before + (u32)__popc(peers);   // the first lane of each group of equal digits
