@@ -217,8 +217,8 @@ dcb_status ensure_scratch(dcb_pipeline* p, int64_t num_tiles, cudaStream_t s, Sc
     *out = &sc;
     if (!sc.partials) {
         CU(ctx, cudaMalloc(&sc.partials, sizeof(dcb::Partial) * kMaxPartials));
-        CU(ctx, cudaMalloc(&sc.words, 512));
-        CU(ctx, cudaMemsetAsync(sc.words, 0, 512, s));
+        CU(ctx, cudaMalloc(&sc.words, 1024));   // words 0..127: compaction (counters at 32, abort word at 64); 128..192: the reductions' tickets
+        CU(ctx, cudaMemsetAsync(sc.words, 0, 1024, s));
     }
     if ((size_t)num_tiles > sc.desc_cap) {
         size_t cap = std::max<size_t>((size_t)num_tiles, 1024);
@@ -1046,7 +1046,7 @@ dcb_status run_async_launch(dcb_pipeline* p, const void* in0, const void* in1, i
         int64_t max_grid = (int64_t)ctx->sm_count * std::min(occ_cap, vec ? p->occ_vec : p->occ_scalar);
         max_grid = std::min<int64_t>(max_grid, kMaxPartials);
         const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(tiles, max_grid));
-        unsigned int* ticket = scp->words;
+        unsigned int* ticket = scp->words + 128;   // main word and one word per group of blocks (last_block_ticket)
         void* args[] = {(void*)&in0, (void*)&in1, (void*)&nn, (void*)&scp->partials, (void*)&ticket, (void*)&res};
         if (launches) *launches += 1;
         if (ctx->opt_overlap_launches) {
